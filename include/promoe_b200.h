@@ -1,0 +1,209 @@
+/*
+ * promoe_b200 -- C ABI of the B200-native MoE hot path (expert cache + fused MoE layer).
+ *
+ * Every function returns 0 on success or a PM_ERR_* code; none aborts the process.
+ * pm_last_error() gives the message of the last failure on the calling thread.
+ * Device pointers are plain CUDA device addresses; `stream` is a cudaStream_t
+ * passed as void* (NULL = the legacy default stream). A context must be used by
+ * one thread at a time.
+ *
+ * The citations name the reference (huwf5/promoe) interface each entry point
+ * stands in for, by the file's path inside that project.
+ */
+#ifndef PROMOE_B200_H_
+#define PROMOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PM_OK 0
+#define PM_ERR_INVALID 1   /* bad argument or configuration */
+#define PM_ERR_CUDA 2      /* a CUDA runtime / driver call failed */
+#define PM_ERR_STATE 3     /* call made in the wrong phase (e.g. forward before build_slab) */
+#define PM_ERR_UNSUPPORTED 4
+#define PM_ERR_TIMEOUT 5   /* a bounded host wait ran out */
+
+typedef struct pm_ctx pm_ctx;
+
+/* ---- library ---------------------------------------------------------- */
+int pm_version(void);
+/* Message of the last error on this thread ("" if none). */
+const char* pm_last_error(void);
+
+/* ---- configuration (ModuleMeta: src/cpp_worker/utils.hpp:127-192,
+ *      init_from_map / handle_uninited_configs: src/cpp_worker/utils.cpp:54-273) ---- */
+
+/* Creates a context for num_layer MoE layers of num_expert routed experts.
+ * config_kv holds "key=value" lines with the reference's config keys (cache_rate,
+ * cache_policy, num_expert_per_token, num_predict_expert_per_layer, reorder_experts,
+ * early_preempt, chunk_prefetch, per_layer_cache, promote_hit_in_prefetch,
+ * layer_predict_interval, layer_predict_max_window, limit_layer_0_window,
+ * limit_layer_0_num_predict, model_arch_string, ... and their dialect aliases).
+ * Values "None" or "" select the default. Unknown keys are an error (the reference aborts). */
+int pm_ctx_create(pm_ctx** out, int num_layer, int num_expert, const char* config_kv);
+int pm_ctx_destroy(pm_ctx* ctx);
+/* Reads one resolved configuration value as text into buf (NUL-terminated). */
+int pm_ctx_get(pm_ctx* ctx, const char* key, char* buf, size_t cap);
+/* Overrides one configuration value after creation (same keys as pm_ctx_get). */
+int pm_ctx_set(pm_ctx* ctx, const char* key, const char* value);
+/* Names of the per-expert tensors, in chunk order (ModuleMeta::init_param_list,
+ * src/cpp_worker/utils.cpp:47-53). names = '\n'-separated. */
+int pm_ctx_set_param_list(pm_ctx* ctx, const char* names);
+
+/* ---- expert registry and slab (ModelLoader: src/cpp_worker/model_loader.hpp:276-319,
+ *      src/cpp_worker/model_loader.cpp:8-31; CacheMngr::init_gpu_mem_buffer:
+ *      src/cpp_worker/cache.cpp:57-132; PrefetchMngr::init_gpu_mem_buffer:
+ *      src/cpp_worker/prefetcher.cpp:162-177) ---- */
+
+/* Registers the host copy of one tensor of one expert. The bytes stay owned by the caller
+ * until pm_pin_all, which copies them into the library's pinned arena (one contiguous
+ * record per expert, so a miss is a single DMA). */
+int pm_register_expert_param(pm_ctx* ctx, int layer, int expert, int param_id, const void* host_ptr,
+                             size_t nbytes);
+int pm_pin_all(pm_ctx* ctx);
+/* Number of cache lines each layer gets (length num_layer, or 1 when per_layer_cache is off). */
+int pm_plan_slots(pm_ctx* ctx, int32_t* per_pool_len, int cap, int* n_pools);
+/* Reserves the VMM range and maps one physical allocation per cache line. */
+int pm_build_slab(pm_ctx* ctx);
+/* Builds the slot pools without any device memory (policy-only use, no GPU needed). */
+int pm_build_policy_only(pm_ctx* ctx);
+/* Device address the tensor currently has in the slab, NULL if the expert is not resident
+ * (ModelLoader::ref_one_expert_param, src/cpp_worker/model_loader.hpp:309-314). */
+int pm_param_device_ptr(pm_ctx* ctx, int layer, int expert, int param_id, void** out);
+/* Slot (index inside the layer's pool, creation order) of an expert, -1 if absent. */
+int pm_expert_slot(pm_ctx* ctx, int layer, int expert, int32_t* slot);
+
+/* ---- cache policy and fetch schedule (PrefetchMngr / FetchScheduleWorker:
+ *      src/cpp_worker/prefetcher.cpp:6-161,188-267,494-659; CacheMngr::hit/miss:
+ *      src/cpp_worker/cache.cpp:236-312; policies: src/cpp_worker/cache.hpp:24-224) ---- */
+
+/* Reports the unique experts one layer call activates. ids is reordered in place when
+ * reorder_experts is on (PrefetchMngr::report_one_layer). Runs the hit/miss/evict
+ * decisions of the sequential schedule and, when a slab exists, enqueues the copies. */
+int pm_report_layer(pm_ctx* ctx, int layer, int64_t* ids, int64_t n);
+/* Queues a prefetch of `ids` (rank order) for `layer` and drains it
+ * (FetchScheduleWorker PrefetchLayerTask, src/cpp_worker/prefetcher.cpp:585-611). */
+int pm_prefetch_layer(pm_ctx* ctx, int layer, const int64_t* ids, int64_t n);
+/* PrefetchMngr::report_one_expert / one_expert_done / one_moe_layer_done
+ * (src/cpp_worker/prefetcher.cpp:203-267). */
+int pm_report_expert(pm_ctx* ctx, int layer, int expert);
+int pm_expert_done(pm_ctx* ctx, int layer, int expert);
+int pm_layer_done(pm_ctx* ctx, int layer);
+/* CacheMngr::set_cur_seq (src/cpp_worker/cache.hpp:310-314), Belady policy only. */
+int pm_set_cur_seq(pm_ctx* ctx, uint64_t seq_id);
+/* Loads the Belady (MIN) trace: per (seq, layer, expert) ascending use times
+ * (CacheOracle::load_from_tensor, src/cpp_worker/cache.cpp:592-644). */
+int pm_oracle_add_use_times(pm_ctx* ctx, uint64_t seq_id, int layer, int expert, const int64_t* times,
+                            int64_t n);
+/* CacheMngr::update_priority (src/cpp_worker/cache.cpp:400-430,584-591): prob is
+ * [n_layers, num_expert] float32 for layers start_layer.. */
+int pm_update_priority(pm_ctx* ctx, const float* prob, int n_layers, int start_layer);
+
+/* One cache decision, in the order the schedule performed it. */
+typedef struct pm_event {
+  int32_t kind;    /* 0 precise hit, 1 precise miss, 2 prefetch hit, 3 prefetch miss */
+  int32_t layer;
+  int32_t expert;
+  int32_t slot;    /* index of the cache line inside its pool, creation order */
+  int32_t evicted; /* expert that lost the line (same pool), -1 if the line was free */
+  int32_t evicted_layer;
+} pm_event;
+int pm_event_log_enable(pm_ctx* ctx, int on);
+int pm_event_log_read(pm_ctx* ctx, pm_event* out, size_t cap, size_t* n);
+int pm_event_log_clear(pm_ctx* ctx);
+
+/* Counters (TimeProfiler series, src/cpp_worker/profiler.hpp:262-275), totals since creation. */
+typedef struct pm_stats {
+  int64_t precise_hit, precise_miss, prefetch_hit, prefetch_miss;
+  int64_t ready, unready;
+  int64_t activated_experts, layer_calls;
+  int64_t h2d_bytes, h2d_copies;
+  int64_t kernel_launches;
+} pm_stats;
+int pm_stats_read(pm_ctx* ctx, pm_stats* out);
+
+/* ---- fused MoE layer ---------------------------------------------------- */
+typedef struct pm_layer_weights {
+  const void* gate_w;        /* device bf16 [num_expert, hidden] */
+  const float* gate_bias;    /* device f32 [num_expert] or NULL */
+  const void* shared_gate_w; /* device bf16 [hidden] or NULL (sigmoid gate on the shared expert) */
+  const void* shared_w_gate; /* device bf16 [shared_inter, hidden] or NULL */
+  const void* shared_w_up;   /* device bf16 [shared_inter, hidden] */
+  const void* shared_w_down; /* device bf16 [hidden, shared_inter] */
+  int32_t hidden;
+  int32_t inter;        /* routed expert intermediate size */
+  int32_t shared_inter; /* 0 = no shared expert */
+  int32_t top_k;
+  int32_t norm_topk;    /* renormalise the k selected probabilities */
+  float routed_scale;   /* multiplies the routing weights */
+  int32_t quant4;       /* routed experts are uint4 group-128 (params: q, scale/zero per matrix) */
+} pm_layer_weights;
+int pm_layer_set_weights(pm_ctx* ctx, int layer, const pm_layer_weights* w);
+
+/* One MoE layer forward on device buffers: x [T, hidden] bf16 -> y [T, hidden] bf16.
+ * Runs K1 (route) and K2 (permute), reads the expert counts back, performs the
+ * report_layer bookkeeping and copies, then K3 (grouped SwiGLU FFN by slot) and K4 (combine).
+ * Stands in for the MoE block forward the reference patches into transformers
+ * (src/sparse_llm_cache/utils/__init__.py:82-89) plus the ExpertHook / MoeLayerHook calls
+ * around it (src/sparse_llm_cache/utils/hooks.py:187-223). */
+int pm_moe_forward(pm_ctx* ctx, int layer, const void* x_dev, int T, void* y_dev, void* stream);
+/* Same with host buffers (pinned or pageable): copies x in and y out on the stream and waits. */
+int pm_moe_forward_host(pm_ctx* ctx, int layer, const void* x_host, int T, void* y_host, void* stream);
+/* Routing of the most recent pm_moe_forward on `layer` (host copies): ids/weights [T, k]. */
+int pm_last_routing(pm_ctx* ctx, int layer, int32_t* topk_ids, float* topk_w, int cap_pairs);
+
+/* Next-layer expert predictor (SepPredictor + PredictWorker: src/cpp_worker/predictor.cpp:558-607,
+ * src/cpp_worker/worker.cpp:6-77). Weights are device pointers of one MLP
+ * hidden -> d -> num_expert (bf16 matrices, f32 biases, ReLU) used for hidden states captured
+ * at input index src_layer to predict dst_layer. */
+int pm_predictor_set(pm_ctx* ctx, int src_layer, int dst_layer, const void* w1, const float* b1, int d,
+                     const void* w2, const float* b2);
+/* PrefetchMngr::report_moe_layer_logits (src/cpp_worker/prefetcher.cpp:447-460): hidden states
+ * [B, seq, hidden] bf16 entering layer `index` (index == num_layer: output of the last layer).
+ * Decode (seq == 1) runs the predictor on the device and issues the prefetches it ranks. */
+int pm_report_hidden(pm_ctx* ctx, int index, const void* hidden_dev, int B, int seq, void* stream);
+
+/* ---- stateless kernels (each usable on its own) -------------------------- */
+int pm_k_gate_topk(const void* x, const void* gate_w, const float* gate_bias, const void* shared_gate_w,
+                   int T, int H, int E, int k, int norm_topk, float routed_scale,
+                   const int32_t* expert_slot, int32_t* topk_ids, float* topk_w, int32_t* topk_slot,
+                   float* shared_scale, float* logits_out, void* stream);
+int pm_k_permute(const int32_t* topk_ids, int R, int k, int E, int32_t* counts, int32_t* offsets,
+                 int32_t* row_token, int32_t* pos, int32_t* err_flag, void* stream);
+
+/* One group of rows sharing one set of FFN weights (device pointers). */
+typedef struct pm_ffn_group {
+  const void* w_gate; /* bf16 [inter, hidden], or packed uint4 [inter, hidden/2] when quant4 */
+  const void* w_up;
+  const void* w_down; /* bf16 [hidden, inter], or packed uint4 [hidden, inter/2] */
+  const void* q_gate; /* quant4: fp16 {scale, zero} pairs [inter, hidden/128]; else NULL */
+  const void* q_up;
+  const void* q_down; /* quant4: [hidden, inter/128] */
+  int32_t row_start;  /* first permuted row */
+  int32_t row_count;
+  int32_t inter;
+  int32_t pad;
+} pm_ffn_group;
+/* Bytes of device scratch pm_k_swiglu_ffn needs for n_rows rows in n_groups groups. */
+size_t pm_k_swiglu_ffn_scratch_bytes(int n_groups, int n_rows, int max_inter);
+/* Grouped SwiGLU FFN: yexp[r, :] = down(silu(gate(x[row_token[r]])) * up(x[row_token[r]])) for
+ * every row r of every group. groups is a HOST array; scratch is device memory of at least
+ * pm_k_swiglu_ffn_scratch_bytes(). yexp is f32 [n_rows, hidden]. */
+int pm_k_swiglu_ffn(const pm_ffn_group* groups, int n_groups, int quant4, const void* x, int hidden,
+                    const int32_t* row_token, int n_rows, float* yexp, void* scratch,
+                    size_t scratch_bytes, void* stream);
+int pm_k_combine(const float* yexp, const int32_t* pos, const float* topk_w, int T, int H, int k, int R,
+                 int n_shared, const float* shared_scale, void* y, void* stream);
+/* scores[e] = sum_b (W2 relu(W1 x_b + b1) + b2)[e]; hidden_scratch is f32 [B, d] device scratch. */
+int pm_k_predictor_mlp(const void* x, int B, int H, const void* w1, const float* b1, int d,
+                       const void* w2, const float* b2, int E, float* hidden_scratch, float* scores,
+                       void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PROMOE_B200_H_ */

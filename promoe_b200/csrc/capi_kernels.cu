@@ -1,0 +1,145 @@
+// C-ABI entry points of the stateless kernels, plus the per-thread error message.
+#include <algorithm>
+#include <cstring>
+#include <vector>
+
+#include "pm_common.cuh"
+
+namespace pm {
+
+static thread_local std::string g_last_error;
+
+int fail(int code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+
+int fail_cuda(cudaError_t e, const char* what) {
+  g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+  return PM_ERR_CUDA;
+}
+
+// Splits the caller's groups into chunks of at most kMaxChunkRows rows, assigns CTA tile
+// ranges and returns the descriptors (host) plus launch geometry.
+int plan_groups(const pm_ffn_group* groups, int n_groups, int hidden, std::vector<GroupDesc>* out,
+                int* tiles_gu, int* tiles_dn, int* max_rows, int* max_inter) {
+  out->clear();
+  int tg = 0, td = 0, mr = 0, mi = 0;
+  if (hidden % 64 != 0) return fail(PM_ERR_INVALID, "hidden must be a multiple of 64");
+  for (int i = 0; i < n_groups; ++i) {
+    const pm_ffn_group& g = groups[i];
+    if (g.row_count <= 0) continue;
+    if (g.inter % 32 != 0 || g.inter <= 0) return fail(PM_ERR_INVALID, "inter must be a positive multiple of 32");
+    for (int r0 = 0; r0 < g.row_count; r0 += kMaxChunkRows) {
+      GroupDesc d{};
+      d.w_gate = g.w_gate; d.w_up = g.w_up; d.w_down = g.w_down;
+      d.q_gate = g.q_gate; d.q_up = g.q_up; d.q_down = g.q_down;
+      d.row_start = g.row_start + r0;
+      d.row_count = std::min(kMaxChunkRows, g.row_count - r0);
+      d.inter = g.inter;
+      d.tile_start_gu = tg;
+      d.tile_start_dn = td;
+      tg += (g.inter + kTileRows - 1) / kTileRows;
+      td += hidden / kTileRows;
+      mr = std::max(mr, d.row_count);
+      mi = std::max(mi, g.inter);
+      out->push_back(d);
+    }
+  }
+  *tiles_gu = tg; *tiles_dn = td; *max_rows = mr; *max_inter = mi;
+  return PM_OK;
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace pm
+
+using namespace pm;
+
+extern "C" {
+
+int pm_version(void) { return 100; }
+
+const char* pm_last_error(void) { return g_last_error.c_str(); }
+
+int pm_k_gate_topk(const void* x, const void* gate_w, const float* gate_bias, const void* shared_gate_w,
+                   int T, int H, int E, int k, int norm_topk, float routed_scale,
+                   const int32_t* expert_slot, int32_t* topk_ids, float* topk_w, int32_t* topk_slot,
+                   float* shared_scale, float* logits_out, void* stream) {
+  if (T < 0 || H <= 0 || H % 8 != 0) return fail(PM_ERR_INVALID, "gate_topk: hidden must be a positive multiple of 8");
+  if (E <= 0 || E > 256) return fail(PM_ERR_INVALID, "gate_topk: num_expert must be in [1, 256]");
+  if (k <= 0 || k > 16 || k > E) return fail(PM_ERR_INVALID, "gate_topk: top_k must be in [1, min(16, num_expert)]");
+  if (T == 0) return PM_OK;
+  if (!x || !gate_w || !topk_ids || !topk_w) return fail(PM_ERR_INVALID, "gate_topk: null pointer");
+  PM_CUDA(launch_gate_topk((const __nv_bfloat16*)x, (const __nv_bfloat16*)gate_w, gate_bias,
+                           (const __nv_bfloat16*)shared_gate_w, T, H, E, k, norm_topk, routed_scale,
+                           expert_slot, topk_ids, topk_w, topk_slot, shared_scale, logits_out,
+                           (cudaStream_t)stream));
+  return PM_OK;
+}
+
+int pm_k_permute(const int32_t* topk_ids, int R, int k, int E, int32_t* counts, int32_t* offsets,
+                 int32_t* row_token, int32_t* pos, int32_t* err_flag, void* stream) {
+  if (R < 0 || k <= 0 || E <= 0 || E > 256) return fail(PM_ERR_INVALID, "permute: bad sizes");
+  if (!counts || !offsets) return fail(PM_ERR_INVALID, "permute: null pointer");
+  if (R > 0 && (!topk_ids || !row_token || !pos)) return fail(PM_ERR_INVALID, "permute: null pointer");
+  PM_CUDA(launch_permute(topk_ids, R, k, E, counts, offsets, row_token, pos, err_flag, (cudaStream_t)stream));
+  return PM_OK;
+}
+
+size_t pm_k_swiglu_ffn_scratch_bytes(int n_groups, int n_rows, int max_inter) {
+  if (n_groups < 0 || n_rows < 0 || max_inter < 0) return 0;
+  // descriptors (groups may split into chunks of kMaxChunkRows rows) + intermediate h rows
+  size_t n_desc = (size_t)n_groups + (size_t)n_rows / kMaxChunkRows + 1;
+  return align_up(n_desc * sizeof(GroupDesc), 256) + align_up((size_t)n_rows * max_inter * 2, 256);
+}
+
+int pm_k_swiglu_ffn(const pm_ffn_group* groups, int n_groups, int quant4, const void* x, int hidden,
+                    const int32_t* row_token, int n_rows, float* yexp, void* scratch,
+                    size_t scratch_bytes, void* stream) {
+  if (n_groups < 0 || n_rows < 0) return fail(PM_ERR_INVALID, "swiglu_ffn: negative size");
+  if (n_groups == 0 || n_rows == 0) return PM_OK;
+  if (!groups || !x || !row_token || !yexp || !scratch) return fail(PM_ERR_INVALID, "swiglu_ffn: null pointer");
+  std::vector<GroupDesc> desc;
+  int tg, td, mr, mi;
+  int rc = plan_groups(groups, n_groups, hidden, &desc, &tg, &td, &mr, &mi);
+  if (rc != PM_OK) return rc;
+  if (desc.empty()) return PM_OK;
+  for (const GroupDesc& d : desc)
+    if (d.row_start < 0 || d.row_start + d.row_count > n_rows)
+      return fail(PM_ERR_INVALID, "swiglu_ffn: group rows outside [0, n_rows)");
+  const size_t desc_bytes = align_up(desc.size() * sizeof(GroupDesc), 256);
+  const size_t need = desc_bytes + align_up((size_t)n_rows * mi * 2, 256);
+  if (scratch_bytes < need) return fail(PM_ERR_INVALID, "swiglu_ffn: scratch too small");
+  cudaStream_t s = (cudaStream_t)stream;
+  // The descriptor upload is from pageable memory, so it is staged before this call returns.
+  PM_CUDA(cudaMemcpyAsync(scratch, desc.data(), desc.size() * sizeof(GroupDesc), cudaMemcpyHostToDevice, s));
+  __nv_bfloat16* hbuf = (__nv_bfloat16*)((unsigned char*)scratch + desc_bytes);
+  PM_CUDA(launch_swiglu_ffn((const GroupDesc*)scratch, (int)desc.size(), tg, td, mr, quant4,
+                            (const __nv_bfloat16*)x, hidden, row_token, hbuf, mi, yexp, s));
+  return PM_OK;
+}
+
+int pm_k_combine(const float* yexp, const int32_t* pos, const float* topk_w, int T, int H, int k, int R,
+                 int n_shared, const float* shared_scale, void* y, void* stream) {
+  if (T < 0 || H <= 0 || H % 4 != 0 || k <= 0 || k > 16) return fail(PM_ERR_INVALID, "combine: bad sizes");
+  if (T == 0) return PM_OK;
+  if (!yexp || !pos || !topk_w || !y) return fail(PM_ERR_INVALID, "combine: null pointer");
+  PM_CUDA(launch_combine(yexp, pos, topk_w, T, H, k, R, n_shared, shared_scale, (__nv_bfloat16*)y,
+                         (cudaStream_t)stream));
+  return PM_OK;
+}
+
+int pm_k_predictor_mlp(const void* x, int B, int H, const void* w1, const float* b1, int d,
+                       const void* w2, const float* b2, int E, float* hidden_scratch, float* scores,
+                       void* stream) {
+  if (B < 0 || H <= 0 || H % 8 != 0 || d <= 0 || E <= 0) return fail(PM_ERR_INVALID, "predictor_mlp: bad sizes");
+  if (B == 0) return PM_OK;
+  if (!x || !w1 || !w2 || !hidden_scratch || !scores) return fail(PM_ERR_INVALID, "predictor_mlp: null pointer");
+  PM_CUDA(launch_predictor_mlp((const __nv_bfloat16*)x, B, H, (const __nv_bfloat16*)w1, b1, d,
+                               (const __nv_bfloat16*)w2, b2, E, hidden_scratch, scores,
+                               (cudaStream_t)stream));
+  return PM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,169 @@
+// K1: router. One CTA per token computes the gate logits of every expert, selects
+// the top-k experts, turns the selection into combine weights and looks the
+// selected experts up in the layer's expert -> cache-slot table.
+//
+// This replaces the first half of the MoE block forward that the reference
+// delegates to its patched transformers fork (gate linear -> softmax -> top-k ->
+// optional renormalisation; contract: src/sparse_llm_cache/utils/__init__.py:82-89,
+// eval/demo-simulate/transformers-deepseek-moe.py:36-49).
+//
+// Selection is done on the logits (softmax is monotonic), ties go to the lower
+// expert id, and the dot product uses a fixed summation order so that a host
+// restatement in float32 reproduces the logits bit for bit:
+//   lane j of a warp accumulates the 8-element vectors v with v % 32 == j in
+//   ascending v, elements 0..7 in order, acc = acc + w*x (the product of two
+//   bf16 values is exact in float32, so fused and unfused multiply-add agree);
+//   lanes are then combined by a butterfly over lane ^ 16, 8, 4, 2, 1.
+#include "pm_common.cuh"
+
+namespace pm {
+namespace {
+
+constexpr int kGateThreads = 256;
+constexpr int kMaxExperts = 256;
+
+__device__ __forceinline__ float canonical_dot(const uint4* __restrict__ w, const uint4* xs, int nvec,
+                                               int lane) {
+  float acc = 0.f;
+  for (int v = lane; v < nvec; v += 32) {
+    uint4 wv = __ldg(w + v);
+    uint4 xv = xs[v];
+    const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+    const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 wf = __bfloat1622float2(wp[i]);
+      float2 xf = __bfloat1622float2(xp[i]);
+      acc = __fmaf_rn(wf.x, xf.x, acc);
+      acc = __fmaf_rn(wf.y, xf.y, acc);
+    }
+  }
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+  return acc;
+}
+
+__global__ void __launch_bounds__(kGateThreads)
+gate_topk_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_gate,
+                 const float* __restrict__ bias, const __nv_bfloat16* __restrict__ w_shared_gate,
+                 int T, int H, int E, int k, int norm_topk, float routed_scale,
+                 const int32_t* __restrict__ expert_slot, int32_t* __restrict__ topk_ids,
+                 float* __restrict__ topk_w, int32_t* __restrict__ topk_slot,
+                 float* __restrict__ shared_scale, float* __restrict__ logits_out) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint4* xs = reinterpret_cast<uint4*>(smem_raw);           // H bf16
+  float* logit_s = reinterpret_cast<float*>(xs + H / 8);    // E (+1 for the shared gate)
+
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nwarp = kGateThreads / 32;
+  const int nvec = H / 8;
+
+  const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)t * H);
+  for (int v = threadIdx.x; v < nvec; v += kGateThreads) xs[v] = __ldg(xrow + v);
+  __syncthreads();
+
+  const int n_rows = E + (w_shared_gate != nullptr ? 1 : 0);
+  for (int e = warp; e < n_rows; e += nwarp) {
+    const uint4* wrow = (e < E) ? reinterpret_cast<const uint4*>(w_gate + (size_t)e * H)
+                                : reinterpret_cast<const uint4*>(w_shared_gate);
+    float d = canonical_dot(wrow, xs, nvec, lane);
+    if (lane == 0) {
+      if (e < E && bias != nullptr) d += bias[e];
+      logit_s[e] = d;
+    }
+  }
+  __syncthreads();
+
+  if (warp != 0) return;
+
+  if (logits_out != nullptr)
+    for (int e = lane; e < E; e += 32) logits_out[(size_t)t * E + e] = logit_s[e];
+  if (w_shared_gate != nullptr && lane == 0 && shared_scale != nullptr)
+    shared_scale[t] = 1.f / (1.f + __expf(-logit_s[E]));
+
+  // Each lane owns experts lane, lane+32, ...
+  constexpr int kPerLane = kMaxExperts / 32;
+  float v[kPerLane];
+  float vmax = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    int e = lane + 32 * i;
+    v[i] = (e < E) ? logit_s[e] : -INFINITY;
+    vmax = fmaxf(vmax, v[i]);
+  }
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, m));
+  float denom = 0.f;
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i)
+    if (lane + 32 * i < E) denom += __expf(v[i] - vmax);
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, m);
+
+  float sel_p = 0.f;   // lane j keeps the probability of the j-th selected expert
+  int sel_e = -1;
+  float sel_sum = 0.f;
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      int e = lane + 32 * i;
+      if (e < E && (v[i] > best)) {  // ascending e per lane: strict > keeps the lower id on ties
+        best = v[i];
+        best_e = e;
+      }
+    }
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) {
+      float ob = __shfl_xor_sync(0xffffffffu, best, m);
+      int oe = __shfl_xor_sync(0xffffffffu, best_e, m);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+      }
+    }
+    float p = __expf(best - vmax) / denom;
+    sel_sum += p;
+    if (lane == j) {
+      sel_p = p;
+      sel_e = best_e;
+    }
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i)
+      if (lane + 32 * i == best_e) v[i] = -INFINITY;
+  }
+  if (lane < k) {
+    float w = sel_p;
+    if (norm_topk) w = w / (sel_sum + 1e-20f);
+    w *= routed_scale;
+    topk_ids[(size_t)t * k + lane] = sel_e;
+    topk_w[(size_t)t * k + lane] = w;
+    if (topk_slot != nullptr)
+      topk_slot[(size_t)t * k + lane] = (expert_slot != nullptr) ? expert_slot[sel_e] : -1;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_gate_topk(const __nv_bfloat16* x, const __nv_bfloat16* w_gate, const float* bias,
+                             const __nv_bfloat16* w_shared_gate, int T, int H, int E, int k,
+                             int norm_topk, float routed_scale, const int32_t* expert_slot,
+                             int32_t* topk_ids, float* topk_w, int32_t* topk_slot,
+                             float* shared_scale, float* logits_out, cudaStream_t s) {
+  if (T <= 0) return cudaSuccess;
+  size_t smem = (size_t)H * 2 + (size_t)(E + 1) * 4;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(gate_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  gate_topk_kernel<<<T, kGateThreads, smem, s>>>(x, w_gate, bias, w_shared_gate, T, H, E, k, norm_topk,
+                                                 routed_scale, expert_slot, topk_ids, topk_w,
+                                                 topk_slot, shared_scale, logits_out);
+  return cudaGetLastError();
+}
+
+}  // namespace pm

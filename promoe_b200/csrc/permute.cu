@@ -1,0 +1,79 @@
+// K2: token permutation. Turns the [T, k] routing table into per-expert
+// contiguous row ranges: counts[E], offsets[E+1], row_token[R] (the token each
+// permuted row reads) and pos[R] (where routed pair (t, j) landed). The order
+// inside one expert is ascending in t*k + j, so the result is deterministic.
+//
+// The reference has no such step: its patched MoE block loops over experts in
+// Python and indexes the hidden states per expert (contract:
+// eval/demo-simulate/transformers-deepseek-moe.py:41-48). counts[] is also what
+// the host reads back to form the unique expert list it reports to the cache
+// (src/cpp_worker/prefetcher.cpp:188-202).
+#include "pm_common.cuh"
+
+namespace pm {
+namespace {
+
+constexpr int kPermThreads = 1024;
+constexpr int kMaxExperts = 256;
+
+__global__ void __launch_bounds__(kPermThreads)
+permute_kernel(const int32_t* __restrict__ topk_ids, int R, int k, int E, int32_t* __restrict__ counts,
+               int32_t* __restrict__ offsets, int32_t* __restrict__ row_token,
+               int32_t* __restrict__ pos, int32_t* __restrict__ err_flag) {
+  __shared__ int cnt[kMaxExperts];
+  __shared__ int off[kMaxExperts + 1];
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  for (int e = tid; e < E; e += kPermThreads) cnt[e] = 0;
+  __syncthreads();
+  for (int i = tid; i < R; i += kPermThreads) {
+    int e = topk_ids[i];
+    if (e >= 0 && e < E) {
+      atomicAdd(&cnt[e], 1);
+    } else if (err_flag != nullptr) {
+      atomicExch(err_flag, 1);  // id outside [0, E): the pair is dropped
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = run;
+      run += cnt[e];
+    }
+    off[E] = run;
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += kPermThreads) counts[e] = cnt[e];
+  for (int e = tid; e <= E; e += kPermThreads) offsets[e] = off[e];
+
+  // Stable placement: warp w places experts w, w+32, ... by scanning the pairs in order.
+  const unsigned lt_mask = (1u << lane) - 1u;
+  for (int e = warp; e < E; e += kPermThreads / 32) {
+    if (cnt[e] == 0) continue;
+    int base = off[e];
+    for (int c = 0; c < R; c += 32) {
+      int i = c + lane;
+      int id = (i < R) ? topk_ids[i] : -1;
+      unsigned m = __ballot_sync(0xffffffffu, id == e);
+      if (id == e) {
+        int p = base + __popc(m & lt_mask);
+        row_token[p] = i / k;
+        pos[i] = p;
+      }
+      base += __popc(m);
+    }
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_permute(const int32_t* topk_ids, int R, int k, int E, int32_t* counts,
+                           int32_t* offsets, int32_t* row_token, int32_t* pos, int32_t* err_flag,
+                           cudaStream_t s) {
+  permute_kernel<<<1, kPermThreads, 0, s>>>(topk_ids, R, k, E, counts, offsets, row_token, pos, err_flag);
+  return cudaGetLastError();
+}
+
+}  // namespace pm

@@ -1,0 +1,76 @@
+// Shared declarations for the sm_100a kernels and the host runtime of the MoE hot path.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#pragma GCC visibility push(default)
+#include "../../include/promoe_b200.h"
+#pragma GCC visibility pop
+
+namespace pm {
+
+// Records a message retrievable through pm_last_error(NULL) and returns `code`.
+int fail(int code, const std::string& msg);
+int fail_cuda(cudaError_t e, const char* what);
+
+#define PM_CUDA(expr)                                         \
+  do {                                                        \
+    cudaError_t pm_e_ = (expr);                               \
+    if (pm_e_ != cudaSuccess) return pm::fail_cuda(pm_e_, #expr); \
+  } while (0)
+
+// One chunk of rows that share one set of FFN weights: a routed expert resolved
+// to its cache slot, or a shared expert. Rows are positions in the permuted
+// (expert-sorted) row order; a chunk never holds more than kMaxChunkRows rows.
+struct GroupDesc {
+  const void* w_gate;   // [inter, hidden] bf16, or packed uint4 [inter, hidden/2]
+  const void* w_up;     // same layout as w_gate
+  const void* w_down;   // [hidden, inter] bf16, or packed uint4 [hidden, inter/2]
+  const void* q_gate;   // int4 only: per (row, 128-group) {scale, zero} fp16 pairs
+  const void* q_up;
+  const void* q_down;
+  int32_t row_start;
+  int32_t row_count;
+  int32_t inter;
+  int32_t tile_start_gu;  // first CTA tile of this chunk in the gate/up launch
+  int32_t tile_start_dn;  // first CTA tile of this chunk in the down launch
+  int32_t pad;
+};
+
+constexpr int kTileRows = 64;       // weight rows per CTA tile (4 warps x 16)
+constexpr int kMaxChunkRows = 64;   // token rows per chunk (8 MMA n-tiles)
+
+// Kernel launchers (defined in the .cu files). All take the caller's stream.
+cudaError_t launch_gate_topk(const __nv_bfloat16* x, const __nv_bfloat16* w_gate, const float* bias,
+                             const __nv_bfloat16* w_shared_gate, int T, int H, int E, int k,
+                             int norm_topk, float routed_scale, const int32_t* expert_slot,
+                             int32_t* topk_ids, float* topk_w, int32_t* topk_slot,
+                             float* shared_scale, float* logits_out, cudaStream_t s);
+
+cudaError_t launch_permute(const int32_t* topk_ids, int R, int k, int E, int32_t* counts,
+                           int32_t* offsets, int32_t* row_token, int32_t* pos, int32_t* err_flag,
+                           cudaStream_t s);
+
+cudaError_t launch_swiglu_ffn(const GroupDesc* groups_dev, int n_groups, int tiles_gu, int tiles_dn,
+                              int max_rows, int quant4, const __nv_bfloat16* x, int H,
+                              const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h, float* yexp,
+                              cudaStream_t s);
+
+cudaError_t launch_combine(const float* yexp, const int32_t* pos, const float* topk_w, int T, int H,
+                           int k, int R, int n_shared, const float* shared_scale,
+                           __nv_bfloat16* y, cudaStream_t s);
+
+// Splits caller groups into chunks of at most kMaxChunkRows rows and assigns CTA tile ranges.
+int plan_groups(const pm_ffn_group* groups, int n_groups, int hidden, std::vector<GroupDesc>* out,
+                int* tiles_gu, int* tiles_dn, int* max_rows, int* max_inter);
+
+cudaError_t launch_predictor_mlp(const __nv_bfloat16* x, int B, int H, const __nv_bfloat16* w1,
+                                 const float* b1, int D, const __nv_bfloat16* w2, const float* b2,
+                                 int E, float* hidden_scratch, float* scores, cudaStream_t s);
+
+}  // namespace pm

@@ -1,0 +1,233 @@
+// K3a: grouped SwiGLU expert FFN for decode-size batches, weights read by cache-slot
+// indirection. Two launches per layer:
+//   gate/up : h[r, i] = silu(x_r . Wg[i, :]) * (x_r . Wu[i, :])
+//   down    : y[r, n] = h_r . Wd[n, :]
+// Every CTA tile streams 64 weight rows (4 warps x 16 rows) exactly once from HBM
+// and applies them to all token rows of its chunk (up to 64) with warp-level
+// bf16 MMAs, fp32 accumulation. The kernel is HBM-bound: the weight bytes of each
+// activated expert are the algorithmic traffic.
+//
+// It replaces the per-expert Python loop over torch linears that the reference
+// drives through ExpertHook (src/sparse_llm_cache/utils/hooks.py:187-198) after
+// report_experts (src/sparse_llm_cache/utils/__init__.py:82-89); the weights it
+// reads are the cache lines the reference re-points module parameters to
+// (src/sparse_llm_cache/utils/__init__.py:58-69).
+//
+// Operand layout trick: a dot product does not care about the order of k, so each
+// lane loads 16 contiguous bytes (8 bf16) of a weight row and of a token row at
+// the same k offset and feeds pairs {0,1} and {2,3} to one m16n8k16 MMA and pairs
+// {4,5}, {6,7} to a second one. Both operands therefore use full 128-bit loads.
+#include "pm_common.cuh"
+
+namespace pm {
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kPadElems = 32;  // 64 B of padding per staged token row: conflict-free 128-bit reads
+constexpr int kDepth = 4;      // k-steps of weight loads issued back to back per lane
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float silu(float v) { return v / (1.f + __expf(-v)); }
+
+// Finds the chunk whose tile range holds `tile`. Chunks are sorted by tile start.
+template <bool GATEUP>
+__device__ __forceinline__ int find_group(const GroupDesc* __restrict__ groups, int n_groups, int tile) {
+  int lo = 0, hi = n_groups - 1;
+  while (lo < hi) {
+    int mid = (lo + hi + 1) >> 1;
+    int start = GATEUP ? groups[mid].tile_start_gu : groups[mid].tile_start_dn;
+    if (start <= tile) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+// NT = number of 8-row n-tiles of tokens a chunk may hold (rows <= 8*NT).
+// NMAT = 2 for the gate/up pass (two weight streams, SwiGLU epilogue), 1 for down.
+template <int NT, int NMAT>
+__global__ void __launch_bounds__(kThreads)
+grouped_ffn_kernel(const GroupDesc* __restrict__ groups, int n_groups,
+                   const __nv_bfloat16* __restrict__ bsrc, int ldb,
+                   const int32_t* __restrict__ row_token, int hidden, int kc_cap,
+                   __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp) {
+  constexpr bool GATEUP = (NMAT == 2);
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint4* xs = reinterpret_cast<uint4*>(smem_raw);
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int g = lane >> 2;
+  const int q = lane & 3;
+
+  const int gi = find_group<GATEUP>(groups, n_groups, blockIdx.x);
+  const GroupDesc grp = groups[gi];
+  const int tile_local = blockIdx.x - (GATEUP ? grp.tile_start_gu : grp.tile_start_dn);
+  const int K = GATEUP ? hidden : grp.inter;       // reduction length
+  const int M = GATEUP ? grp.inter : hidden;       // weight rows
+  const int m0 = tile_local * kTileRows + warp * 16;
+  const bool active = (m0 + 16 <= M);
+  const int rows = grp.row_count;
+
+  const int kc = min(K, kc_cap);
+  const int xs_stride = (kc_cap + kPadElems) / 8;  // in uint4
+
+  const unsigned char* a_ptr[NMAT][2];
+  {
+    const size_t row_bytes = (size_t)K * 2;
+    const unsigned char* w0 = reinterpret_cast<const unsigned char*>(GATEUP ? grp.w_gate : grp.w_down);
+    const int mr = active ? m0 : 0;
+    a_ptr[0][0] = w0 + (size_t)(mr + g) * row_bytes + q * 16;
+    a_ptr[0][1] = w0 + (size_t)(mr + g + 8) * row_bytes + q * 16;
+    if (GATEUP) {
+      const unsigned char* w1 = reinterpret_cast<const unsigned char*>(grp.w_up);
+      a_ptr[NMAT - 1][0] = w1 + (size_t)(mr + g) * row_bytes + q * 16;
+      a_ptr[NMAT - 1][1] = w1 + (size_t)(mr + g + 8) * row_bytes + q * 16;
+    }
+  }
+
+  float acc[NMAT][NT][4];
+#pragma unroll
+  for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[m][nt][i] = 0.f;
+
+  for (int kc0 = 0; kc0 < K; kc0 += kc) {
+    const int kc_len = min(kc, K - kc0);
+    const int vec_per_row = kc_len / 8;
+    __syncthreads();
+    // Stage this k-chunk of the chunk's token rows (zero rows beyond row_count).
+    for (int idx = threadIdx.x; idx < 8 * NT * vec_per_row; idx += kThreads) {
+      int n = idx / vec_per_row;
+      int c = idx - n * vec_per_row;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (n < rows) {
+        const __nv_bfloat16* src =
+            GATEUP ? bsrc + (size_t)row_token[grp.row_start + n] * ldb
+                   : bsrc + (size_t)(grp.row_start + n) * ldb;
+        v = *reinterpret_cast<const uint4*>(src + kc0 + c * 8);
+      }
+      xs[n * xs_stride + c] = v;
+    }
+    __syncthreads();
+    if (!active) continue;
+
+    const int steps = kc_len / 32;
+    const size_t a_off = (size_t)kc0 * 2;
+    for (int s0 = 0; s0 < steps; s0 += kDepth) {
+      uint4 a[kDepth][NMAT][2];
+#pragma unroll
+      for (int d = 0; d < kDepth; ++d) {
+        if (s0 + d < steps) {
+#pragma unroll
+          for (int m = 0; m < NMAT; ++m) {
+            a[d][m][0] = ldg_stream(a_ptr[m][0] + a_off + (size_t)(s0 + d) * 64);
+            a[d][m][1] = ldg_stream(a_ptr[m][1] + a_off + (size_t)(s0 + d) * 64);
+          }
+        }
+      }
+#pragma unroll
+      for (int d = 0; d < kDepth; ++d) {
+        if (s0 + d < steps) {
+          const int kb_vec = (s0 + d) * 4 + q;  // uint4 index inside the staged row
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            uint4 b = xs[(nt * 8 + g) * xs_stride + kb_vec];
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) {
+              mma_bf16(acc[m][nt], a[d][m][0].x, a[d][m][1].x, a[d][m][0].y, a[d][m][1].y, b.x, b.y);
+              mma_bf16(acc[m][nt], a[d][m][0].z, a[d][m][1].z, a[d][m][0].w, a[d][m][1].w, b.z, b.w);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  if (!active) return;
+  // acc[..][nt][0..3] = (row m0+g, token n0), (m0+g, n0+1), (m0+g+8, n0), (m0+g+8, n0+1)
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int n = nt * 8 + 2 * q + (i & 1);
+      const int m = m0 + g + ((i & 2) ? 8 : 0);
+      if (n < rows) {
+        const size_t r = (size_t)(grp.row_start + n);
+        if (GATEUP) {
+          float h = silu(acc[0][nt][i]) * acc[NMAT - 1][nt][i];
+          hbuf[r * ld_h + m] = __float2bfloat16_rn(h);
+        } else {
+          yexp[r * hidden + m] = acc[0][nt][i];
+        }
+      }
+    }
+  }
+}
+
+int kc_cap_for(int nt, int maxK) {
+  // Keep the staged token rows near 33 KB per CTA so several CTAs share an SM.
+  int cap = (nt == 1) ? 2048 : (nt == 2) ? 1024 : (nt == 4) ? 512 : 256;
+  if (cap > maxK) cap = maxK;
+  return cap;
+}
+
+template <int NT, int NMAT>
+cudaError_t launch_one(const GroupDesc* groups, int n_groups, int tiles, const __nv_bfloat16* bsrc,
+                       int ldb, const int32_t* row_token, int hidden, int maxK,
+                       __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s) {
+  const int cap = kc_cap_for(NT, maxK);
+  const size_t smem = (size_t)8 * NT * (cap + kPadElems) * 2;
+  auto kern = grouped_ffn_kernel<NT, NMAT>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  kern<<<tiles, kThreads, smem, s>>>(groups, n_groups, bsrc, ldb, row_token, hidden, cap, hbuf, ld_h, yexp);
+  return cudaGetLastError();
+}
+
+template <int NMAT>
+cudaError_t dispatch_nt(int max_rows, const GroupDesc* groups, int n_groups, int tiles,
+                        const __nv_bfloat16* bsrc, int ldb, const int32_t* row_token, int hidden,
+                        int maxK, __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s) {
+  if (max_rows <= 8)
+    return launch_one<1, NMAT>(groups, n_groups, tiles, bsrc, ldb, row_token, hidden, maxK, hbuf, ld_h, yexp, s);
+  if (max_rows <= 16)
+    return launch_one<2, NMAT>(groups, n_groups, tiles, bsrc, ldb, row_token, hidden, maxK, hbuf, ld_h, yexp, s);
+  if (max_rows <= 32)
+    return launch_one<4, NMAT>(groups, n_groups, tiles, bsrc, ldb, row_token, hidden, maxK, hbuf, ld_h, yexp, s);
+  return launch_one<8, NMAT>(groups, n_groups, tiles, bsrc, ldb, row_token, hidden, maxK, hbuf, ld_h, yexp, s);
+}
+
+}  // namespace
+
+cudaError_t launch_swiglu_ffn(const GroupDesc* groups_dev, int n_groups, int tiles_gu, int tiles_dn,
+                              int max_rows, int quant4, const __nv_bfloat16* x, int H,
+                              const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h, float* yexp,
+                              cudaStream_t s) {
+  if (n_groups <= 0) return cudaSuccess;
+  if (quant4) return cudaErrorNotSupported;
+  cudaError_t e = dispatch_nt<2>(max_rows, groups_dev, n_groups, tiles_gu, x, H, row_token, H, H, hbuf,
+                                 ld_h, yexp, s);
+  if (e != cudaSuccess) return e;
+  return dispatch_nt<1>(max_rows, groups_dev, n_groups, tiles_dn, hbuf, ld_h, row_token, H, ld_h, hbuf,
+                        ld_h, yexp, s);
+}
+
+}  // namespace pm
