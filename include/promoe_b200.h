@@ -65,6 +65,9 @@ int pm_ctx_set_param_list(pm_ctx* ctx, const char* names);
 int pm_register_expert_param(pm_ctx* ctx, int layer, int expert, int param_id, const void* host_ptr,
                              size_t nbytes);
 int pm_pin_all(pm_ctx* ctx);
+/* Address of one tensor inside the pinned record of an expert (valid after pm_pin_all), for
+ * callers that registered the tensor with host_ptr == NULL and fill the record in place. */
+int pm_expert_host_ptr(pm_ctx* ctx, int layer, int expert, int param_id, void** out, size_t* nbytes);
 /* Number of cache lines each layer gets (length num_layer, or 1 when per_layer_cache is off). */
 int pm_plan_slots(pm_ctx* ctx, int32_t* per_pool_len, int cap, int* n_pools);
 /* Reserves the VMM range and maps one physical allocation per cache line. */

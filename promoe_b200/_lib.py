@@ -59,6 +59,7 @@ SIGNATURES = {
     "pm_ctx_set_param_list": (_i, [_vp, _cp]),
     "pm_register_expert_param": (_i, [_vp, _i, _i, _i, _vp, _sz]),
     "pm_pin_all": (_i, [_vp]),
+    "pm_expert_host_ptr": (_i, [_vp, _i, _i, _i, C.POINTER(_vp), C.POINTER(_sz)]),
     "pm_plan_slots": (_i, [_vp, C.POINTER(C.c_int32), _i, C.POINTER(_i)]),
     "pm_build_slab": (_i, [_vp]),
     "pm_build_policy_only": (_i, [_vp]),
@@ -105,9 +106,7 @@ def load() -> C.CDLL:
             "(there is no CPU or PyTorch fallback for this library)")
     lib = C.CDLL(str(LIB_PATH))
     for name, (res, args) in SIGNATURES.items():
-        fn = getattr(lib, name, None) if __import__("os").environ.get("PM_DEV_LENIENT") else getattr(lib, name)
-        if fn is None:
-            continue
+        fn = getattr(lib, name)  # AttributeError if the header and the build disagree
         fn.restype = res
         fn.argtypes = args
     _lib = lib

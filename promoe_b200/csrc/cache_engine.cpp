@@ -304,7 +304,7 @@ void midpoint_order(const std::vector<int>& arr, std::vector<int>* out) {
 }  // namespace
 
 // ------------------------------------------------------------------------------------------
-CacheEngine::CacheEngine(const Config& cfg) : cfg_(cfg) {
+CacheEngine::CacheEngine(Config& cfg) : cfg_(cfg) {
   experts_.resize((size_t)cfg_.num_layer * cfg_.num_expert);
   layer_q_.resize(cfg_.num_layer);
 }
@@ -392,7 +392,8 @@ void CacheEngine::record(int kind, int layer, int e, int victim_flat) {
 void CacheEngine::hit(int layer, int e, bool precise) {
   const int f = flat(layer, e);
   Pool& p = pool_for(layer);
-  p.policy->on_hit(f, precise);
+  std::string err = p.policy->on_hit(f, precise);
+  if (!err.empty() && deferred_error_.empty()) deferred_error_ = err;
   if (precise) {
     max_priority_ += 1.f;
     p.policy->set_priority(f, max_priority_);
@@ -522,11 +523,19 @@ std::string CacheEngine::drain(std::vector<Action>* out) {
     } else {
       int l = 0;
       while (l < cfg_.num_layer && layer_q_[l].empty()) ++l;
-      if (l == cfg_.num_layer) return "";
+      if (l == cfg_.num_layer) {
+        std::string e = deferred_error_;
+        deferred_error_.clear();
+        return e;
+      }
       t = layer_q_[l].front();
       layer_q_[l].pop_front();
     }
     std::string err = send(t, out);
+    if (err.empty() && !deferred_error_.empty()) {
+      err = deferred_error_;
+      deferred_error_.clear();
+    }
     if (!err.empty()) return err;
   }
 }

@@ -62,7 +62,7 @@ struct Pool {
 
 class CacheEngine {
  public:
-  explicit CacheEngine(const Config& cfg);
+  explicit CacheEngine(Config& cfg);  // keeps a reference: the context owns the configuration
   ~CacheEngine();
 
   // Lines per pool for `total` lines: floor share plus one for the first `total % n` pools in
@@ -117,11 +117,12 @@ class CacheEngine {
   std::string drain(std::vector<Action>* out);
   void record(int kind, int layer, int e, int victim_flat);
 
-  Config cfg_;
+  Config& cfg_;
   std::vector<Pool> pools_;
   std::vector<ExpertState> experts_;
   std::vector<float> priority_;  // "nn" policy only: [L * E]
   float max_priority_ = std::numeric_limits<float>::min();
+  std::string deferred_error_;  // first policy error raised inside hit()
   std::deque<Task> precise_q_;
   std::vector<std::deque<Task>> layer_q_;
   std::unordered_map<uint64_t, std::unordered_map<int, std::vector<int64_t>>> traces_;

@@ -83,7 +83,7 @@ int pm_k_permute(const int32_t* topk_ids, int R, int k, int E, int32_t* counts, 
   if (R < 0 || k <= 0 || E <= 0 || E > 256) return fail(PM_ERR_INVALID, "permute: bad sizes");
   if (!counts || !offsets) return fail(PM_ERR_INVALID, "permute: null pointer");
   if (R > 0 && (!topk_ids || !row_token || !pos)) return fail(PM_ERR_INVALID, "permute: null pointer");
-  PM_CUDA(launch_permute(topk_ids, R, k, E, counts, offsets, row_token, pos, err_flag, (cudaStream_t)stream));
+  PM_CUDA(launch_permute(topk_ids, R, k, E, counts, offsets, row_token, pos, err_flag, 0, 1, (cudaStream_t)stream));
   return PM_OK;
 }
 

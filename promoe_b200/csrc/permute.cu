@@ -19,13 +19,15 @@ constexpr int kMaxExperts = 256;
 __global__ void __launch_bounds__(kPermThreads)
 permute_kernel(const int32_t* __restrict__ topk_ids, int R, int k, int E, int32_t* __restrict__ counts,
                int32_t* __restrict__ offsets, int32_t* __restrict__ row_token,
-               int32_t* __restrict__ pos, int32_t* __restrict__ err_flag) {
+               int32_t* __restrict__ pos, int32_t* __restrict__ err_flag, int tail_rows, int T) {
   __shared__ int cnt[kMaxExperts];
   __shared__ int off[kMaxExperts + 1];
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
   for (int e = tid; e < E; e += kPermThreads) cnt[e] = 0;
+  // Rows after the R routed ones belong to the shared experts: every token once per shared expert.
+  for (int i = tid; i < tail_rows; i += kPermThreads) row_token[R + i] = i % T;
   __syncthreads();
   for (int i = tid; i < R; i += kPermThreads) {
     int e = topk_ids[i];
@@ -71,8 +73,9 @@ permute_kernel(const int32_t* __restrict__ topk_ids, int R, int k, int E, int32_
 
 cudaError_t launch_permute(const int32_t* topk_ids, int R, int k, int E, int32_t* counts,
                            int32_t* offsets, int32_t* row_token, int32_t* pos, int32_t* err_flag,
-                           cudaStream_t s) {
-  permute_kernel<<<1, kPermThreads, 0, s>>>(topk_ids, R, k, E, counts, offsets, row_token, pos, err_flag);
+                           int tail_rows, int T, cudaStream_t s) {
+  permute_kernel<<<1, kPermThreads, 0, s>>>(topk_ids, R, k, E, counts, offsets, row_token, pos, err_flag,
+                                            tail_rows, T > 0 ? T : 1);
   return cudaGetLastError();
 }
 

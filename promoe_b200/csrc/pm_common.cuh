@@ -54,7 +54,7 @@ cudaError_t launch_gate_topk(const __nv_bfloat16* x, const __nv_bfloat16* w_gate
 
 cudaError_t launch_permute(const int32_t* topk_ids, int R, int k, int E, int32_t* counts,
                            int32_t* offsets, int32_t* row_token, int32_t* pos, int32_t* err_flag,
-                           cudaStream_t s);
+                           int tail_rows, int T, cudaStream_t s);
 
 cudaError_t launch_swiglu_ffn(const GroupDesc* groups_dev, int n_groups, int tiles_gu, int tiles_dn,
                               int max_rows, int quant4, const __nv_bfloat16* x, int H,

@@ -1,0 +1,592 @@
+#include "runtime.hpp"
+
+#include <algorithm>
+#include <chrono>
+#include <cstdlib>
+#include <cstring>
+
+namespace pm {
+namespace {
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// CUDA driver (virtual memory management) entry points, resolved through the runtime so the
+// library has no link-time dependency on the driver.
+struct Driver {
+  CUresult (*GetGranularity)(size_t*, const CUmemAllocationProp*, CUmemAllocationGranularity_flags) = nullptr;
+  CUresult (*AddressReserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long) = nullptr;
+  CUresult (*Create)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long) = nullptr;
+  CUresult (*Map)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long) = nullptr;
+  CUresult (*SetAccess)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) = nullptr;
+  CUresult (*Unmap)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*Release)(CUmemGenericAllocationHandle) = nullptr;
+  CUresult (*AddressFree)(CUdeviceptr, size_t) = nullptr;
+  bool ok = false;
+};
+
+Driver& driver() {
+  static Driver d;
+  static bool tried = false;
+  if (tried) return d;
+  tried = true;
+  auto get = [](const char* name, void** fn) {
+    cudaDriverEntryPointQueryResult q;
+    return cudaGetDriverEntryPoint(name, fn, cudaEnableDefault, &q) == cudaSuccess &&
+           q == cudaDriverEntryPointSuccess && *fn != nullptr;
+  };
+  d.ok = get("cuMemGetAllocationGranularity", (void**)&d.GetGranularity) &&
+         get("cuMemAddressReserve", (void**)&d.AddressReserve) && get("cuMemCreate", (void**)&d.Create) &&
+         get("cuMemMap", (void**)&d.Map) && get("cuMemSetAccess", (void**)&d.SetAccess) &&
+         get("cuMemUnmap", (void**)&d.Unmap) && get("cuMemRelease", (void**)&d.Release) &&
+         get("cuMemAddressFree", (void**)&d.AddressFree);
+  return d;
+}
+
+int fail_cu(CUresult r, const char* what) {
+  return fail(PM_ERR_CUDA, std::string(what) + " failed with CUresult " + std::to_string((int)r));
+}
+
+// Waits for an event with a deadline instead of an unbounded block.
+int wait_event(cudaEvent_t ev, double seconds) {
+  auto t0 = std::chrono::steady_clock::now();
+  while (true) {
+    cudaError_t q = cudaEventQuery(ev);
+    if (q == cudaSuccess) return PM_OK;
+    if (q != cudaErrorNotReady) return fail_cuda(q, "cudaEventQuery");
+    if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > seconds)
+      return fail(PM_ERR_TIMEOUT, "device did not reach the routing read-back within the deadline");
+  }
+}
+
+unsigned char* line_ptr(pm_ctx* c, int line) { return c->slab + (size_t)line * c->line_stride; }
+
+cudaEvent_t next_seg_event(pm_ctx* c) {
+  cudaEvent_t e = c->seg_events[c->seg_next];
+  c->seg_next = (c->seg_next + 1) % c->seg_events.size();
+  return e;
+}
+
+int enqueue_copy(pm_ctx* c, const Action& a) {
+  const int E = c->cfg.num_expert;
+  const size_t f = (size_t)a.layer * E + a.expert;
+  const size_t b0 = c->param_offset[a.chunk_begin], b1 = c->param_offset[a.chunk_end];
+  cudaStream_t cs = c->cfg.cache_only ? c->last_stream : c->copy_stream;
+  if (c->line_read[a.line] != nullptr) PM_CUDA(cudaStreamWaitEvent(cs, c->line_read[a.line], 0));
+  PM_CUDA(cudaMemcpyAsync(line_ptr(c, a.line) + b0, c->host_rec[f] + b0, b1 - b0, cudaMemcpyHostToDevice, cs));
+  PM_CUDA(cudaEventRecord(c->line_ready[a.line], cs));
+  c->line_pending[a.line] = 1;
+  c->line_waiter[a.line] = nullptr;
+  c->h2d_bytes += (int64_t)(b1 - b0);
+  c->h2d_copies += 1;
+  return PM_OK;
+}
+
+int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
+  const int E = c->cfg.num_expert;
+  const int max_inter = std::max(w.inter, w.shared_inter);
+  if (T <= c->ws_tokens && w.hidden <= c->ws_hidden && max_inter <= c->ws_inter && w.top_k <= c->ws_topk)
+    return PM_OK;
+  if (c->have_last_stream) PM_CUDA(cudaStreamSynchronize(c->last_stream));
+  if (c->ws_dev) PM_CUDA(cudaFree(c->ws_dev));
+  if (c->h_stage) PM_CUDA(cudaFreeHost(c->h_stage));
+  c->ws_dev = nullptr;
+  c->h_stage = nullptr;
+  const int cap = std::max(T, std::max(16, c->ws_tokens * 2));
+  const int H = std::max(w.hidden, c->ws_hidden), I = std::max(max_inter, c->ws_inter);
+  const int k = std::max(w.top_k, c->ws_topk);
+  const size_t R = (size_t)cap * k, rows = R + cap;  // routed rows + one shared-expert row per token
+  c->desc_cap = (size_t)E + rows / kMaxChunkRows + 8;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    size_t o = off;
+    off += align_up(bytes, 256);
+    return o;
+  };
+  size_t o_ids = take(R * 4), o_slot = take(R * 4), o_w = take(R * 4), o_ss = take((size_t)cap * 4);
+  size_t o_cnt = take((size_t)(2 * E + 1) * 4), o_rt = take(rows * 4), o_pos = take(R * 4), o_err = take(4);
+  size_t o_h = take(rows * I * 2), o_y = take(rows * H * 4), o_desc = take(c->desc_cap * sizeof(GroupDesc));
+  size_t o_sc = take((size_t)c->cfg.num_layer * E * 4), o_ph = take((size_t)cap * 4096 * 4);
+  size_t o_x = take((size_t)cap * H * 2), o_yo = take((size_t)cap * H * 2);
+  PM_CUDA(cudaMalloc(&c->ws_dev, off));
+  PM_CUDA(cudaMemset(c->ws_dev, 0, off));
+  c->ws_bytes = off;
+  unsigned char* b = c->ws_dev;
+  c->d_topk_ids = (int32_t*)(b + o_ids);
+  c->d_topk_slot = (int32_t*)(b + o_slot);
+  c->d_topk_w = (float*)(b + o_w);
+  c->d_shared_scale = (float*)(b + o_ss);
+  c->d_counts = (int32_t*)(b + o_cnt);
+  c->d_offsets = c->d_counts + E;
+  c->d_row_token = (int32_t*)(b + o_rt);
+  c->d_pos = (int32_t*)(b + o_pos);
+  c->d_err = (int32_t*)(b + o_err);
+  c->d_hbuf = (__nv_bfloat16*)(b + o_h);
+  c->d_yexp = (float*)(b + o_y);
+  c->d_desc = (GroupDesc*)(b + o_desc);
+  c->d_scores = (float*)(b + o_sc);
+  c->d_pred_hidden = (float*)(b + o_ph);
+  c->d_xin = (__nv_bfloat16*)(b + o_x);
+  c->d_yout = (__nv_bfloat16*)(b + o_yo);
+  // pinned staging: [counts+offsets | scores | routing ids | routing weights | descriptors]
+  c->h_stage_bytes = align_up((size_t)(2 * E + 1) * 4, 256) + align_up((size_t)c->cfg.num_layer * E * 4, 256) +
+                     2 * align_up(R * 4, 256) + align_up(c->desc_cap * sizeof(GroupDesc), 256) +
+                     align_up((size_t)E * 4, 256);
+  PM_CUDA(cudaHostAlloc((void**)&c->h_stage, c->h_stage_bytes, cudaHostAllocDefault));
+  c->ws_tokens = cap;
+  c->ws_hidden = H;
+  c->ws_inter = I;
+  c->ws_topk = k;
+  return PM_OK;
+}
+
+struct Stage {
+  int32_t* counts;  // [E] then offsets [E+1]
+  float* scores;    // [L, E]
+  int32_t* ids;
+  float* w;
+  GroupDesc* desc;
+  int32_t* slot_table;
+};
+
+Stage stage_of(pm_ctx* c) {
+  const int E = c->cfg.num_expert;
+  const size_t R = (size_t)c->ws_tokens * c->ws_topk;
+  Stage s;
+  unsigned char* p = c->h_stage;
+  s.counts = (int32_t*)p;
+  p += align_up((size_t)(2 * E + 1) * 4, 256);
+  s.scores = (float*)p;
+  p += align_up((size_t)c->cfg.num_layer * E * 4, 256);
+  s.ids = (int32_t*)p;
+  p += align_up(R * 4, 256);
+  s.w = (float*)p;
+  p += align_up(R * 4, 256);
+  s.desc = (GroupDesc*)p;
+  p += align_up(c->desc_cap * sizeof(GroupDesc), 256);
+  s.slot_table = (int32_t*)p;
+  return s;
+}
+
+// Ranks one predicted layer and issues its prefetch (PredictWorker::do_one_task_impl,
+// src/cpp_worker/worker.cpp:6-77).
+int issue_prediction(pm_ctx* c, int dst, const float* scores) {
+  const int E = c->cfg.num_expert;
+  if (c->cfg.cache_policy == "nn") {
+    std::string err = c->eng->update_priority(scores, 1, dst);
+    if (!err.empty()) return fail(PM_ERR_STATE, err);
+  }
+  int n = std::min(c->cfg.num_predict_expert_per_layer, E);
+  if (dst == 0 && c->cfg.limit_layer_0_num_predict != -1) n = std::min(n, c->cfg.limit_layer_0_num_predict);
+  std::vector<int64_t> order(E);
+  for (int i = 0; i < E; ++i) order[i] = i;
+  std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return scores[a] > scores[b]; });
+  std::vector<Action> acts;
+  std::string err = c->eng->prefetch_layer(dst, order.data(), n, &acts);
+  if (!err.empty()) return fail(PM_ERR_STATE, err);
+  rt_mark_dirty(c, acts);
+  return rt_execute_copies(c, acts);
+}
+
+// Launches the predictor MLPs of source index `src` on x [B, H]; returns how many ran.
+int launch_predictors(pm_ctx* c, int src, const __nv_bfloat16* x, int B, int H, cudaStream_t s,
+                      std::vector<int>* dsts) {
+  dsts->clear();
+  if (c->cfg.predict_input_mode != "moe_layer_logits" || c->cfg.num_predict_expert_per_layer <= 0) return PM_OK;
+  const int L = c->cfg.num_layer, E = c->cfg.num_expert;
+  auto map = c->cfg.predict_layer_mapping();
+  if (src < 0 || src > L) return PM_OK;
+  if ((src % L) % c->cfg.layer_predict_interval != 0) return PM_OK;
+  if (c->cfg.cross_token_pred && src == 0) return PM_OK;
+  for (int dst = map[src].first; dst < map[src].second; ++dst) {
+    const pm_ctx::Predictor& p = c->predictors[(size_t)src * L + dst];
+    if (p.w1 == nullptr) continue;
+    if (p.d > 4096) return fail(PM_ERR_UNSUPPORTED, "predictor hidden width above 4096");
+    PM_CUDA(launch_predictor_mlp(x, B, H, (const __nv_bfloat16*)p.w1, p.b1, p.d, (const __nv_bfloat16*)p.w2,
+                                 p.b2, E, c->d_pred_hidden, c->d_scores + (size_t)dst * E, s));
+    c->kernel_launches += 2;
+    dsts->push_back(dst);
+  }
+  return PM_OK;
+}
+
+}  // namespace
+
+void rt_mark_dirty(pm_ctx* c, const std::vector<Action>& actions) {
+  for (const Action& a : actions)
+    if (a.type == Action::kCopy) {
+      if (c->cfg.per_layer_cache) {
+        c->layers[a.layer].slot_table_dirty = true;
+      } else {
+        for (auto& l : c->layers) l.slot_table_dirty = true;  // a shared pool can evict across layers
+      }
+    }
+}
+
+int rt_execute_copies(pm_ctx* c, const std::vector<Action>& actions) {
+  if (!c->slab_built) return PM_OK;
+  for (const Action& a : actions)
+    if (a.type == Action::kCopy) {
+      int rc = enqueue_copy(c, a);
+      if (rc != PM_OK) return rc;
+    }
+  return PM_OK;
+}
+
+int rt_pin_all(pm_ctx* c) {
+  if (c->pinned) return fail(PM_ERR_STATE, "pin_all called twice");
+  const int L = c->cfg.num_layer, E = c->cfg.num_expert, N = c->cfg.num_per_expert_param();
+  if (N <= 0) return fail(PM_ERR_STATE, "pin_all before set_param_list");
+  c->param_offset.assign(N + 1, 0);
+  for (int p = 0; p < N; ++p) {
+    size_t mx = 0;
+    for (size_t f = 0; f < (size_t)L * E; ++f) mx = std::max(mx, c->params[f * N + p].nbytes);
+    c->param_offset[p + 1] = c->param_offset[p] + align_up(mx, 256);
+  }
+  const size_t rec = c->param_offset[N];
+  if (rec == 0) return fail(PM_ERR_STATE, "no expert tensors registered");
+  c->host_rec.assign((size_t)L * E, nullptr);
+  for (int l = 0; l < L; ++l) {
+    void* block = nullptr;
+    PM_CUDA(cudaHostAlloc(&block, rec * E, cudaHostAllocDefault));
+    c->arena_blocks.push_back(block);
+    for (int e = 0; e < E; ++e) {
+      unsigned char* dst = (unsigned char*)block + rec * e;
+      c->host_rec[(size_t)l * E + e] = dst;
+      for (int p = 0; p < N; ++p) {
+        const pm_ctx::Param& pr = c->params[((size_t)l * E + e) * N + p];
+        if (pr.src != nullptr && pr.nbytes > 0) std::memcpy(dst + c->param_offset[p], pr.src, pr.nbytes);
+      }
+    }
+  }
+  c->pinned = true;
+  return PM_OK;
+}
+
+int rt_build_slab(pm_ctx* c) {
+  if (c->slab_built) return fail(PM_ERR_STATE, "slab already built");
+  if (!c->pinned) return fail(PM_ERR_STATE, "build_slab before pin_all");
+  if (!c->eng->built()) {
+    std::string err = c->eng->build();
+    if (!err.empty()) return fail(PM_ERR_STATE, err);
+  }
+  int n_lines = 0;
+  for (const Pool& p : c->eng->pools()) n_lines += p.full_len;
+  if (n_lines <= 0) return fail(PM_ERR_INVALID, "cache_rate gives zero cache lines");
+  const size_t rec = c->param_offset.back();
+  const char* impl = std::getenv("PM_SLAB_IMPL");
+  const bool want_vmm = impl == nullptr || std::string(impl) != "cudamalloc";
+  int dev = 0;
+  PM_CUDA(cudaGetDevice(&dev));
+  PM_CUDA(cudaFree(0));  // make sure the primary context exists before driver calls
+  c->slab_vmm = false;
+  if (want_vmm && driver().ok) {
+    Driver& d = driver();
+    CUmemAllocationProp prop{};
+    prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+    prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    prop.location.id = dev;
+    size_t gran = 0;
+    CUresult r = d.GetGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM);
+    if (r != CUDA_SUCCESS) return fail_cu(r, "cuMemGetAllocationGranularity");
+    c->line_stride = align_up(rec, gran);
+    c->slab_va_bytes = c->line_stride * n_lines;
+    CUdeviceptr base = 0;
+    r = d.AddressReserve(&base, c->slab_va_bytes, gran, 0, 0);
+    if (r != CUDA_SUCCESS) return fail_cu(r, "cuMemAddressReserve");
+    c->slab = (unsigned char*)base;
+    c->line_handles.resize(n_lines);
+    for (int i = 0; i < n_lines; ++i) {
+      r = d.Create(&c->line_handles[i], c->line_stride, &prop, 0);
+      if (r != CUDA_SUCCESS) return fail_cu(r, "cuMemCreate");
+      r = d.Map(base + (size_t)i * c->line_stride, c->line_stride, 0, c->line_handles[i], 0);
+      if (r != CUDA_SUCCESS) return fail_cu(r, "cuMemMap");
+    }
+    CUmemAccessDesc acc{};
+    acc.location = prop.location;
+    acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    r = d.SetAccess(base, c->slab_va_bytes, &acc, 1);
+    if (r != CUDA_SUCCESS) return fail_cu(r, "cuMemSetAccess");
+    c->slab_vmm = true;
+  } else {
+    c->line_stride = align_up(rec, 256);
+    PM_CUDA(cudaMalloc((void**)&c->slab, c->line_stride * n_lines));
+  }
+  c->n_lines = n_lines;
+  // cache_only: copies run on the caller's compute stream (src/cpp_worker/prefetcher.cpp:420-424)
+  if (!c->cfg.cache_only) PM_CUDA(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+  c->line_ready.resize(n_lines);
+  for (auto& e : c->line_ready) PM_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  c->line_read.assign(n_lines, nullptr);
+  c->line_pending.assign(n_lines, 0);
+  c->line_waiter.assign(n_lines, nullptr);
+  c->seg_events.resize(64);
+  for (auto& e : c->seg_events) PM_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  PM_CUDA(cudaEventCreateWithFlags(&c->sync_event, cudaEventDisableTiming));
+  for (auto& l : c->layers) {
+    PM_CUDA(cudaMalloc((void**)&l.slot_table_dev, (size_t)c->cfg.num_expert * 4));
+    PM_CUDA(cudaMemset(l.slot_table_dev, 0xff, (size_t)c->cfg.num_expert * 4));
+    l.slot_table_dirty = true;
+  }
+  c->slab_built = true;
+  return PM_OK;
+}
+
+namespace {
+
+// One grouped FFN launch: the experts in it, and the lines whose copies it has to wait for.
+struct Segment {
+  std::vector<pm_ffn_group> groups;
+  std::vector<int> lines;
+  std::vector<int> waits;
+  bool has_line(int line) const { return std::find(lines.begin(), lines.end(), line) != lines.end(); }
+  bool empty() const { return groups.empty(); }
+};
+
+int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv_bfloat16* x, int n_rows,
+                  size_t* desc_used, cudaStream_t s) {
+  if (seg->empty()) return PM_OK;
+  for (int line : seg->waits) {
+    if (c->line_pending[line] || c->line_waiter[line] != s) {
+      PM_CUDA(cudaStreamWaitEvent(s, c->line_ready[line], 0));
+      c->line_pending[line] = 0;
+      c->line_waiter[line] = s;
+    }
+  }
+  std::vector<GroupDesc> desc;
+  int tg, td, mr, mi;
+  int rc = plan_groups(seg->groups.data(), (int)seg->groups.size(), w.hidden, &desc, &tg, &td, &mr, &mi);
+  if (rc != PM_OK) return rc;
+  if (*desc_used + desc.size() > c->desc_cap) return fail(PM_ERR_STATE, "descriptor buffer overflow");
+  Stage st = stage_of(c);
+  std::memcpy(st.desc + *desc_used, desc.data(), desc.size() * sizeof(GroupDesc));
+  PM_CUDA(cudaMemcpyAsync(c->d_desc + *desc_used, st.desc + *desc_used, desc.size() * sizeof(GroupDesc),
+                          cudaMemcpyHostToDevice, s));
+  PM_CUDA(launch_swiglu_ffn(c->d_desc + *desc_used, (int)desc.size(), tg, td, mr, w.quant4, x, w.hidden,
+                            c->d_row_token, c->d_hbuf, c->ws_inter, c->d_yexp, s));
+  c->kernel_launches += 2;
+  *desc_used += desc.size();
+  if (!seg->lines.empty()) {
+    cudaEvent_t ev = next_seg_event(c);
+    PM_CUDA(cudaEventRecord(ev, s));
+    for (int line : seg->lines) c->line_read[line] = ev;
+  }
+  seg->groups.clear();
+  seg->lines.clear();
+  seg->waits.clear();
+  (void)n_rows;
+  return PM_OK;
+}
+
+}  // namespace
+
+int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream_t s) {
+  if (!c->slab_built) return fail(PM_ERR_STATE, "moe_forward before build_slab");
+  if (layer < 0 || layer >= c->cfg.num_layer) return fail(PM_ERR_INVALID, "layer out of range");
+  pm_ctx::Layer& ly = c->layers[layer];
+  if (!ly.set) return fail(PM_ERR_STATE, "moe_forward before layer_set_weights");
+  if (T < 0) return fail(PM_ERR_INVALID, "negative token count");
+  if (T == 0) return PM_OK;
+  if (!xv || !yv) return fail(PM_ERR_INVALID, "null activation pointer");
+  const pm_layer_weights& w = ly.w;
+  const int E = c->cfg.num_expert, k = w.top_k, H = w.hidden, N = c->cfg.num_per_expert_param();
+  const int R = T * k;
+  const int n_shared = w.shared_inter > 0 ? 1 : 0;
+  int rc = ensure_workspace(c, T, w);
+  if (rc != PM_OK) return rc;
+  if (c->have_last_stream && c->last_stream != s) PM_CUDA(cudaStreamSynchronize(c->last_stream));
+  c->last_stream = s;
+  c->have_last_stream = true;
+  const __nv_bfloat16* x = (const __nv_bfloat16*)xv;
+  Stage st = stage_of(c);
+
+  // Refresh this layer's expert -> slot table if the cache changed since the last upload.
+  if (ly.slot_table_dirty) {
+    for (int e = 0; e < E; ++e) st.slot_table[e] = c->eng->slot_of(layer, e);
+    PM_CUDA(cudaMemcpyAsync(ly.slot_table_dev, st.slot_table, (size_t)E * 4, cudaMemcpyHostToDevice, s));
+    ly.slot_table_dirty = false;
+  }
+  PM_CUDA(launch_gate_topk(x, (const __nv_bfloat16*)w.gate_w, w.gate_bias, (const __nv_bfloat16*)w.shared_gate_w,
+                           T, H, E, k, w.norm_topk, w.routed_scale, ly.slot_table_dev, c->d_topk_ids,
+                           c->d_topk_w, c->d_topk_slot, c->d_shared_scale, nullptr, s));
+  PM_CUDA(launch_permute(c->d_topk_ids, R, k, E, c->d_counts, c->d_offsets, c->d_row_token, c->d_pos, c->d_err,
+                         n_shared * T, T, s));
+  c->kernel_launches += 2;
+  std::vector<int> pred_dsts;
+  if (c->cfg.predict_from_moe_input && c->seq_len == 1) {
+    rc = launch_predictors(c, layer, x, T, H, s, &pred_dsts);
+    if (rc != PM_OK) return rc;
+    if (!pred_dsts.empty())
+      PM_CUDA(cudaMemcpyAsync(st.scores, c->d_scores, (size_t)c->cfg.num_layer * E * 4, cudaMemcpyDeviceToHost, s));
+  }
+  PM_CUDA(cudaMemcpyAsync(st.counts, c->d_counts, (size_t)(2 * E + 1) * 4, cudaMemcpyDeviceToHost, s));
+  if (c->keep_routing) {
+    PM_CUDA(cudaMemcpyAsync(st.ids, c->d_topk_ids, (size_t)R * 4, cudaMemcpyDeviceToHost, s));
+    PM_CUDA(cudaMemcpyAsync(st.w, c->d_topk_w, (size_t)R * 4, cudaMemcpyDeviceToHost, s));
+  }
+  PM_CUDA(cudaEventRecord(c->sync_event, s));
+  rc = wait_event(c->sync_event, 30.0);
+  if (rc != PM_OK) return rc;
+
+  if (c->keep_routing) {
+    c->last_ids[layer].assign(st.ids, st.ids + R);
+    c->last_w[layer].assign(st.w, st.w + R);
+  }
+
+  // Prediction made from this layer's input comes before the layer's own report, as in the
+  // reference (report_moe_layer_logits precedes report_one_layer for the same index).
+  for (int dst : pred_dsts) {
+    rc = issue_prediction(c, dst, st.scores + (size_t)dst * E);
+    if (rc != PM_OK) return rc;
+  }
+
+  const int32_t* counts = st.counts;
+  const int32_t* offsets = st.counts + E;
+  std::vector<int64_t> ids;
+  for (int e = 0; e < E; ++e)
+    if (counts[e] > 0) ids.push_back(e);
+  std::vector<Action> acts;
+  std::string err = c->eng->report_layer(layer, ids.data(), (int64_t)ids.size(), &acts);
+  if (!err.empty()) return fail(PM_ERR_STATE, err);
+  if (!c->cfg.early_preempt) {
+    for (int64_t id : ids) {
+      err = c->eng->report_expert(layer, (int)id, &acts);
+      if (!err.empty()) return fail(PM_ERR_STATE, err);
+    }
+  }
+  rt_mark_dirty(c, acts);
+
+  auto group_of = [&](int e, int line) {
+    const unsigned char* base = line_ptr(c, line);
+    pm_ffn_group g{};
+    g.w_gate = base + c->param_offset[c->role_gate];
+    g.w_up = base + c->param_offset[c->role_up];
+    g.w_down = base + c->param_offset[c->role_down];
+    if (w.quant4) {
+      g.q_gate = base + c->param_offset[c->role_qgate];
+      g.q_up = base + c->param_offset[c->role_qup];
+      g.q_down = base + c->param_offset[c->role_qdown];
+    }
+    g.row_start = offsets[e];
+    g.row_count = counts[e];
+    g.inter = w.inter;
+    return g;
+  };
+
+  Segment seg;
+  size_t desc_used = 0;
+  if (n_shared) {
+    pm_ffn_group g{};
+    g.w_gate = w.shared_w_gate;
+    g.w_up = w.shared_w_up;
+    g.w_down = w.shared_w_down;
+    g.row_start = R;
+    g.row_count = T;
+    g.inter = w.shared_inter;
+    seg.groups.push_back(g);
+  }
+  for (const Action& a : acts) {
+    if (a.type == Action::kCopy) {
+      if (seg.has_line(a.line)) {  // the victim is still waiting to run in the open segment
+        rc = flush_segment(c, &seg, w, x, R + n_shared * T, &desc_used, s);
+        if (rc != PM_OK) return rc;
+      }
+      rc = enqueue_copy(c, a);
+      if (rc != PM_OK) return rc;
+    } else {
+      const bool must_wait = c->line_pending[a.line] || (c->line_waiter[a.line] != nullptr && c->line_waiter[a.line] != s);
+      if (must_wait && seg.waits.empty() && !seg.empty()) {
+        // let everything that is already resident run while the copies are in flight
+        rc = flush_segment(c, &seg, w, x, R + n_shared * T, &desc_used, s);
+        if (rc != PM_OK) return rc;
+      }
+      seg.groups.push_back(group_of(a.expert, a.line));
+      seg.lines.push_back(a.line);
+      if (must_wait) seg.waits.push_back(a.line);
+    }
+  }
+  rc = flush_segment(c, &seg, w, x, R + n_shared * T, &desc_used, s);
+  if (rc != PM_OK) return rc;
+
+  PM_CUDA(launch_combine(c->d_yexp, c->d_pos, c->d_topk_w, T, H, k, R, n_shared,
+                         w.shared_gate_w ? c->d_shared_scale : nullptr, (__nv_bfloat16*)yv, s));
+  c->kernel_launches += 1;
+  for (int64_t id : ids) c->eng->expert_done(layer, (int)id);
+  c->eng->layer_done(layer);
+  (void)N;
+  return PM_OK;
+}
+
+int rt_forward_host(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStream_t s) {
+  if (layer < 0 || layer >= c->cfg.num_layer || !c->layers[layer].set)
+    return fail(PM_ERR_STATE, "moe_forward_host: layer not configured");
+  if (T <= 0) return T == 0 ? PM_OK : fail(PM_ERR_INVALID, "negative token count");
+  if (!x || !y) return fail(PM_ERR_INVALID, "null activation pointer");
+  const pm_layer_weights& w = c->layers[layer].w;
+  int rc = ensure_workspace(c, T, w);
+  if (rc != PM_OK) return rc;
+  const size_t bytes = (size_t)T * w.hidden * 2;
+  PM_CUDA(cudaMemcpyAsync(c->d_xin, x, bytes, cudaMemcpyHostToDevice, s));
+  rc = rt_forward(c, layer, c->d_xin, T, c->d_yout, s);
+  if (rc != PM_OK) return rc;
+  PM_CUDA(cudaMemcpyAsync(y, c->d_yout, bytes, cudaMemcpyDeviceToHost, s));
+  PM_CUDA(cudaStreamSynchronize(s));
+  return PM_OK;
+}
+
+int rt_report_hidden(pm_ctx* c, int index, const void* hidden, int B, int seq, cudaStream_t s) {
+  if (index < 0 || index > c->cfg.num_layer) return fail(PM_ERR_INVALID, "hidden-state index out of range");
+  if (seq != 1 || B <= 0) return PM_OK;  // prefill or empty: nothing is captured (predictor.cpp:657-661)
+  if (!c->slab_built) return fail(PM_ERR_STATE, "report_hidden before build_slab");
+  int H = 0;
+  for (auto& l : c->layers)
+    if (l.set) H = l.w.hidden;
+  if (H == 0) return fail(PM_ERR_STATE, "report_hidden before layer_set_weights");
+  pm_layer_weights shape{};
+  shape.hidden = H;
+  shape.top_k = std::max(1, c->ws_topk);
+  int rc = ensure_workspace(c, B, shape);
+  if (rc != PM_OK) return rc;
+  std::vector<int> dsts;
+  rc = launch_predictors(c, index, (const __nv_bfloat16*)hidden, B, H, s, &dsts);
+  if (rc != PM_OK || dsts.empty()) return rc;
+  Stage st = stage_of(c);
+  const int E = c->cfg.num_expert;
+  PM_CUDA(cudaMemcpyAsync(st.scores, c->d_scores, (size_t)c->cfg.num_layer * E * 4, cudaMemcpyDeviceToHost, s));
+  PM_CUDA(cudaEventRecord(c->sync_event, s));
+  rc = wait_event(c->sync_event, 30.0);
+  if (rc != PM_OK) return rc;
+  for (int dst : dsts) {
+    rc = issue_prediction(c, dst, st.scores + (size_t)dst * E);
+    if (rc != PM_OK) return rc;
+  }
+  return PM_OK;
+}
+
+}  // namespace pm
+
+pm_ctx::~pm_ctx() {
+  // Best effort: the context may die with work in flight only if the caller ignored errors.
+  if (have_last_stream) cudaStreamSynchronize(last_stream);
+  if (copy_stream) {
+    cudaStreamSynchronize(copy_stream);
+    cudaStreamDestroy(copy_stream);
+  }
+  for (auto e : line_ready) cudaEventDestroy(e);
+  for (auto e : seg_events) cudaEventDestroy(e);
+  if (sync_event) cudaEventDestroy(sync_event);
+  for (auto& l : layers)
+    if (l.slot_table_dev) cudaFree(l.slot_table_dev);
+  if (ws_dev) cudaFree(ws_dev);
+  if (h_stage) cudaFreeHost(h_stage);
+  if (slab_built) {
+    if (slab_vmm) {
+      pm::Driver& d = pm::driver();
+      d.Unmap((CUdeviceptr)slab, slab_va_bytes);
+      for (auto h : line_handles) d.Release(h);
+      d.AddressFree((CUdeviceptr)slab, slab_va_bytes);
+    } else {
+      cudaFree(slab);
+    }
+  }
+  for (void* b : arena_blocks) cudaFreeHost(b);
+}

@@ -1,0 +1,110 @@
+// Device side of a context: pinned expert records on the host, the VMM-backed slab of cache
+// lines on the GPU, the side copy stream with its events, and the fused MoE layer forward.
+//
+// The reference keeps experts in pinned torch tensors (src/cpp_worker/model_loader.cpp:23-31,
+// :43-58), carves cache lines out of one cudaMalloc or maps them with the CUDA VMM API
+// (src/cpp_worker/model_loader.cpp:102-164,222-233) and copies on a FetchWorker thread that
+// drains the copy stream after every task (src/cpp_worker/worker.cpp:84-105). Here a copy is
+// one cudaMemcpyAsync of the expert's contiguous record, ordered against the kernels that read
+// or last read the line by events, and the host never waits for a copy.
+#pragma once
+#include <cuda.h>
+
+#include <memory>
+#include <vector>
+
+#include "cache_engine.hpp"
+#include "pm_common.cuh"
+
+struct pm_ctx {
+  pm::Config cfg;
+  std::unique_ptr<pm::CacheEngine> eng;
+  std::string error;  // scratch for building messages
+
+  // ---- expert registry -------------------------------------------------------------
+  struct Param {
+    const void* src = nullptr;
+    size_t nbytes = 0;
+  };
+  std::vector<Param> params;            // [(layer * E + expert) * N + param]
+  std::vector<size_t> param_offset;     // [N + 1] offsets inside a record; [N] = record size
+  std::vector<unsigned char*> host_rec; // [L * E] pinned record of each expert
+  std::vector<void*> arena_blocks;      // one pinned block per layer
+  bool pinned = false;
+  int role_gate = 0, role_up = 1, role_down = 2;        // which tensor plays which part
+  int role_qgate = -1, role_qup = -1, role_qdown = -1;  // uint4 experts: scale/zero tensors
+
+  // ---- slab -------------------------------------------------------------------------
+  bool slab_built = false;
+  bool slab_vmm = false;
+  unsigned char* slab = nullptr;
+  size_t line_stride = 0;
+  int n_lines = 0;
+  std::vector<CUmemGenericAllocationHandle> line_handles;
+  size_t slab_va_bytes = 0;
+
+  // ---- streams and events -------------------------------------------------------------
+  cudaStream_t copy_stream = nullptr;
+  cudaStream_t last_stream = nullptr;
+  bool have_last_stream = false;
+  std::vector<cudaEvent_t> line_ready;    // recorded on the copy stream after a copy into the line
+  std::vector<cudaStream_t> line_waiter;  // compute stream that already waits for line_ready
+  std::vector<char> line_pending;         // a copy was issued that no compute stream waits for yet
+  std::vector<cudaEvent_t> line_read;     // event after the last kernel that read the line (or null)
+  std::vector<cudaEvent_t> seg_events;    // ring of read events
+  size_t seg_next = 0;
+  cudaEvent_t sync_event = nullptr;
+
+  // ---- per-layer model weights ----------------------------------------------------------
+  struct Layer {
+    pm_layer_weights w{};
+    bool set = false;
+    int32_t* slot_table_dev = nullptr;  // [E] slot of each expert, -1 if absent
+    bool slot_table_dirty = true;
+  };
+  std::vector<Layer> layers;
+  struct Predictor {
+    const void* w1 = nullptr;
+    const float* b1 = nullptr;
+    int d = 0;
+    const void* w2 = nullptr;
+    const float* b2 = nullptr;
+  };
+  std::vector<Predictor> predictors;  // [(L + 1) * L], index src * L + dst
+
+  // ---- forward workspace ------------------------------------------------------------------
+  int ws_tokens = 0;  // capacity in tokens
+  int ws_hidden = 0, ws_inter = 0, ws_topk = 0;
+  unsigned char* ws_dev = nullptr;
+  size_t ws_bytes = 0;
+  int32_t *d_topk_ids = nullptr, *d_topk_slot = nullptr, *d_counts = nullptr, *d_offsets = nullptr;
+  int32_t *d_row_token = nullptr, *d_pos = nullptr, *d_err = nullptr;
+  float *d_topk_w = nullptr, *d_shared_scale = nullptr, *d_yexp = nullptr, *d_scores = nullptr;
+  float* d_pred_hidden = nullptr;
+  __nv_bfloat16 *d_hbuf = nullptr, *d_xin = nullptr, *d_yout = nullptr;
+  pm::GroupDesc* d_desc = nullptr;
+  size_t desc_cap = 0;
+  unsigned char* h_stage = nullptr;  // pinned: counts+offsets, scores, descriptors, slot tables, routing
+  size_t h_stage_bytes = 0;
+
+  bool keep_routing = false;
+  int seq_len = 1;
+  std::vector<std::vector<int32_t>> last_ids;  // per layer routing copies (keep_routing)
+  std::vector<std::vector<float>> last_w;
+
+  int64_t h2d_bytes = 0, h2d_copies = 0, kernel_launches = 0;
+
+  ~pm_ctx();
+};
+
+namespace pm {
+
+int rt_pin_all(pm_ctx* c);
+int rt_build_slab(pm_ctx* c);
+int rt_execute_copies(pm_ctx* c, const std::vector<Action>& actions);
+int rt_forward(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStream_t s);
+int rt_forward_host(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStream_t s);
+int rt_report_hidden(pm_ctx* c, int index, const void* hidden, int B, int seq, cudaStream_t s);
+void rt_mark_dirty(pm_ctx* c, const std::vector<Action>& actions);
+
+}  // namespace pm
