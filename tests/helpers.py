@@ -22,3 +22,70 @@ def dev(a: np.ndarray) -> torch.Tensor:
 
 def ptr(t: torch.Tensor | None):
     return None if t is None else t.data_ptr()
+
+
+class TinyModel:
+    """Random MoE stack in the HF 4.x layout (per-expert gate/up/down matrices), values
+    bf16-representable, plus the synthetic AR(1) hidden-state stream of the benchmark."""
+
+    def __init__(self, seed, L, E, H, I, k, shared_I=0, shared_gate=False, norm_topk=False, routed_scale=1.0,
+                 zipf_bias=True, w_std=0.02, gate_std=0.02):
+        rng = np.random.default_rng(seed)
+        self.L, self.E, self.H, self.I, self.k = L, E, H, I, k
+        self.shared_I, self.norm_topk, self.routed_scale = shared_I, norm_topk, routed_scale
+        self.gate_w = [bf16_weights(rng, (E, H), gate_std) for _ in range(L)]
+        self.gate_bias = None
+        if zipf_bias:
+            self.gate_bias = []
+            for _ in range(L):
+                p = 1.0 / (rng.permutation(E) + 1.0) ** 1.1
+                self.gate_bias.append((0.5 * np.log(p / p.sum())).astype(np.float32))
+        self.experts = [[(bf16_weights(rng, (I, H), w_std), bf16_weights(rng, (I, H), w_std),
+                          bf16_weights(rng, (H, I), w_std)) for _ in range(E)] for _ in range(L)]
+        self.shared = None
+        if shared_I:
+            self.shared = [(bf16_weights(rng, (shared_I, H), w_std), bf16_weights(rng, (shared_I, H), w_std),
+                            bf16_weights(rng, (H, shared_I), w_std)) for _ in range(L)]
+        self.shared_gate_w = [bf16_weights(rng, (H,), w_std) for _ in range(L)] if shared_gate else None
+        self.rng = rng
+
+    def hidden_stream(self, batch, steps):
+        """h_0 ~ N(0,1), h_t = 0.8 h_{t-1} + 0.6 N(0,1), rounded to bf16."""
+        h = self.rng.standard_normal((batch, self.H))
+        out = []
+        for _ in range(steps):
+            out.append(om.bf16_round(h.astype(np.float32)))
+            h = 0.8 * h + 0.6 * self.rng.standard_normal((batch, self.H))
+        return out
+
+    def oracle_forward(self, layer, x, report_experts=None):
+        return om.moe_block_forward(
+            x, self.gate_w[layer], self.experts[layer], self.k, self.norm_topk, self.routed_scale,
+            gate_bias=None if self.gate_bias is None else self.gate_bias[layer],
+            shared=None if self.shared is None else self.shared[layer],
+            shared_gate_w=None if self.shared_gate_w is None else self.shared_gate_w[layer],
+            report_experts=report_experts, round_h_bf16=True)
+
+    def canonical_routing(self, layer, x):
+        lg = om.gate_logits_canonical(x, self.gate_w[layer], None if self.gate_bias is None else self.gate_bias[layer])
+        return om.route(lg, self.k, self.norm_topk, self.routed_scale)
+
+    def make_cache(self, **config):
+        """An ExpertCache holding this model: experts in pinned host records, the rest on the GPU."""
+        from promoe_b200.engine import ExpertCache
+        cfg = dict(num_expert_per_token=self.k)
+        cfg.update(config)
+        cache = ExpertCache(self.L, self.E, **cfg)
+        cache.set_param_list(["gate_proj.weight", "up_proj.weight", "down_proj.weight"])
+        for l in range(self.L):
+            for e in range(self.E):
+                cache.register_expert(l, e, [om.to_bf16_bits(w) for w in self.experts[l][e]])
+        cache.pin_all()
+        cache.build_slab()
+        for l in range(self.L):
+            cache.set_layer_weights(
+                l, dev_bf16(self.gate_w[l]), self.I, self.k, self.norm_topk, self.routed_scale,
+                gate_bias=None if self.gate_bias is None else dev(self.gate_bias[l]),
+                shared=None if self.shared is None else [dev_bf16(w) for w in self.shared[l]],
+                shared_gate_w=None if self.shared_gate_w is None else dev_bf16(self.shared_gate_w[l]))
+        return cache
