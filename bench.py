@@ -1,0 +1,307 @@
+"""Benchmark of the MoE hot path: decode tokens/s of an MoE stack at cache_rate 0.375.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config c2]
+
+One "step" is one decode step of the whole stack: every layer's fused MoE forward (route,
+permute, cache bookkeeping, host-to-device copies of missed experts, grouped SwiGLU FFN by
+cache slot, combine) over one batch of synthetic hidden states. Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "moe_decode_tokens_per_s_cache_rate_0.375"
+UNIT = "tokens/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="c2")
+    ap.add_argument("--num-predict", type=int, default=None, help="experts prefetched per predicted layer (0 = off)")
+    ap.add_argument("--cpu-sample-layers", type=int, default=2)
+    ap.add_argument("--cpu-sample-steps", type=int, default=12)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            f = [v.strip() for v in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peak_gbs():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+# --------------------------------------------------------------------------- CPU baseline
+def cpu_baseline(cfg, sample_layers, sample_steps, threads, stack=None):
+    """Times the oracle's float32 torch block (the code shape the reference executes) on host cores."""
+    import torch
+    from oracle import cpu_baseline as cb
+    from promoe_b200 import synth
+    blocks = []
+    n = min(sample_layers, cfg.num_layer)
+    for l in range(n):
+        experts = []
+        for e in range(cfg.num_expert):
+            if stack is not None:
+                experts.append(stack.host_expert(l, e))
+            else:
+                experts.append([synth._randn(s, synth.seed_for(cfg.name, l, e, nm), "cpu", dtype=torch.float32)
+                                for nm, s in (("gate", (cfg.inter, cfg.hidden)), ("up", (cfg.inter, cfg.hidden)),
+                                              ("down", (cfg.hidden, cfg.inter)))])
+        bias = torch.from_numpy(synth.zipf_gate_bias(cfg.num_expert, synth.seed_for(cfg.name, l, "bias")))
+        if stack is not None:  # the very tensors the GPU arm uses
+            gate_w = stack.gate_w[l].float().cpu()
+            shared = [w.float().cpu() for w in stack.shared[l]] if cfg.shared_inter else None
+            sgw = stack.shared_gate_w[l].float().cpu() if cfg.shared_gate else None
+            blocks.append(cb.SparseMoeBlock(gate_w, bias, experts, cfg.top_k, cfg.norm_topk, shared, sgw))
+            continue
+        gate_w = synth._randn((cfg.num_expert, cfg.hidden), synth.seed_for(cfg.name, l, "router"), "cpu", dtype=torch.float32)
+        shared = None
+        if cfg.shared_inter:
+            shared = [synth._randn(s, synth.seed_for(cfg.name, l, nm), "cpu", dtype=torch.float32)
+                      for nm, s in (("shared_gate_proj", (cfg.shared_inter, cfg.hidden)),
+                                    ("shared_up_proj", (cfg.shared_inter, cfg.hidden)),
+                                    ("shared_down_proj", (cfg.hidden, cfg.shared_inter)))]
+        sgw = synth._randn((cfg.hidden,), synth.seed_for(cfg.name, l, "shared_expert_gate"), "cpu", dtype=torch.float32) \
+            if cfg.shared_gate else None
+        blocks.append(cb.SparseMoeBlock(gate_w, bias, experts, cfg.top_k, cfg.norm_topk, shared, sgw))
+    xs = synth.hidden_stream(cfg, sample_steps, cfg.batch, "cpu").float()
+    res = cb.time_stack_sample(blocks, xs, cfg.num_layer, cfg.cache_rate, cfg.top_k, cfg.num_expert, threads)
+    res["sample"] = (f"first {n} of {cfg.num_layer} layers x {sample_steps} decode steps of batch {cfg.batch} "
+                     f"(1 warm-up step untimed), tokens/s scaled to the whole stack")
+    return res
+
+
+def run_reference(args, cfg):
+    """The reference arm: its CPU code path on all host cores, rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    threads = os.cpu_count() or 1
+    steps = max(2, min(args.steps + args.warmup, 64))
+    res = cpu_baseline(cfg, args.cpu_sample_layers, steps, threads)
+    ms = res["seconds_per_layer_step"] * cfg.num_layer * 1e3
+    line = {
+        "impl": "reference", "metric": METRIC, "value": res["tokens_per_s"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(cfg, args.gpus, predictor=False),
+        "cpu_baseline": {"value": res["tokens_per_s"], "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": res["sample"], "torch": torch.__version__, "hit_rate": res["hit_rate"]},
+        "e2e": {"value": res["tokens_per_s"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(cfg, n_gpus, predictor, num_predict=0):
+    return {"workload": f"{cfg.name}: {cfg.num_layer} MoE layers, hidden {cfg.hidden}, {cfg.num_expert} experts, "
+                        f"top-{cfg.top_k}, expert inter {cfg.inter}, shared inter {cfg.shared_inter}, "
+                        f"batch {cfg.batch} per GPU, cache_rate {cfg.cache_rate}, LRU",
+            "batch_per_gpu": cfg.batch, "n_gpus": n_gpus, "cache_rate": cfg.cache_rate,
+            "predictor": (f"mlp {cfg.hidden}-{cfg.predictor_width}-{cfg.num_expert} relu, random init, "
+                          f"{num_predict} experts per predicted layer") if predictor else "off",
+            "l2": "weights read per step exceed L2 (no flush needed)",
+            "parallelism": "single GPU" if n_gpus == 1 else f"independent replicas x{n_gpus}"}
+
+
+# --------------------------------------------------------------------------- our arm
+def run_ours(args, cfg):
+    import torch
+    import torch.distributed as dist
+    from promoe_b200 import synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the MoE path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = torch.device("cuda", local_rank)
+
+    num_predict = args.num_predict
+    if num_predict is None:
+        num_predict = cfg.top_k if cfg.predictor_width else 0
+    use_pred = num_predict > 0 and cfg.predictor_width > 0
+    stack = synth.SyntheticStack(cfg, dev, num_predict_expert_per_layer=num_predict,
+                                 predict_from_moe_input=use_pred)
+    stack.install_layers()
+    if use_pred:
+        stack.install_predictors()
+    cache = stack.cache
+    L, B, H = cfg.num_layer, cfg.batch, cfg.hidden
+    K, W = args.steps, args.warmup
+    xs = synth.hidden_stream(cfg, W + 2 * K + 4, B, dev, seed_tag=f"hidden{rank}")
+    y = torch.empty((B, H), dtype=torch.bfloat16, device=dev)
+
+    def step_device(t):
+        for l in range(L):
+            cache.forward(l, xs[t], out=y)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for t in range(W):
+        step_device(t)
+    barrier()
+    cache.set("profile_ffn", 1)
+    cache.profile(reset=True)
+    s0 = cache.stats()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for t in range(W, W + K):
+        step_device(t)
+    ev1.record()
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    clocks = sampler.stop()
+    prof = cache.profile(reset=True)
+    cache.set("profile_ffn", 0)
+    s1 = cache.stats()
+
+    # end to end: host buffers in, host buffers out, through the same public call
+    xh = xs[W + K: W + 2 * K].cpu().pin_memory()
+    yh = torch.empty((B, H), dtype=torch.bfloat16).pin_memory()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for t in range(K):
+        for l in range(L):
+            cache.forward_host(l, xh[t], out=yh)
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+
+    if world > 1:
+        tt = torch.tensor([ms_total, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms_total, ms_e2e = tt.tolist()
+    tokens = B * K * world
+    value = tokens / (ms_total / 1e3)
+    e2e = tokens / (ms_e2e / 1e3)
+
+    peak, peak_src = measured_peak_gbs()
+    gu_gbs = prof["gateup_bytes"] / (prof["gateup_ms"] / 1e3) / 1e9 if prof["gateup_ms"] > 0 else 0.0
+    dn_gbs = prof["down_bytes"] / (prof["down_ms"] / 1e3) / 1e9 if prof["down_ms"] > 0 else 0.0
+    hits, misses = s1["precise_hit"] - s0["precise_hit"], s1["precise_miss"] - s0["precise_miss"]
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(cfg, world, use_pred, num_predict),
+        "clocks": clocks,
+        "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": L * B * H * 2, "d2h_bytes_per_step": L * B * H * 2,
+                "ms_per_step": ms_e2e / K},
+        "gpu_launches": s1["kernel_launches"] - s0["kernel_launches"],
+        "roofline": {"bound": "hbm", "kernel": "grouped_ffn_kernel gate/up (SwiGLU) launch",
+                     "achieved": gu_gbs, "peak": peak, "unit": "GB/s", "frac": gu_gbs / peak, "peak_source": peak_src,
+                     "traffic": None, "launches": prof["ffn_launches"],
+                     "avg_launch_us": prof["gateup_ms"] * 1e3 / max(1, prof["ffn_launches"]),
+                     "bytes_per_launch": prof["gateup_bytes"] / max(1, prof["ffn_launches"]),
+                     "down_kernel": {"achieved": dn_gbs, "frac": dn_gbs / peak,
+                                     "avg_launch_us": prof["down_ms"] * 1e3 / max(1, prof["ffn_launches"])},
+                     "frac_of_8tbs_nominal": gu_gbs / 8000.0},
+        "cache": {"hit_rate": hits / max(1, hits + misses), "precise_hit": hits, "precise_miss": misses,
+                  "prefetch_miss": s1["prefetch_miss"] - s0["prefetch_miss"],
+                  "h2d_gb_per_step": (s1["h2d_bytes"] - s0["h2d_bytes"]) / K / 1e9,
+                  "h2d_gbs_effective": (s1["h2d_bytes"] - s0["h2d_bytes"]) / (ms_total / 1e3) / 1e9,
+                  "slab_impl": cache.get("slab_impl")},
+    }
+    if rank == 0 and not args.no_cpu_baseline and world == 1:
+        threads = min(8, os.cpu_count() or 1)  # the reference pins torch to 8 threads (utils/__init__.py:343)
+        res = cpu_baseline(cfg, args.cpu_sample_layers, args.cpu_sample_steps, threads, stack=stack)
+        line["cpu_baseline"] = {"value": res["tokens_per_s"], "unit": UNIT, "cores": threads, "kind": "port",
+                                "sample": res["sample"], "host_cores": os.cpu_count(), "torch": torch.__version__,
+                                "hit_rate": res["hit_rate"], "cpu_seconds": res["cpu_seconds"]}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    cache.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    from promoe_b200 import synth
+    cfg = synth.CONFIGS[args.config]
+    if args.impl == "reference":
+        run_reference(args, cfg)
+    else:
+        run_ours(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

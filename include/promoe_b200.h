@@ -129,6 +129,15 @@ typedef struct pm_stats {
 } pm_stats;
 int pm_stats_read(pm_ctx* ctx, pm_stats* out);
 
+/* Device time and weight bytes of the grouped FFN launches made while the context option
+ * profile_ffn=1 was set (CUDA events on the caller's stream around each launch). */
+typedef struct pm_profile {
+  int64_t ffn_launches;  /* gate/up + down launch pairs */
+  double gateup_ms, down_ms;
+  int64_t gateup_bytes, down_bytes; /* weight bytes those launches had to read once */
+} pm_profile;
+int pm_profile_read(pm_ctx* ctx, pm_profile* out, int reset);
+
 /* ---- fused MoE layer ---------------------------------------------------- */
 typedef struct pm_layer_weights {
   const void* gate_w;        /* device bf16 [num_expert, hidden] */

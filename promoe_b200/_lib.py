@@ -30,6 +30,11 @@ class pm_stats(C.Structure):
         "activated_experts", "layer_calls", "h2d_bytes", "h2d_copies", "kernel_launches")]
 
 
+class pm_profile(C.Structure):
+    _fields_ = [("ffn_launches", C.c_int64), ("gateup_ms", C.c_double), ("down_ms", C.c_double),
+                ("gateup_bytes", C.c_int64), ("down_bytes", C.c_int64)]
+
+
 class pm_layer_weights(C.Structure):
     _fields_ = [("gate_w", C.c_void_p), ("gate_bias", C.c_void_p), ("shared_gate_w", C.c_void_p),
                 ("shared_w_gate", C.c_void_p), ("shared_w_up", C.c_void_p), ("shared_w_down", C.c_void_p),
@@ -77,6 +82,7 @@ SIGNATURES = {
     "pm_event_log_read": (_i, [_vp, C.POINTER(pm_event), _sz, C.POINTER(_sz)]),
     "pm_event_log_clear": (_i, [_vp]),
     "pm_stats_read": (_i, [_vp, C.POINTER(pm_stats)]),
+    "pm_profile_read": (_i, [_vp, C.POINTER(pm_profile), _i]),
     "pm_layer_set_weights": (_i, [_vp, _i, C.POINTER(pm_layer_weights)]),
     "pm_moe_forward": (_i, [_vp, _i, _vp, _i, _vp, _vp]),
     "pm_moe_forward_host": (_i, [_vp, _i, _vp, _i, _vp, _vp]),

@@ -97,6 +97,10 @@ int pm_ctx_set(pm_ctx* ctx, const char* key, const char* value) {
     ctx->seq_len = std::atoi(value);
     return PM_OK;
   }
+  if (k == "profile_ffn") {
+    ctx->profile_ffn = (v == "1" || v == "true" || v == "True" || v == "on");
+    return PM_OK;
+  }
   return from(ctx->cfg.set(k, v), PM_ERR_INVALID);
 }
 
@@ -286,6 +290,24 @@ int pm_stats_read(pm_ctx* ctx, pm_stats* out) {
   out->h2d_bytes = ctx->h2d_bytes;
   out->h2d_copies = ctx->h2d_copies;
   out->kernel_launches = ctx->kernel_launches;
+  return PM_OK;
+}
+
+int pm_profile_read(pm_ctx* ctx, pm_profile* out, int reset) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  if (!out) return fail(PM_ERR_INVALID, "null output pointer");
+  int rc = rt_profile_collect(ctx);
+  if (rc != PM_OK) return rc;
+  out->ffn_launches = ctx->ffn_launches;
+  out->gateup_ms = ctx->ffn_ms_gu;
+  out->down_ms = ctx->ffn_ms_dn;
+  out->gateup_bytes = ctx->ffn_bytes_gu;
+  out->down_bytes = ctx->ffn_bytes_dn;
+  if (reset) {
+    ctx->ffn_launches = 0;
+    ctx->ffn_ms_gu = ctx->ffn_ms_dn = 0;
+    ctx->ffn_bytes_gu = ctx->ffn_bytes_dn = 0;
+  }
   return PM_OK;
 }
 

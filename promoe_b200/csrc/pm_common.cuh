@@ -56,10 +56,11 @@ cudaError_t launch_permute(const int32_t* topk_ids, int R, int k, int E, int32_t
                            int32_t* offsets, int32_t* row_token, int32_t* pos, int32_t* err_flag,
                            int tail_rows, int T, cudaStream_t s);
 
+// mid_event (optional) is recorded between the gate/up and the down launch.
 cudaError_t launch_swiglu_ffn(const GroupDesc* groups_dev, int n_groups, int tiles_gu, int tiles_dn,
                               int max_rows, int quant4, const __nv_bfloat16* x, int H,
                               const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h, float* yexp,
-                              cudaStream_t s);
+                              cudaStream_t s, cudaEvent_t mid_event = nullptr);
 
 cudaError_t launch_combine(const float* yexp, const int32_t* pos, const float* topk_w, int T, int H,
                            int k, int R, int n_shared, const float* shared_scale,

@@ -232,6 +232,26 @@ int rt_execute_copies(pm_ctx* c, const std::vector<Action>& actions) {
   return PM_OK;
 }
 
+// Turns the recorded FFN event triples into accumulated milliseconds. Waits for the last one.
+int rt_profile_collect(pm_ctx* c) {
+  for (pm_ctx::FfnSample& f : c->ffn_samples) {
+    PM_CUDA(cudaEventSynchronize(f.e2));
+    float a = 0.f, b = 0.f;
+    PM_CUDA(cudaEventElapsedTime(&a, f.e0, f.e1));
+    PM_CUDA(cudaEventElapsedTime(&b, f.e1, f.e2));
+    c->ffn_ms_gu += a;
+    c->ffn_ms_dn += b;
+    c->ffn_bytes_gu += f.bytes_gu;
+    c->ffn_bytes_dn += f.bytes_dn;
+    c->ffn_launches += 1;
+    c->ffn_event_pool.push_back(f.e0);
+    c->ffn_event_pool.push_back(f.e1);
+    c->ffn_event_pool.push_back(f.e2);
+  }
+  c->ffn_samples.clear();
+  return PM_OK;
+}
+
 int rt_pin_all(pm_ctx* c) {
   if (c->pinned) return fail(PM_ERR_STATE, "pin_all called twice");
   const int L = c->cfg.num_layer, E = c->cfg.num_expert, N = c->cfg.num_per_expert_param();
@@ -361,8 +381,37 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
   std::memcpy(st.desc + *desc_used, desc.data(), desc.size() * sizeof(GroupDesc));
   PM_CUDA(cudaMemcpyAsync(c->d_desc + *desc_used, st.desc + *desc_used, desc.size() * sizeof(GroupDesc),
                           cudaMemcpyHostToDevice, s));
+  pm_ctx::FfnSample sample{};
+  if (c->profile_ffn) {
+    auto take_event = [&](cudaEvent_t* e) -> cudaError_t {
+      if (!c->ffn_event_pool.empty()) {
+        *e = c->ffn_event_pool.back();
+        c->ffn_event_pool.pop_back();
+        return cudaSuccess;
+      }
+      return cudaEventCreate(e);
+    };
+    PM_CUDA(take_event(&sample.e0));
+    PM_CUDA(take_event(&sample.e1));
+    PM_CUDA(take_event(&sample.e2));
+    const int64_t elem = w.quant4 ? 1 : 4;  // bytes of one gate+up weight pair / two uint4 pairs
+    for (const pm_ffn_group& g : seg->groups) {
+      int64_t mat = (int64_t)g.inter * w.hidden;
+      // uint4: half a byte per weight plus one fp16 {scale, zero} pair per 128 weights
+      int64_t one = w.quant4 ? mat / 2 + mat / 128 * 4 : mat * 2;
+      sample.bytes_gu += 2 * one;
+      sample.bytes_dn += one;
+    }
+    (void)elem;
+    PM_CUDA(cudaEventRecord(sample.e0, s));
+  }
   PM_CUDA(launch_swiglu_ffn(c->d_desc + *desc_used, (int)desc.size(), tg, td, mr, w.quant4, x, w.hidden,
-                            c->d_row_token, c->d_hbuf, c->ws_inter, c->d_yexp, s));
+                            c->d_row_token, c->d_hbuf, c->ws_inter, c->d_yexp, s,
+                            c->profile_ffn ? sample.e1 : nullptr));
+  if (c->profile_ffn) {
+    PM_CUDA(cudaEventRecord(sample.e2, s));
+    c->ffn_samples.push_back(sample);
+  }
   c->kernel_launches += 2;
   *desc_used += desc.size();
   if (!seg->lines.empty()) {
@@ -574,6 +623,12 @@ pm_ctx::~pm_ctx() {
   for (auto e : line_ready) cudaEventDestroy(e);
   for (auto e : seg_events) cudaEventDestroy(e);
   if (sync_event) cudaEventDestroy(sync_event);
+  for (auto& f : ffn_samples) {
+    cudaEventDestroy(f.e0);
+    cudaEventDestroy(f.e1);
+    cudaEventDestroy(f.e2);
+  }
+  for (auto e : ffn_event_pool) cudaEventDestroy(e);
   for (auto& l : layers)
     if (l.slot_table_dev) cudaFree(l.slot_table_dev);
   if (ws_dev) cudaFree(ws_dev);

@@ -94,6 +94,17 @@ struct pm_ctx {
 
   int64_t h2d_bytes = 0, h2d_copies = 0, kernel_launches = 0;
 
+  // ---- optional timing of the grouped FFN launches (for the roofline figure) ------------------
+  struct FfnSample {
+    cudaEvent_t e0, e1, e2;  // before gate/up, between, after down
+    int64_t bytes_gu, bytes_dn;
+  };
+  bool profile_ffn = false;
+  std::vector<FfnSample> ffn_samples;      // recorded, not yet read
+  std::vector<cudaEvent_t> ffn_event_pool; // free events
+  double ffn_ms_gu = 0, ffn_ms_dn = 0;
+  int64_t ffn_bytes_gu = 0, ffn_bytes_dn = 0, ffn_launches = 0;
+
   ~pm_ctx();
 };
 
@@ -106,5 +117,6 @@ int rt_forward(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStream_t
 int rt_forward_host(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStream_t s);
 int rt_report_hidden(pm_ctx* c, int index, const void* hidden, int B, int seq, cudaStream_t s);
 void rt_mark_dirty(pm_ctx* c, const std::vector<Action>& actions);
+int rt_profile_collect(pm_ctx* c);
 
 }  // namespace pm

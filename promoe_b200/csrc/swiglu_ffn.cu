@@ -220,13 +220,17 @@ cudaError_t dispatch_nt(int max_rows, const GroupDesc* groups, int n_groups, int
 cudaError_t launch_swiglu_ffn(const GroupDesc* groups_dev, int n_groups, int tiles_gu, int tiles_dn,
                               int max_rows, int quant4, const __nv_bfloat16* x, int H,
                               const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h, float* yexp,
-                              cudaStream_t s) {
+                              cudaStream_t s, cudaEvent_t mid_event) {
   if (n_groups <= 0) return cudaSuccess;
   if (quant4) return cudaErrorNotSupported;
   cudaError_t e = dispatch_nt<2>(max_rows, groups_dev, n_groups, tiles_gu, x, H, row_token, H, H, hbuf,
                                  ld_h, yexp, s);
   if (e != cudaSuccess) return e;
-  return dispatch_nt<1>(max_rows, groups_dev, n_groups, tiles_dn, hbuf, ld_h, row_token, H, ld_h, hbuf,
+  if (mid_event != nullptr) {
+    e = cudaEventRecord(mid_event, s);
+    if (e != cudaSuccess) return e;
+  }
+  return dispatch_nt<1>(max_rows, groups_dev, n_groups, tiles_dn, hbuf, ld_h, row_token, H, ld_h, nullptr,
                         ld_h, yexp, s);
 }
 

@@ -167,6 +167,12 @@ class ExpertCache:
         _lib.call("pm_stats_read", self._ctx, C.byref(s))
         return {name: getattr(s, name) for name, _ in s._fields_}
 
+    def profile(self, reset: bool = False) -> dict:
+        """Accumulated device time / weight bytes of the grouped FFN launches (profile_ffn=1)."""
+        p = _lib.pm_profile()
+        _lib.call("pm_profile_read", self._ctx, C.byref(p), int(reset))
+        return {name: getattr(p, name) for name, _ in p._fields_}
+
     # ------------------------------------------------------------------ fused layer
     def set_layer_weights(self, layer: int, gate_w: torch.Tensor, inter: int, top_k: int, norm_topk: bool,
                           routed_scale: float = 1.0, gate_bias: torch.Tensor | None = None,
