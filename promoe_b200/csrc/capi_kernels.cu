@@ -26,6 +26,12 @@ int plan_groups(const pm_ffn_group* groups, int n_groups, int hidden, std::vecto
   out->clear();
   int tg = 0, td = 0, mr = 0, mi = 0;
   if (hidden % 64 != 0) return fail(PM_ERR_INVALID, "hidden must be a multiple of 64");
+  // The kernel variant, and with it the tile size, follows from the largest chunk of the launch.
+  int largest = 0;
+  for (int i = 0; i < n_groups; ++i) largest = std::max(largest, std::min(groups[i].row_count, kMaxChunkRows));
+  const bool split = largest <= kSplitMaxRows;
+  const int tile_gu = split ? kSplitTileGu : kTileRows;
+  const int tile_dn = split ? kSplitTileDn : kTileRows;
   for (int i = 0; i < n_groups; ++i) {
     const pm_ffn_group& g = groups[i];
     if (g.row_count <= 0) continue;
@@ -39,8 +45,8 @@ int plan_groups(const pm_ffn_group* groups, int n_groups, int hidden, std::vecto
       d.inter = g.inter;
       d.tile_start_gu = tg;
       d.tile_start_dn = td;
-      tg += (g.inter + kTileRows - 1) / kTileRows;
-      td += hidden / kTileRows;
+      tg += (g.inter + tile_gu - 1) / tile_gu;
+      td += hidden / tile_dn;
       mr = std::max(mr, d.row_count);
       mi = std::max(mi, g.inter);
       out->push_back(d);

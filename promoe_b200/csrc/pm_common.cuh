@@ -42,8 +42,11 @@ struct GroupDesc {
   int32_t pad;
 };
 
-constexpr int kTileRows = 64;       // weight rows per CTA tile (4 warps x 16)
+constexpr int kTileRows = 64;       // weight rows per CTA tile of the staged kernel (4 warps x 16)
 constexpr int kMaxChunkRows = 64;   // token rows per chunk (8 MMA n-tiles)
+constexpr int kSplitMaxRows = 16;   // launches whose chunks all fit use the split-K decode kernel,
+constexpr int kSplitTileGu = 16;    // whose tiles are 16 gate+up rows
+constexpr int kSplitTileDn = 32;    // or 32 down rows
 
 // Kernel launchers (defined in the .cu files). All take the caller's stream.
 cudaError_t launch_gate_topk(const __nv_bfloat16* x, const __nv_bfloat16* w_gate, const float* bias,

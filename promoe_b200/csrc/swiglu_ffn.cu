@@ -180,6 +180,150 @@ grouped_ffn_kernel(const GroupDesc* __restrict__ groups, int n_groups,
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Decode variant for chunks of at most 16 token rows (the common case: a handful of tokens per
+// expert). A CTA owns one m-tile (16 gate rows + the same 16 up rows, or 32 down rows) and its
+// 8 warps split the reduction dimension, so every warp issues its whole share of weight loads
+// in one or two batches and a tile lives for a couple of DRAM round trips. Token rows are
+// read straight from global memory (they are tiny and stay in L1/L2) into MMA B fragments,
+// so there is no shared-memory staging and no barrier before the final cross-warp reduction.
+// ---------------------------------------------------------------------------------------------
+constexpr int kSplitWarps = 8;
+constexpr int kSplitThreads = kSplitWarps * 32;
+
+template <int NT, int NMAT, int DEPTH>
+__global__ void __launch_bounds__(kSplitThreads, 2)
+grouped_ffn_splitk_kernel(const GroupDesc* __restrict__ groups, int n_groups,
+                          const __nv_bfloat16* __restrict__ bsrc, int ldb,
+                          const int32_t* __restrict__ row_token, int hidden,
+                          __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp) {
+  constexpr bool GATEUP = (NMAT == 2);
+  constexpr int kVals = 2 * NT * 4;  // accumulator values per lane
+  __shared__ float red[kSplitWarps][kVals][32];
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int g = lane >> 2;
+  const int q = lane & 3;
+
+  const int gi = find_group<GATEUP>(groups, n_groups, blockIdx.x);
+  const GroupDesc grp = groups[gi];
+  const int tile_local = blockIdx.x - (GATEUP ? grp.tile_start_gu : grp.tile_start_dn);
+  const int K = GATEUP ? hidden : grp.inter;
+  const int rows = grp.row_count;
+  const int m0 = tile_local * (GATEUP ? 16 : 32);
+  const size_t row_bytes = (size_t)K * 2;
+
+  // Four weight-row streams per lane: gate rows g / g+8 and up rows g / g+8, or down rows
+  // g, g+8, g+16, g+24 of the tile.
+  const unsigned char* a_ptr[4];
+  if (GATEUP) {
+    const unsigned char* w0 = reinterpret_cast<const unsigned char*>(grp.w_gate);
+    const unsigned char* w1 = reinterpret_cast<const unsigned char*>(grp.w_up);
+    a_ptr[0] = w0 + (size_t)(m0 + g) * row_bytes + q * 16;
+    a_ptr[1] = w0 + (size_t)(m0 + g + 8) * row_bytes + q * 16;
+    a_ptr[2] = w1 + (size_t)(m0 + g) * row_bytes + q * 16;
+    a_ptr[3] = w1 + (size_t)(m0 + g + 8) * row_bytes + q * 16;
+  } else {
+    const unsigned char* w0 = reinterpret_cast<const unsigned char*>(grp.w_down);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) a_ptr[j] = w0 + (size_t)(m0 + g + 8 * j) * row_bytes + q * 16;
+  }
+  const unsigned char* b_ptr[NT];
+  bool b_ok[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int n = nt * 8 + g;
+    b_ok[nt] = n < rows;
+    const int src_row = b_ok[nt] ? (GATEUP ? row_token[grp.row_start + n] : grp.row_start + n) : 0;
+    b_ptr[nt] = reinterpret_cast<const unsigned char*>(bsrc + (size_t)src_row * ldb) + q * 16;
+  }
+
+  float acc[2][NT][4];
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[m][nt][i] = 0.f;
+
+  const int steps = K / 32;
+  const int s_begin = (warp * steps) / kSplitWarps;
+  const int s_end = ((warp + 1) * steps) / kSplitWarps;
+  for (int s0 = s_begin; s0 < s_end; s0 += DEPTH) {
+    uint4 a[DEPTH][4];
+    uint4 b[DEPTH][NT];
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      if (s0 + d < s_end) {
+        const size_t off = (size_t)(s0 + d) * 64;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a[d][j] = ldg_stream(a_ptr[j] + off);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+          b[d][nt] = b_ok[nt] ? __ldg(reinterpret_cast<const uint4*>(b_ptr[nt] + off)) : make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      if (s0 + d < s_end) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+          for (int m = 0; m < 2; ++m) {
+            const uint4& lo = a[d][2 * m];
+            const uint4& hi = a[d][2 * m + 1];
+            mma_bf16(acc[m][nt], lo.x, hi.x, lo.y, hi.y, b[d][nt].x, b[d][nt].y);
+            mma_bf16(acc[m][nt], lo.z, hi.z, lo.w, hi.w, b[d][nt].z, b[d][nt].w);
+          }
+        }
+      }
+    }
+  }
+
+  // Cross-warp reduction of the split-K partial sums, then the epilogue.
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) red[warp][(m * NT + nt) * 4 + i][lane] = acc[m][nt][i];
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < NT * 4 * 32; idx += kSplitThreads) {
+    const int l = idx & 31;
+    const int v = idx >> 5;  // nt * 4 + i
+    const int nt = v >> 2, i = v & 3;
+    float s0v = 0.f, s1v = 0.f;
+#pragma unroll
+    for (int w = 0; w < kSplitWarps; ++w) {
+      s0v += red[w][v][l];
+      s1v += red[w][NT * 4 + v][l];
+    }
+    const int lg = l >> 2, lq = l & 3;
+    const int n = nt * 8 + 2 * lq + (i & 1);
+    if (n >= rows) continue;
+    const int m = m0 + lg + ((i & 2) ? 8 : 0);
+    const size_t r = (size_t)(grp.row_start + n);
+    if (GATEUP) {
+      hbuf[r * ld_h + m] = __float2bfloat16_rn(silu(s0v) * s1v);
+    } else {
+      yexp[r * hidden + m] = s0v;
+      yexp[r * hidden + m + 16] = s1v;
+    }
+  }
+}
+
+template <int NT, int NMAT>
+cudaError_t launch_splitk(const GroupDesc* groups, int n_groups, int tiles, const __nv_bfloat16* bsrc, int ldb,
+                          const int32_t* row_token, int hidden, __nv_bfloat16* hbuf, int ld_h, float* yexp,
+                          cudaStream_t s) {
+  constexpr int kDepthSplit = (NT == 1) ? 4 : 2;
+  grouped_ffn_splitk_kernel<NT, NMAT, kDepthSplit><<<tiles, kSplitThreads, 0, s>>>(
+      groups, n_groups, bsrc, ldb, row_token, hidden, hbuf, ld_h, yexp);
+  return cudaGetLastError();
+}
+
 int kc_cap_for(int nt, int maxK) {
   // Keep the staged token rows near 33 KB per CTA so several CTAs share an SM.
   int cap = (nt == 1) ? 2048 : (nt == 2) ? 1024 : (nt == 4) ? 512 : 256;
@@ -223,13 +367,23 @@ cudaError_t launch_swiglu_ffn(const GroupDesc* groups_dev, int n_groups, int til
                               cudaStream_t s, cudaEvent_t mid_event) {
   if (n_groups <= 0) return cudaSuccess;
   if (quant4) return cudaErrorNotSupported;
-  cudaError_t e = dispatch_nt<2>(max_rows, groups_dev, n_groups, tiles_gu, x, H, row_token, H, H, hbuf,
-                                 ld_h, yexp, s);
+  cudaError_t e;
+  if (max_rows <= 8) {
+    e = launch_splitk<1, 2>(groups_dev, n_groups, tiles_gu, x, H, row_token, H, hbuf, ld_h, yexp, s);
+  } else if (max_rows <= kSplitMaxRows) {
+    e = launch_splitk<2, 2>(groups_dev, n_groups, tiles_gu, x, H, row_token, H, hbuf, ld_h, yexp, s);
+  } else {
+    e = dispatch_nt<2>(max_rows, groups_dev, n_groups, tiles_gu, x, H, row_token, H, H, hbuf, ld_h, yexp, s);
+  }
   if (e != cudaSuccess) return e;
   if (mid_event != nullptr) {
     e = cudaEventRecord(mid_event, s);
     if (e != cudaSuccess) return e;
   }
+  if (max_rows <= 8)
+    return launch_splitk<1, 1>(groups_dev, n_groups, tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s);
+  if (max_rows <= kSplitMaxRows)
+    return launch_splitk<2, 1>(groups_dev, n_groups, tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s);
   return dispatch_nt<1>(max_rows, groups_dev, n_groups, tiles_dn, hbuf, ld_h, row_token, H, ld_h, nullptr,
                         ld_h, yexp, s);
 }

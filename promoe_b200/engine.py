@@ -43,6 +43,7 @@ class ExpertCache:
         self._keep: list = []          # device tensors whose addresses the context holds
         self._hidden = 0
         self._n_params = 0
+        self.pinned = False
 
     # ------------------------------------------------------------------ lifecycle
     def close(self):
@@ -89,6 +90,7 @@ class ExpertCache:
 
     def pin_all(self) -> None:
         _lib.call("pm_pin_all", self._ctx)
+        self.pinned = True
         self._keep = [k for k in self._keep if isinstance(k, torch.Tensor) and k.is_cuda]
 
     def host_record(self, layer: int, expert: int, param: int) -> tuple[int, int]:
