@@ -228,6 +228,8 @@ class ModelLoader:
         t = param.detach()
         if t.device.type != "cpu":
             t = t.cpu()
+        if t.is_floating_point() and t.dtype != torch.bfloat16 and t.dim() == 2:
+            t = t.to(torch.bfloat16)  # the device kernels compute on bf16 weight matrices
         self._dtype[pid] = t.dtype
         _register_one(self.metas.cache, layer_id, expert_id, pid, t)
 
@@ -429,6 +431,8 @@ class PrefetchMngr:
         pass  # only the moe_layer_logits input mode has a device predictor
 
     def report_moe_layer_logits(self, layer_id: int, layer_logits: torch.Tensor):
+        if self._cache.get("predict_input_mode") != "moe_layer_logits":
+            return  # the other input modes ignore hidden states (predictor.cpp:641-648)
         if layer_logits.dim() != 3:
             raise ValueError(f"input logits must be [batch, seq_len, hidden], found {tuple(layer_logits.shape)}")
         if layer_logits.shape[1] != 1 or not layer_logits.is_cuda:

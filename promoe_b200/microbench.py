@@ -1,0 +1,69 @@
+"""Times the grouped SwiGLU FFN kernels alone (pm_k_swiglu_ffn): G experts with distinct weights,
+`rows` token rows each, so that one launch pair streams G * 3 * inter * hidden * 2 bytes.
+
+    python -m promoe_b200.microbench --groups 60 --rows 4 [--hidden 2048 --inter 1408 --iters 20]
+
+Prints one line with the mean time of a launch pair (CUDA events on the launching stream, after
+warm-up) and the achieved weight bandwidth. Weights above 126 MB do not fit in L2, so repeated
+launches read them from HBM every time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import _lib
+
+
+def run(groups: int, rows: int, hidden: int, inter: int, iters: int, warmup: int = 3) -> dict:
+    _lib.load()
+    dev = torch.device("cuda")
+    weights = [(torch.randn(3 * inter * hidden, device=dev) * 0.02).to(torch.bfloat16) for _ in range(groups)]
+    tokens = 64
+    x = torch.randn((tokens, hidden), device=dev).to(torch.bfloat16)
+    arr = (_lib.pm_ffn_group * groups)()
+    for i, w in enumerate(weights):
+        p = w.data_ptr()
+        arr[i] = _lib.pm_ffn_group(p, p + inter * hidden * 2, p + 2 * inter * hidden * 2, None, None, None,
+                                   i * rows, rows, inter, 0)
+    n_rows = groups * rows
+    row_token = torch.randint(0, tokens, (n_rows,), dtype=torch.int32, device=dev)
+    nbytes = _lib.call("pm_k_swiglu_ffn_scratch_bytes", groups, n_rows, inter)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    yexp = torch.empty((n_rows, hidden), dtype=torch.float32, device=dev)
+
+    def once():
+        _lib.call("pm_k_swiglu_ffn", arr, groups, 0, x.data_ptr(), hidden, row_token.data_ptr(), n_rows,
+                  yexp.data_ptr(), scratch.data_ptr(), nbytes, None)
+
+    for _ in range(warmup):
+        once()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        once()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    weight_bytes = groups * 3 * inter * hidden * 2
+    return {"groups": groups, "rows": rows, "hidden": hidden, "inter": inter, "us_per_launch_pair": ms * 1e3,
+            "weight_mb": weight_bytes / 1e6, "gb_per_s": weight_bytes / ms / 1e6}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--groups", type=int, default=60)
+    ap.add_argument("--rows", type=int, default=4)
+    ap.add_argument("--hidden", type=int, default=2048)
+    ap.add_argument("--inter", type=int, default=1408)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args()
+    print(json.dumps(run(a.groups, a.rows, a.hidden, a.inter, a.iters, a.warmup)))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,176 @@
+"""The drop-in Python API: inject_model on an HF 4.x style MoE model replaces the block forward by
+the fused path and keeps outputs and cache decisions equal to the oracles; the hook-only path
+(fused=False) replays a routing trace through stand-in modules like the reference's simulate demo."""
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+from torch import nn
+
+from oracle import moe_math as om
+from oracle import srs_policy as sp
+
+pytestmark = pytest.mark.gpu
+
+
+@dataclass
+class Cfg:
+    _name_or_path: str
+    num_experts_per_tok: int = 4
+    norm_topk_prob: bool = False
+
+
+class MLP(nn.Module):
+    def __init__(self, H, I):
+        super().__init__()
+        self.gate_proj, self.up_proj, self.down_proj = nn.Linear(H, I, bias=False), nn.Linear(H, I, bias=False), nn.Linear(I, H, bias=False)
+
+    def forward(self, x):
+        return self.down_proj(nn.functional.silu(self.gate_proj(x)) * self.up_proj(x))
+
+
+class QwenStyleMoeBlock(nn.Module):
+    def __init__(self, cfg, H, E, I, I_sh):
+        super().__init__()
+        self.top_k, self.norm_topk_prob = cfg.num_experts_per_tok, cfg.norm_topk_prob
+        self.gate = nn.Linear(H, E, bias=False)
+        self.experts = nn.ModuleList([MLP(H, I) for _ in range(E)])
+        self.shared_expert = MLP(H, I_sh)
+        self.shared_expert_gate = nn.Linear(H, 1, bias=False)
+
+    def report_experts(self, experts):
+        return experts
+
+    def forward(self, hidden_states):
+        shape = hidden_states.shape
+        x = hidden_states.reshape(-1, shape[-1])
+        w, ids = torch.topk(torch.softmax(self.gate(x).float(), -1), self.top_k, -1)
+        y = torch.zeros_like(x)
+        for e in self.report_experts(torch.unique(ids).cpu()).tolist():
+            tok, slot = torch.where(ids == e)
+            y.index_add_(0, tok, self.experts[e](x[tok]) * w[tok, slot, None].to(x.dtype))
+        y = y + torch.sigmoid(self.shared_expert_gate(x)) * self.shared_expert(x)
+        return y.view(shape)
+
+
+class Layer(nn.Module):
+    def __init__(self, cfg, H, E, I, I_sh):
+        super().__init__()
+        self.mlp = QwenStyleMoeBlock(cfg, H, E, I, I_sh)
+
+    def forward(self, hidden_states):
+        return (hidden_states + self.mlp(hidden_states),)
+
+
+class TinyQwen(nn.Module):
+    def __init__(self, L=3, H=128, E=12, I=64, I_sh=128):
+        super().__init__()
+        self.config = Cfg("Qwen/Qwen1.5-MoE-A2.7B-Chat")
+        self.model = nn.Module()
+        self.model.layers = nn.ModuleList([Layer(self.config, H, E, I, I_sh) for _ in range(L)])
+
+    def forward(self, h):
+        for layer in self.model.layers:
+            h = layer(h)[0]
+        return h
+
+
+def test_inject_model_fused_matches_unfused(lib):
+    from promoe_b200.utils import inject_model
+    torch.manual_seed(0)
+    L, H, E, I, k = 3, 128, 12, 64, 4
+    model = TinyQwen(L, H, E, I).eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            p.copy_((p * (3.0 if p.shape[0] == E and p.dim() == 2 and p.shape[1] == H else 1.0)).to(torch.bfloat16).float())
+    xs = [torch.randn(5, 1, H).to(torch.bfloat16).float() for _ in range(4)]
+    with torch.no_grad():
+        ref = [model(x) for x in xs]          # float32 python-loop forward before injection
+    routed = []                               # expert lists per (step, layer) from the unfused run
+    for l, layer in enumerate(model.model.layers):
+        layer.mlp.report_experts = (lambda ll: lambda ids: routed.append((ll, ids.tolist())) or ids)(l)
+    with torch.no_grad():
+        for x in xs:
+            model(x)
+    mngr = inject_model(model, num_moe_layer=L, num_expert_per_layer=E, num_expert_per_token=k, cache_rate=0.5,
+                        num_predict_expert_per_layer=0, enable_model_timer=True)
+    cache = mngr.metas.cache
+    cache.enable_event_log(True)
+    model.model.layers[0].mlp.gate  # structure is intact
+    for name, p in model.named_parameters():
+        if ".experts." in name:
+            assert p.numel() == 0, "expert parameters are released to placeholders"
+    model.to("cuda")
+    with torch.no_grad():
+        for x, r in zip(xs, ref):
+            y = model(x.to("cuda", torch.bfloat16))
+            torch.cuda.synchronize()
+            got = y.float().cpu().numpy()
+            np.testing.assert_allclose(got, r.numpy(), rtol=3e-2, atol=3e-2 * np.abs(r.numpy()).max())
+    oc = sp.SequentialCache(L, E, k, cache_rate=0.5, num_predict=0)
+    for l, ids in routed:
+        oc.report_layer(l, ids)
+    assert cache.events() == oc.events
+    assert mngr.profiler.series[0], "the model timer recorded forwards"
+    assert mngr.launched
+
+
+class SimExpert(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.fc = nn.Linear(0, 0, bias=False)
+
+    def forward(self, x):
+        return x
+
+
+class SimLayer(nn.Module):
+    def __init__(self, E):
+        super().__init__()
+        self.experts = nn.ModuleList([SimExpert() for _ in range(E)])
+
+    def report_experts(self, experts):
+        return experts
+
+    def forward(self, expert_ids):
+        for e in self.report_experts(expert_ids).tolist():
+            self.experts[e](e)
+        return (expert_ids,)
+
+
+class SimModel(nn.Module):
+    def __init__(self, L, E):
+        super().__init__()
+        self.config = Cfg("deepseek-ai/deepseek-moe-16b-chat-simulate")
+        self.layers = nn.ModuleList([SimLayer(E) for _ in range(L)])
+
+    def forward(self, per_layer_ids):
+        for ids, layer in zip(per_layer_ids, self.layers):
+            layer(torch.as_tensor(ids, dtype=torch.int64))
+
+
+def test_hook_path_replays_a_trace_like_the_simulate_demo(lib):
+    """eval/demo-simulate pattern: zero-sized experts, the routing trace is the input, every cache
+    decision goes through report_experts and the per-expert hooks (fused=False)."""
+    from promoe_b200.utils import inject_model
+    from promoe_b200.utils.filter import RegexFilter
+    from tests.policy_driver import make_stream
+    L, E, k = 27, 64, 6
+    model = SimModel(L, E)
+    mngr = inject_model(model, cache_rate=0.375, num_predict_expert_per_layer=0, fused=False,
+                        predict_input_mode="no_predict",
+                        moe_mlp_name_filter=RegexFilter(r".*layers\.(\d+)$"), enable_model_timer=False)
+    cache = mngr.metas.cache
+    cache.enable_event_log(True)
+    stream = make_stream(3, L, E, k, steps=5, batch=1, prefill_first=True)
+    oc = sp.SequentialCache(L, E, k, cache_rate=0.375, num_predict=0, num_per_expert_param=1)
+    step = []
+    for kind, layer, ids in stream:
+        step.append(ids)
+        oc.report_layer(layer, ids)
+        if layer == L - 1:
+            model(step)
+            step = []
+    assert cache.events() == oc.events
+    assert cache.plan_slots() == oc.lens
