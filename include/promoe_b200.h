@@ -200,8 +200,9 @@ typedef struct pm_ffn_group {
   int32_t inter;
   int32_t pad;
 } pm_ffn_group;
-/* Bytes of device scratch pm_k_swiglu_ffn needs for n_rows rows in n_groups groups. */
-size_t pm_k_swiglu_ffn_scratch_bytes(int n_groups, int n_rows, int max_inter);
+/* Bytes of device scratch pm_k_swiglu_ffn needs for n_rows rows in n_groups groups (launch plan:
+ * group descriptors and per-tile tables, plus the bf16 intermediate rows). */
+size_t pm_k_swiglu_ffn_scratch_bytes(int n_groups, int n_rows, int max_inter, int hidden);
 /* Grouped SwiGLU FFN: yexp[r, :] = down(silu(gate(x[row_token[r]])) * up(x[row_token[r]])) for
  * every row r of every group. groups is a HOST array; scratch is device memory of at least
  * pm_k_swiglu_ffn_scratch_bytes(). yexp is f32 [n_rows, hidden]. */

@@ -91,7 +91,7 @@ SIGNATURES = {
     "pm_report_hidden": (_i, [_vp, _i, _vp, _i, _i, _vp]),
     "pm_k_gate_topk": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "pm_k_permute": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
-    "pm_k_swiglu_ffn_scratch_bytes": (_sz, [_i, _i, _i]),
+    "pm_k_swiglu_ffn_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "pm_k_swiglu_ffn": (_i, [C.POINTER(pm_ffn_group), _i, _i, _vp, _i, _vp, _i, _vp, _vp, _sz, _vp]),
     "pm_k_combine": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
     "pm_k_predictor_mlp": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp]),

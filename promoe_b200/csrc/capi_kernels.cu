@@ -19,12 +19,9 @@ int fail_cuda(cudaError_t e, const char* what) {
   return PM_ERR_CUDA;
 }
 
-// Splits the caller's groups into chunks of at most kMaxChunkRows rows, assigns CTA tile
-// ranges and returns the descriptors (host) plus launch geometry.
-int plan_groups(const pm_ffn_group* groups, int n_groups, int hidden, std::vector<GroupDesc>* out,
-                int* tiles_gu, int* tiles_dn, int* max_rows, int* max_inter) {
-  out->clear();
-  int tg = 0, td = 0, mr = 0, mi = 0;
+// One planner for both passes: with blob == nullptr it only sizes the launch.
+static int plan_core(const pm_ffn_group* groups, int n_groups, int hidden, unsigned char* blob, size_t cap,
+                     FfnPlanInfo* info) {
   if (hidden % 64 != 0) return fail(PM_ERR_INVALID, "hidden must be a multiple of 64");
   // The kernel variant, and with it the tile size, follows from the largest chunk of the launch.
   int largest = 0;
@@ -32,28 +29,52 @@ int plan_groups(const pm_ffn_group* groups, int n_groups, int hidden, std::vecto
   const bool split = largest <= kSplitMaxRows;
   const int tile_gu = split ? kSplitTileGu : kTileRows;
   const int tile_dn = split ? kSplitTileDn : kTileRows;
+  FfnPlanInfo sized;
+  if (blob != nullptr) {
+    sized = *info;  // result of the size pass
+    if (sized.blob_bytes() > cap) return fail(PM_ERR_INVALID, "launch plan does not fit its buffer");
+  }
+  GroupDesc* desc = reinterpret_cast<GroupDesc*>(blob);
+  int32_t* t_gu = blob ? reinterpret_cast<int32_t*>(blob + sized.off_tile_gu()) : nullptr;
+  int32_t* t_dn = blob ? reinterpret_cast<int32_t*>(blob + sized.off_tile_dn()) : nullptr;
+  int n = 0, tg = 0, td = 0, mr = 0, mi = 0;
   for (int i = 0; i < n_groups; ++i) {
     const pm_ffn_group& g = groups[i];
     if (g.row_count <= 0) continue;
     if (g.inter % 32 != 0 || g.inter <= 0) return fail(PM_ERR_INVALID, "inter must be a positive multiple of 32");
     for (int r0 = 0; r0 < g.row_count; r0 += kMaxChunkRows) {
-      GroupDesc d{};
-      d.w_gate = g.w_gate; d.w_up = g.w_up; d.w_down = g.w_down;
-      d.q_gate = g.q_gate; d.q_up = g.q_up; d.q_down = g.q_down;
-      d.row_start = g.row_start + r0;
-      d.row_count = std::min(kMaxChunkRows, g.row_count - r0);
-      d.inter = g.inter;
-      d.tile_start_gu = tg;
-      d.tile_start_dn = td;
-      tg += (g.inter + tile_gu - 1) / tile_gu;
-      td += hidden / tile_dn;
-      mr = std::max(mr, d.row_count);
+      const int n_gu = (g.inter + tile_gu - 1) / tile_gu, n_dn = hidden / tile_dn;
+      if (blob != nullptr) {
+        GroupDesc d{};
+        d.w_gate = g.w_gate; d.w_up = g.w_up; d.w_down = g.w_down;
+        d.q_gate = g.q_gate; d.q_up = g.q_up; d.q_down = g.q_down;
+        d.row_start = g.row_start + r0;
+        d.row_count = std::min(kMaxChunkRows, g.row_count - r0);
+        d.inter = g.inter;
+        d.tile_start_gu = tg;
+        d.tile_start_dn = td;
+        desc[n] = d;
+        for (int t = 0; t < n_gu; ++t) t_gu[tg + t] = n;
+        for (int t = 0; t < n_dn; ++t) t_dn[td + t] = n;
+      }
+      tg += n_gu;
+      td += n_dn;
+      mr = std::max(mr, std::min(kMaxChunkRows, g.row_count - r0));
       mi = std::max(mi, g.inter);
-      out->push_back(d);
+      ++n;
     }
   }
-  *tiles_gu = tg; *tiles_dn = td; *max_rows = mr; *max_inter = mi;
+  info->n_desc = n; info->tiles_gu = tg; info->tiles_dn = td; info->max_rows = mr; info->max_inter = mi;
   return PM_OK;
+}
+
+int plan_groups_size(const pm_ffn_group* groups, int n_groups, int hidden, FfnPlanInfo* info) {
+  return plan_core(groups, n_groups, hidden, nullptr, 0, info);
+}
+
+int plan_groups_into(const pm_ffn_group* groups, int n_groups, int hidden, unsigned char* blob, size_t cap,
+                     FfnPlanInfo* info) {
+  return plan_core(groups, n_groups, hidden, blob, cap, info);
 }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -93,11 +114,14 @@ int pm_k_permute(const int32_t* topk_ids, int R, int k, int E, int32_t* counts, 
   return PM_OK;
 }
 
-size_t pm_k_swiglu_ffn_scratch_bytes(int n_groups, int n_rows, int max_inter) {
-  if (n_groups < 0 || n_rows < 0 || max_inter < 0) return 0;
-  // descriptors (groups may split into chunks of kMaxChunkRows rows) + intermediate h rows
-  size_t n_desc = (size_t)n_groups + (size_t)n_rows / kMaxChunkRows + 1;
-  return align_up(n_desc * sizeof(GroupDesc), 256) + align_up((size_t)n_rows * max_inter * 2, 256);
+size_t pm_k_swiglu_ffn_scratch_bytes(int n_groups, int n_rows, int max_inter, int hidden) {
+  if (n_groups < 0 || n_rows < 0 || max_inter < 0 || hidden < 0) return 0;
+  // worst case: every group split into chunks of kMaxChunkRows rows, smallest tiles
+  FfnPlanInfo worst;
+  worst.n_desc = n_groups + n_rows / kMaxChunkRows + 1;
+  worst.tiles_gu = worst.n_desc * ((max_inter + kSplitTileGu - 1) / kSplitTileGu);
+  worst.tiles_dn = worst.n_desc * ((hidden + kSplitTileDn - 1) / kSplitTileDn);
+  return align_up(worst.blob_bytes(), 256) + align_up((size_t)n_rows * max_inter * 2, 256);
 }
 
 int pm_k_swiglu_ffn(const pm_ffn_group* groups, int n_groups, int quant4, const void* x, int hidden,
@@ -106,23 +130,25 @@ int pm_k_swiglu_ffn(const pm_ffn_group* groups, int n_groups, int quant4, const 
   if (n_groups < 0 || n_rows < 0) return fail(PM_ERR_INVALID, "swiglu_ffn: negative size");
   if (n_groups == 0 || n_rows == 0) return PM_OK;
   if (!groups || !x || !row_token || !yexp || !scratch) return fail(PM_ERR_INVALID, "swiglu_ffn: null pointer");
-  std::vector<GroupDesc> desc;
-  int tg, td, mr, mi;
-  int rc = plan_groups(groups, n_groups, hidden, &desc, &tg, &td, &mr, &mi);
-  if (rc != PM_OK) return rc;
-  if (desc.empty()) return PM_OK;
-  for (const GroupDesc& d : desc)
-    if (d.row_start < 0 || d.row_start + d.row_count > n_rows)
+  for (int i = 0; i < n_groups; ++i)
+    if (groups[i].row_count > 0 && (groups[i].row_start < 0 || groups[i].row_start + groups[i].row_count > n_rows))
       return fail(PM_ERR_INVALID, "swiglu_ffn: group rows outside [0, n_rows)");
-  const size_t desc_bytes = align_up(desc.size() * sizeof(GroupDesc), 256);
-  const size_t need = desc_bytes + align_up((size_t)n_rows * mi * 2, 256);
+  FfnPlanInfo info;
+  int rc = plan_groups_size(groups, n_groups, hidden, &info);
+  if (rc != PM_OK) return rc;
+  if (info.n_desc == 0) return PM_OK;
+  const size_t plan_bytes = align_up(info.blob_bytes(), 256);
+  const size_t need = plan_bytes + align_up((size_t)n_rows * info.max_inter * 2, 256);
   if (scratch_bytes < need) return fail(PM_ERR_INVALID, "swiglu_ffn: scratch too small");
+  std::vector<unsigned char> blob(info.blob_bytes());
+  rc = plan_groups_into(groups, n_groups, hidden, blob.data(), blob.size(), &info);
+  if (rc != PM_OK) return rc;
   cudaStream_t s = (cudaStream_t)stream;
-  // The descriptor upload is from pageable memory, so it is staged before this call returns.
-  PM_CUDA(cudaMemcpyAsync(scratch, desc.data(), desc.size() * sizeof(GroupDesc), cudaMemcpyHostToDevice, s));
-  __nv_bfloat16* hbuf = (__nv_bfloat16*)((unsigned char*)scratch + desc_bytes);
-  PM_CUDA(launch_swiglu_ffn((const GroupDesc*)scratch, (int)desc.size(), tg, td, mr, quant4,
-                            (const __nv_bfloat16*)x, hidden, row_token, hbuf, mi, yexp, s));
+  // The plan upload is from pageable memory, so it is staged before this call returns.
+  PM_CUDA(cudaMemcpyAsync(scratch, blob.data(), blob.size(), cudaMemcpyHostToDevice, s));
+  __nv_bfloat16* hbuf = (__nv_bfloat16*)((unsigned char*)scratch + plan_bytes);
+  PM_CUDA(launch_swiglu_ffn((const unsigned char*)scratch, info, quant4, (const __nv_bfloat16*)x, hidden,
+                            row_token, hbuf, info.max_inter, yexp, s));
   return PM_OK;
 }
 

@@ -59,19 +59,32 @@ cudaError_t launch_permute(const int32_t* topk_ids, int R, int k, int E, int32_t
                            int32_t* offsets, int32_t* row_token, int32_t* pos, int32_t* err_flag,
                            int tail_rows, int T, cudaStream_t s);
 
+// Geometry of one grouped FFN launch pair. The device blob it describes holds, 16-byte aligned
+// and in this order: n_desc GroupDesc, tiles_gu int32 (chunk index of every gate/up CTA tile),
+// tiles_dn int32 (same for the down launch).
+struct FfnPlanInfo {
+  int n_desc = 0, tiles_gu = 0, tiles_dn = 0, max_rows = 0, max_inter = 0;
+  size_t off_tile_gu() const { return ((size_t)n_desc * sizeof(GroupDesc) + 15) / 16 * 16; }
+  size_t off_tile_dn() const { return off_tile_gu() + ((size_t)tiles_gu * 4 + 15) / 16 * 16; }
+  size_t blob_bytes() const { return off_tile_dn() + ((size_t)tiles_dn * 4 + 15) / 16 * 16; }
+};
+
+// Splits caller groups into chunks of at most kMaxChunkRows rows, assigns CTA tile ranges and
+// writes the blob into `blob` (host memory, `cap` bytes). Allocates nothing.
+int plan_groups_into(const pm_ffn_group* groups, int n_groups, int hidden, unsigned char* blob, size_t cap,
+                     FfnPlanInfo* info);
+// Size pass of the same planner (blob == nullptr): fills `info` only.
+int plan_groups_size(const pm_ffn_group* groups, int n_groups, int hidden, FfnPlanInfo* info);
+
 // mid_event (optional) is recorded between the gate/up and the down launch.
-cudaError_t launch_swiglu_ffn(const GroupDesc* groups_dev, int n_groups, int tiles_gu, int tiles_dn,
-                              int max_rows, int quant4, const __nv_bfloat16* x, int H,
-                              const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h, float* yexp,
-                              cudaStream_t s, cudaEvent_t mid_event = nullptr);
+cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& info, int quant4,
+                              const __nv_bfloat16* x, int H, const int32_t* row_token,
+                              __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s,
+                              cudaEvent_t mid_event = nullptr);
 
 cudaError_t launch_combine(const float* yexp, const int32_t* pos, const float* topk_w, int T, int H,
                            int k, int R, int n_shared, const float* shared_scale,
                            __nv_bfloat16* y, cudaStream_t s);
-
-// Splits caller groups into chunks of at most kMaxChunkRows rows and assigns CTA tile ranges.
-int plan_groups(const pm_ffn_group* groups, int n_groups, int hidden, std::vector<GroupDesc>* out,
-                int* tiles_gu, int* tiles_dn, int* max_rows, int* max_inter);
 
 cudaError_t launch_predictor_mlp(const __nv_bfloat16* x, int B, int H, const __nv_bfloat16* w1,
                                  const float* b1, int D, const __nv_bfloat16* w2, const float* b2,

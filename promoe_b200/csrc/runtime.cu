@@ -95,7 +95,15 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
   const int H = std::max(w.hidden, c->ws_hidden), I = std::max(max_inter, c->ws_inter);
   const int k = std::max(w.top_k, c->ws_topk);
   const size_t R = (size_t)cap * k, rows = R + cap;  // routed rows + one shared-expert row per token
-  c->desc_cap = (size_t)E + rows / kMaxChunkRows + 8;
+  {
+    // worst case of one layer call: every expert plus the shared expert, chunks of 64 rows, smallest
+    // tiles, and a few extra segments each aligned to 256 bytes
+    FfnPlanInfo worst;
+    worst.n_desc = E + (int)(rows / kMaxChunkRows) + 8;
+    worst.tiles_gu = worst.n_desc * ((I + kSplitTileGu - 1) / kSplitTileGu);
+    worst.tiles_dn = worst.n_desc * ((H + kSplitTileDn - 1) / kSplitTileDn);
+    c->plan_cap = align_up(worst.blob_bytes(), 256) + 64 * 256;
+  }
   size_t off = 0;
   auto take = [&](size_t bytes) {
     size_t o = off;
@@ -104,7 +112,7 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
   };
   size_t o_ids = take(R * 4), o_slot = take(R * 4), o_w = take(R * 4), o_ss = take((size_t)cap * 4);
   size_t o_cnt = take((size_t)(2 * E + 1) * 4), o_rt = take(rows * 4), o_pos = take(R * 4), o_err = take(4);
-  size_t o_h = take(rows * I * 2), o_y = take(rows * H * 4), o_desc = take(c->desc_cap * sizeof(GroupDesc));
+  size_t o_h = take(rows * I * 2), o_y = take(rows * H * 4), o_desc = take(c->plan_cap);
   size_t o_sc = take((size_t)c->cfg.num_layer * E * 4), o_ph = take((size_t)cap * 4096 * 4);
   size_t o_x = take((size_t)cap * H * 2), o_yo = take((size_t)cap * H * 2);
   PM_CUDA(cudaMalloc(&c->ws_dev, off));
@@ -122,14 +130,14 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
   c->d_err = (int32_t*)(b + o_err);
   c->d_hbuf = (__nv_bfloat16*)(b + o_h);
   c->d_yexp = (float*)(b + o_y);
-  c->d_desc = (GroupDesc*)(b + o_desc);
+  c->d_plan = b + o_desc;
   c->d_scores = (float*)(b + o_sc);
   c->d_pred_hidden = (float*)(b + o_ph);
   c->d_xin = (__nv_bfloat16*)(b + o_x);
   c->d_yout = (__nv_bfloat16*)(b + o_yo);
   // pinned staging: [counts+offsets | scores | routing ids | routing weights | descriptors]
   c->h_stage_bytes = align_up((size_t)(2 * E + 1) * 4, 256) + align_up((size_t)c->cfg.num_layer * E * 4, 256) +
-                     2 * align_up(R * 4, 256) + align_up(c->desc_cap * sizeof(GroupDesc), 256) +
+                     2 * align_up(R * 4, 256) + align_up(c->plan_cap, 256) +
                      align_up((size_t)E * 4, 256);
   PM_CUDA(cudaHostAlloc((void**)&c->h_stage, c->h_stage_bytes, cudaHostAllocDefault));
   c->ws_tokens = cap;
@@ -144,7 +152,7 @@ struct Stage {
   float* scores;    // [L, E]
   int32_t* ids;
   float* w;
-  GroupDesc* desc;
+  unsigned char* plan;
   int32_t* slot_table;
 };
 
@@ -161,8 +169,8 @@ Stage stage_of(pm_ctx* c) {
   p += align_up(R * 4, 256);
   s.w = (float*)p;
   p += align_up(R * 4, 256);
-  s.desc = (GroupDesc*)p;
-  p += align_up(c->desc_cap * sizeof(GroupDesc), 256);
+  s.plan = p;
+  p += align_up(c->plan_cap, 256);
   s.slot_table = (int32_t*)p;
   return s;
 }
@@ -373,15 +381,15 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
       c->line_waiter[line] = s;
     }
   }
-  std::vector<GroupDesc> desc;
-  int tg, td, mr, mi;
-  int rc = plan_groups(seg->groups.data(), (int)seg->groups.size(), w.hidden, &desc, &tg, &td, &mr, &mi);
+  FfnPlanInfo info;
+  int rc = plan_groups_size(seg->groups.data(), (int)seg->groups.size(), w.hidden, &info);
   if (rc != PM_OK) return rc;
-  if (*desc_used + desc.size() > c->desc_cap) return fail(PM_ERR_STATE, "descriptor buffer overflow");
+  if (*desc_used + info.blob_bytes() > c->plan_cap) return fail(PM_ERR_STATE, "launch plan buffer overflow");
   Stage st = stage_of(c);
-  std::memcpy(st.desc + *desc_used, desc.data(), desc.size() * sizeof(GroupDesc));
-  PM_CUDA(cudaMemcpyAsync(c->d_desc + *desc_used, st.desc + *desc_used, desc.size() * sizeof(GroupDesc),
-                          cudaMemcpyHostToDevice, s));
+  rc = plan_groups_into(seg->groups.data(), (int)seg->groups.size(), w.hidden, st.plan + *desc_used,
+                        c->plan_cap - *desc_used, &info);
+  if (rc != PM_OK) return rc;
+  PM_CUDA(cudaMemcpyAsync(c->d_plan + *desc_used, st.plan + *desc_used, info.blob_bytes(), cudaMemcpyHostToDevice, s));
   pm_ctx::FfnSample sample{};
   if (c->profile_ffn) {
     auto take_event = [&](cudaEvent_t* e) -> cudaError_t {
@@ -395,7 +403,6 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
     PM_CUDA(take_event(&sample.e0));
     PM_CUDA(take_event(&sample.e1));
     PM_CUDA(take_event(&sample.e2));
-    const int64_t elem = w.quant4 ? 1 : 4;  // bytes of one gate+up weight pair / two uint4 pairs
     for (const pm_ffn_group& g : seg->groups) {
       int64_t mat = (int64_t)g.inter * w.hidden;
       // uint4: half a byte per weight plus one fp16 {scale, zero} pair per 128 weights
@@ -403,18 +410,16 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
       sample.bytes_gu += 2 * one;
       sample.bytes_dn += one;
     }
-    (void)elem;
     PM_CUDA(cudaEventRecord(sample.e0, s));
   }
-  PM_CUDA(launch_swiglu_ffn(c->d_desc + *desc_used, (int)desc.size(), tg, td, mr, w.quant4, x, w.hidden,
-                            c->d_row_token, c->d_hbuf, c->ws_inter, c->d_yexp, s,
-                            c->profile_ffn ? sample.e1 : nullptr));
+  PM_CUDA(launch_swiglu_ffn(c->d_plan + *desc_used, info, w.quant4, x, w.hidden, c->d_row_token, c->d_hbuf,
+                            c->ws_inter, c->d_yexp, s, c->profile_ffn ? sample.e1 : nullptr));
   if (c->profile_ffn) {
     PM_CUDA(cudaEventRecord(sample.e2, s));
     c->ffn_samples.push_back(sample);
   }
   c->kernel_launches += 2;
-  *desc_used += desc.size();
+  *desc_used += align_up(info.blob_bytes(), 256);
   if (!seg->lines.empty()) {
     cudaEvent_t ev = next_seg_event(c);
     PM_CUDA(cudaEventRecord(ev, s));

@@ -82,8 +82,8 @@ struct pm_ctx {
   float *d_topk_w = nullptr, *d_shared_scale = nullptr, *d_yexp = nullptr, *d_scores = nullptr;
   float* d_pred_hidden = nullptr;
   __nv_bfloat16 *d_hbuf = nullptr, *d_xin = nullptr, *d_yout = nullptr;
-  pm::GroupDesc* d_desc = nullptr;
-  size_t desc_cap = 0;
+  unsigned char* d_plan = nullptr;  // launch plans of one layer call (descriptors + tile tables)
+  size_t plan_cap = 0;              // bytes
   unsigned char* h_stage = nullptr;  // pinned: counts+offsets, scores, descriptors, slot tables, routing
   size_t h_stage_bytes = 0;
 

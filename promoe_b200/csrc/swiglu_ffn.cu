@@ -44,23 +44,11 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 
 __device__ __forceinline__ float silu(float v) { return v / (1.f + __expf(-v)); }
 
-// Finds the chunk whose tile range holds `tile`. Chunks are sorted by tile start.
-template <bool GATEUP>
-__device__ __forceinline__ int find_group(const GroupDesc* __restrict__ groups, int n_groups, int tile) {
-  int lo = 0, hi = n_groups - 1;
-  while (lo < hi) {
-    int mid = (lo + hi + 1) >> 1;
-    int start = GATEUP ? groups[mid].tile_start_gu : groups[mid].tile_start_dn;
-    if (start <= tile) lo = mid; else hi = mid - 1;
-  }
-  return lo;
-}
-
 // NT = number of 8-row n-tiles of tokens a chunk may hold (rows <= 8*NT).
 // NMAT = 2 for the gate/up pass (two weight streams, SwiGLU epilogue), 1 for down.
 template <int NT, int NMAT>
 __global__ void __launch_bounds__(kThreads)
-grouped_ffn_kernel(const GroupDesc* __restrict__ groups, int n_groups,
+grouped_ffn_kernel(const GroupDesc* __restrict__ groups, const int32_t* __restrict__ tile_group,
                    const __nv_bfloat16* __restrict__ bsrc, int ldb,
                    const int32_t* __restrict__ row_token, int hidden, int kc_cap,
                    __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp) {
@@ -73,8 +61,7 @@ grouped_ffn_kernel(const GroupDesc* __restrict__ groups, int n_groups,
   const int g = lane >> 2;
   const int q = lane & 3;
 
-  const int gi = find_group<GATEUP>(groups, n_groups, blockIdx.x);
-  const GroupDesc grp = groups[gi];
+  const GroupDesc grp = groups[tile_group[blockIdx.x]];
   const int tile_local = blockIdx.x - (GATEUP ? grp.tile_start_gu : grp.tile_start_dn);
   const int K = GATEUP ? hidden : grp.inter;       // reduction length
   const int M = GATEUP ? grp.inter : hidden;       // weight rows
@@ -194,7 +181,7 @@ constexpr int kSplitThreads = kSplitWarps * 32;
 
 template <int NT, int NMAT, int DEPTH>
 __global__ void __launch_bounds__(kSplitThreads, 2)
-grouped_ffn_splitk_kernel(const GroupDesc* __restrict__ groups, int n_groups,
+grouped_ffn_splitk_kernel(const GroupDesc* __restrict__ groups, const int32_t* __restrict__ tile_group,
                           const __nv_bfloat16* __restrict__ bsrc, int ldb,
                           const int32_t* __restrict__ row_token, int hidden,
                           __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp) {
@@ -207,8 +194,7 @@ grouped_ffn_splitk_kernel(const GroupDesc* __restrict__ groups, int n_groups,
   const int g = lane >> 2;
   const int q = lane & 3;
 
-  const int gi = find_group<GATEUP>(groups, n_groups, blockIdx.x);
-  const GroupDesc grp = groups[gi];
+  const GroupDesc grp = groups[tile_group[blockIdx.x]];
   const int tile_local = blockIdx.x - (GATEUP ? grp.tile_start_gu : grp.tile_start_dn);
   const int K = GATEUP ? hidden : grp.inter;
   const int rows = grp.row_count;
@@ -315,12 +301,12 @@ grouped_ffn_splitk_kernel(const GroupDesc* __restrict__ groups, int n_groups,
 }
 
 template <int NT, int NMAT>
-cudaError_t launch_splitk(const GroupDesc* groups, int n_groups, int tiles, const __nv_bfloat16* bsrc, int ldb,
+cudaError_t launch_splitk(const GroupDesc* groups, const int32_t* tile_group, int tiles, const __nv_bfloat16* bsrc, int ldb,
                           const int32_t* row_token, int hidden, __nv_bfloat16* hbuf, int ld_h, float* yexp,
                           cudaStream_t s) {
   constexpr int kDepthSplit = (NT == 1) ? 4 : 2;
   grouped_ffn_splitk_kernel<NT, NMAT, kDepthSplit><<<tiles, kSplitThreads, 0, s>>>(
-      groups, n_groups, bsrc, ldb, row_token, hidden, hbuf, ld_h, yexp);
+      groups, tile_group, bsrc, ldb, row_token, hidden, hbuf, ld_h, yexp);
   return cudaGetLastError();
 }
 
@@ -332,7 +318,7 @@ int kc_cap_for(int nt, int maxK) {
 }
 
 template <int NT, int NMAT>
-cudaError_t launch_one(const GroupDesc* groups, int n_groups, int tiles, const __nv_bfloat16* bsrc,
+cudaError_t launch_one(const GroupDesc* groups, const int32_t* tile_group, int tiles, const __nv_bfloat16* bsrc,
                        int ldb, const int32_t* row_token, int hidden, int maxK,
                        __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s) {
   const int cap = kc_cap_for(NT, maxK);
@@ -342,38 +328,42 @@ cudaError_t launch_one(const GroupDesc* groups, int n_groups, int tiles, const _
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  kern<<<tiles, kThreads, smem, s>>>(groups, n_groups, bsrc, ldb, row_token, hidden, cap, hbuf, ld_h, yexp);
+  kern<<<tiles, kThreads, smem, s>>>(groups, tile_group, bsrc, ldb, row_token, hidden, cap, hbuf, ld_h, yexp);
   return cudaGetLastError();
 }
 
 template <int NMAT>
-cudaError_t dispatch_nt(int max_rows, const GroupDesc* groups, int n_groups, int tiles,
+cudaError_t dispatch_nt(int max_rows, const GroupDesc* groups, const int32_t* tile_group, int tiles,
                         const __nv_bfloat16* bsrc, int ldb, const int32_t* row_token, int hidden,
                         int maxK, __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s) {
   if (max_rows <= 8)
-    return launch_one<1, NMAT>(groups, n_groups, tiles, bsrc, ldb, row_token, hidden, maxK, hbuf, ld_h, yexp, s);
+    return launch_one<1, NMAT>(groups, tile_group, tiles, bsrc, ldb, row_token, hidden, maxK, hbuf, ld_h, yexp, s);
   if (max_rows <= 16)
-    return launch_one<2, NMAT>(groups, n_groups, tiles, bsrc, ldb, row_token, hidden, maxK, hbuf, ld_h, yexp, s);
+    return launch_one<2, NMAT>(groups, tile_group, tiles, bsrc, ldb, row_token, hidden, maxK, hbuf, ld_h, yexp, s);
   if (max_rows <= 32)
-    return launch_one<4, NMAT>(groups, n_groups, tiles, bsrc, ldb, row_token, hidden, maxK, hbuf, ld_h, yexp, s);
-  return launch_one<8, NMAT>(groups, n_groups, tiles, bsrc, ldb, row_token, hidden, maxK, hbuf, ld_h, yexp, s);
+    return launch_one<4, NMAT>(groups, tile_group, tiles, bsrc, ldb, row_token, hidden, maxK, hbuf, ld_h, yexp, s);
+  return launch_one<8, NMAT>(groups, tile_group, tiles, bsrc, ldb, row_token, hidden, maxK, hbuf, ld_h, yexp, s);
 }
 
 }  // namespace
 
-cudaError_t launch_swiglu_ffn(const GroupDesc* groups_dev, int n_groups, int tiles_gu, int tiles_dn,
-                              int max_rows, int quant4, const __nv_bfloat16* x, int H,
-                              const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h, float* yexp,
-                              cudaStream_t s, cudaEvent_t mid_event) {
-  if (n_groups <= 0) return cudaSuccess;
+cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& info, int quant4,
+                              const __nv_bfloat16* x, int H, const int32_t* row_token,
+                              __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s,
+                              cudaEvent_t mid_event) {
+  if (info.n_desc <= 0) return cudaSuccess;
   if (quant4) return cudaErrorNotSupported;
+  const GroupDesc* groups = reinterpret_cast<const GroupDesc*>(blob_dev);
+  const int32_t* t_gu = reinterpret_cast<const int32_t*>(blob_dev + info.off_tile_gu());
+  const int32_t* t_dn = reinterpret_cast<const int32_t*>(blob_dev + info.off_tile_dn());
+  const int max_rows = info.max_rows;
   cudaError_t e;
   if (max_rows <= 8) {
-    e = launch_splitk<1, 2>(groups_dev, n_groups, tiles_gu, x, H, row_token, H, hbuf, ld_h, yexp, s);
+    e = launch_splitk<1, 2>(groups, t_gu, info.tiles_gu, x, H, row_token, H, hbuf, ld_h, yexp, s);
   } else if (max_rows <= kSplitMaxRows) {
-    e = launch_splitk<2, 2>(groups_dev, n_groups, tiles_gu, x, H, row_token, H, hbuf, ld_h, yexp, s);
+    e = launch_splitk<2, 2>(groups, t_gu, info.tiles_gu, x, H, row_token, H, hbuf, ld_h, yexp, s);
   } else {
-    e = dispatch_nt<2>(max_rows, groups_dev, n_groups, tiles_gu, x, H, row_token, H, H, hbuf, ld_h, yexp, s);
+    e = dispatch_nt<2>(max_rows, groups, t_gu, info.tiles_gu, x, H, row_token, H, H, hbuf, ld_h, yexp, s);
   }
   if (e != cudaSuccess) return e;
   if (mid_event != nullptr) {
@@ -381,11 +371,11 @@ cudaError_t launch_swiglu_ffn(const GroupDesc* groups_dev, int n_groups, int til
     if (e != cudaSuccess) return e;
   }
   if (max_rows <= 8)
-    return launch_splitk<1, 1>(groups_dev, n_groups, tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s);
+    return launch_splitk<1, 1>(groups, t_dn, info.tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s);
   if (max_rows <= kSplitMaxRows)
-    return launch_splitk<2, 1>(groups_dev, n_groups, tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s);
-  return dispatch_nt<1>(max_rows, groups_dev, n_groups, tiles_dn, hbuf, ld_h, row_token, H, ld_h, nullptr,
-                        ld_h, yexp, s);
+    return launch_splitk<2, 1>(groups, t_dn, info.tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s);
+  return dispatch_nt<1>(max_rows, groups, t_dn, info.tiles_dn, hbuf, ld_h, row_token, H, ld_h, nullptr, ld_h,
+                        yexp, s);
 }
 
 }  // namespace pm

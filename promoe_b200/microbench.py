@@ -30,7 +30,7 @@ def run(groups: int, rows: int, hidden: int, inter: int, iters: int, warmup: int
                                    i * rows, rows, inter, 0)
     n_rows = groups * rows
     row_token = torch.randint(0, tokens, (n_rows,), dtype=torch.int32, device=dev)
-    nbytes = _lib.call("pm_k_swiglu_ffn_scratch_bytes", groups, n_rows, inter)
+    nbytes = _lib.call("pm_k_swiglu_ffn_scratch_bytes", groups, n_rows, inter, hidden)
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     yexp = torch.empty((n_rows, hidden), dtype=torch.float32, device=dev)
 

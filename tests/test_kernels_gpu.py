@@ -141,7 +141,7 @@ def run_ffn(lib, x, groups, row_token, H):
     n_rows = int(row_token.shape[0])
     rt = dev(row_token)
     max_inter = max(g[5] for g in groups)
-    nbytes = _lib.call("pm_k_swiglu_ffn_scratch_bytes", len(groups), n_rows, max_inter)
+    nbytes = _lib.call("pm_k_swiglu_ffn_scratch_bytes", len(groups), n_rows, max_inter, H)
     scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
     yexp = torch.full((n_rows, H), float("nan"), dtype=torch.float32, device="cuda")
     _lib.call("pm_k_swiglu_ffn", arr, len(groups), 0, ptr(xd), H, ptr(rt), n_rows, ptr(yexp),
