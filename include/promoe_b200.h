@@ -209,6 +209,19 @@ size_t pm_k_swiglu_ffn_scratch_bytes(int n_groups, int n_rows, int max_inter, in
 int pm_k_swiglu_ffn(const pm_ffn_group* groups, int n_groups, int quant4, const void* x, int hidden,
                     const int32_t* row_token, int n_rows, float* yexp, void* scratch,
                     size_t scratch_bytes, void* stream);
+/* No counterpart in the reference. The same grouped SwiGLU FFN for callers that cannot supply
+ * scratch: hosts whose own pools already own all device memory, or code paths where an
+ * allocation (which synchronises the device) is not acceptable. Plan and intermediate rows live
+ * in an array built into the library image (pm_k_swiglu_ffn_static_capacity() bytes, 8 MiB, held
+ * by every GPU that loads the library until exit); this call performs no cudaMalloc / cudaFree
+ * and no allocating library call. A launch that needs more than the array holds (plan above
+ * 64 KiB, or plan + n_rows * max_inter * 2 bytes above the capacity) is rejected with
+ * PM_ERR_INVALID. bf16 experts only. The first call on a device looks the array's device
+ * address up; make that call before any stream capture. All calls share the array: calls that
+ * overlap on the GPU race, serialise them. */
+size_t pm_k_swiglu_ffn_static_capacity(void);
+int pm_k_swiglu_ffn_static(const pm_ffn_group* groups, int n_groups, const void* x, int hidden,
+                           const int32_t* row_token, int n_rows, float* yexp, void* stream);
 int pm_k_combine(const float* yexp, const int32_t* pos, const float* topk_w, int T, int H, int k, int R,
                  int n_shared, const float* shared_scale, void* y, void* stream);
 /* scores[e] = sum_b (W2 relu(W1 x_b + b1) + b2)[e]; hidden_scratch is f32 [B, d] device scratch. */

@@ -93,10 +93,12 @@ SIGNATURES = {
     "pm_k_permute": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "pm_k_swiglu_ffn_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "pm_k_swiglu_ffn": (_i, [C.POINTER(pm_ffn_group), _i, _i, _vp, _i, _vp, _i, _vp, _vp, _sz, _vp]),
+    "pm_k_swiglu_ffn_static_capacity": (_sz, []),
+    "pm_k_swiglu_ffn_static": (_i, [C.POINTER(pm_ffn_group), _i, _vp, _i, _vp, _i, _vp, _vp]),
     "pm_k_combine": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
     "pm_k_predictor_mlp": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp]),
 }
-_RAW = {"pm_version", "pm_last_error", "pm_k_swiglu_ffn_scratch_bytes"}
+_RAW = {"pm_version", "pm_last_error", "pm_k_swiglu_ffn_scratch_bytes", "pm_k_swiglu_ffn_static_capacity"}
 
 _lib = None
 
