@@ -132,9 +132,12 @@ int pm_stats_read(pm_ctx* ctx, pm_stats* out);
 /* Device time and weight bytes of the grouped FFN launches made while the context option
  * profile_ffn=1 was set (CUDA events on the caller's stream around each launch). */
 typedef struct pm_profile {
-  int64_t ffn_launches;  /* gate/up + down launch pairs */
+  int64_t ffn_launches;  /* gate/up + down launch pairs (two-launch path) */
   double gateup_ms, down_ms;
   int64_t gateup_bytes, down_bytes; /* weight bytes those launches had to read once */
+  int64_t fused_launches; /* single cooperative launches (gate/up, grid barrier, down) */
+  double fused_ms;
+  int64_t fused_bytes;
 } pm_profile;
 int pm_profile_read(pm_ctx* ctx, pm_profile* out, int reset);
 

@@ -1,5 +1,6 @@
 // C-ABI entry points of the stateless kernels, plus the per-thread error message.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -65,6 +66,7 @@ static int plan_core(const pm_ffn_group* groups, int n_groups, int hidden, unsig
     }
   }
   info->n_desc = n; info->tiles_gu = tg; info->tiles_dn = td; info->max_rows = mr; info->max_inter = mi;
+  if (blob != nullptr) std::memset(blob + info->off_counters(), 0, 16);
   return PM_OK;
 }
 
@@ -147,8 +149,10 @@ int pm_k_swiglu_ffn(const pm_ffn_group* groups, int n_groups, int quant4, const 
   // The plan upload is from pageable memory, so it is staged before this call returns.
   PM_CUDA(cudaMemcpyAsync(scratch, blob.data(), blob.size(), cudaMemcpyHostToDevice, s));
   __nv_bfloat16* hbuf = (__nv_bfloat16*)((unsigned char*)scratch + plan_bytes);
+  // PM_FFN_TWO_LAUNCH=1 selects the two-launch path (for comparisons); the default is the fused kernel.
+  static const bool two_launch = std::getenv("PM_FFN_TWO_LAUNCH") != nullptr;
   PM_CUDA(launch_swiglu_ffn((const unsigned char*)scratch, info, quant4, (const __nv_bfloat16*)x, hidden,
-                            row_token, hbuf, info.max_inter, yexp, s));
+                            row_token, hbuf, info.max_inter, yexp, s, nullptr, !two_launch));
   return PM_OK;
 }
 

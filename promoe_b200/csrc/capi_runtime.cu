@@ -97,6 +97,10 @@ int pm_ctx_set(pm_ctx* ctx, const char* key, const char* value) {
     ctx->seq_len = std::atoi(value);
     return PM_OK;
   }
+  if (k == "fused_ffn") {
+    ctx->fused_ffn = (v == "1" || v == "true" || v == "True" || v == "on");
+    return PM_OK;
+  }
   if (k == "profile_ffn") {
     ctx->profile_ffn = (v == "1" || v == "true" || v == "True" || v == "on");
     return PM_OK;
@@ -303,7 +307,13 @@ int pm_profile_read(pm_ctx* ctx, pm_profile* out, int reset) {
   out->down_ms = ctx->ffn_ms_dn;
   out->gateup_bytes = ctx->ffn_bytes_gu;
   out->down_bytes = ctx->ffn_bytes_dn;
+  out->fused_launches = ctx->ffn_fused_launches;
+  out->fused_ms = ctx->ffn_ms_fused;
+  out->fused_bytes = ctx->ffn_bytes_fused;
   if (reset) {
+    ctx->ffn_fused_launches = 0;
+    ctx->ffn_ms_fused = 0;
+    ctx->ffn_bytes_fused = 0;
     ctx->ffn_launches = 0;
     ctx->ffn_ms_gu = ctx->ffn_ms_dn = 0;
     ctx->ffn_bytes_gu = ctx->ffn_bytes_dn = 0;

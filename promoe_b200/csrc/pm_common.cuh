@@ -61,12 +61,13 @@ cudaError_t launch_permute(const int32_t* topk_ids, int R, int k, int E, int32_t
 
 // Geometry of one grouped FFN launch pair. The device blob it describes holds, 16-byte aligned
 // and in this order: n_desc GroupDesc, tiles_gu int32 (chunk index of every gate/up CTA tile),
-// tiles_dn int32 (same for the down launch).
+// tiles_dn int32 (same for the down launch), then two int32 tile counters that start at zero.
 struct FfnPlanInfo {
   int n_desc = 0, tiles_gu = 0, tiles_dn = 0, max_rows = 0, max_inter = 0;
   size_t off_tile_gu() const { return ((size_t)n_desc * sizeof(GroupDesc) + 15) / 16 * 16; }
   size_t off_tile_dn() const { return off_tile_gu() + ((size_t)tiles_gu * 4 + 15) / 16 * 16; }
-  size_t blob_bytes() const { return off_tile_dn() + ((size_t)tiles_dn * 4 + 15) / 16 * 16; }
+  size_t off_counters() const { return off_tile_dn() + ((size_t)tiles_dn * 4 + 15) / 16 * 16; }
+  size_t blob_bytes() const { return off_counters() + 16; }  // two zeroed tile counters (fused kernel)
 };
 
 // Splits caller groups into chunks of at most kMaxChunkRows rows, assigns CTA tile ranges and
@@ -76,11 +77,13 @@ int plan_groups_into(const pm_ffn_group* groups, int n_groups, int hidden, unsig
 // Size pass of the same planner (blob == nullptr): fills `info` only.
 int plan_groups_size(const pm_ffn_group* groups, int n_groups, int hidden, FfnPlanInfo* info);
 
-// mid_event (optional) is recorded between the gate/up and the down launch.
+// Launches of at most kSplitMaxRows rows per chunk run as ONE cooperative kernel (gate/up tiles,
+// grid barrier, down tiles) unless `fused` is false or a mid_event is wanted; mid_event
+// (optional) is recorded between the gate/up and the down launch of the two-launch path.
 cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& info, int quant4,
                               const __nv_bfloat16* x, int H, const int32_t* row_token,
                               __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s,
-                              cudaEvent_t mid_event = nullptr);
+                              cudaEvent_t mid_event = nullptr, bool fused = true);
 
 cudaError_t launch_combine(const float* yexp, const int32_t* pos, const float* topk_w, int T, int H,
                            int k, int R, int n_shared, const float* shared_scale,

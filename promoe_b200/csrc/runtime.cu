@@ -245,15 +245,22 @@ int rt_profile_collect(pm_ctx* c) {
   for (pm_ctx::FfnSample& f : c->ffn_samples) {
     PM_CUDA(cudaEventSynchronize(f.e2));
     float a = 0.f, b = 0.f;
-    PM_CUDA(cudaEventElapsedTime(&a, f.e0, f.e1));
-    PM_CUDA(cudaEventElapsedTime(&b, f.e1, f.e2));
-    c->ffn_ms_gu += a;
-    c->ffn_ms_dn += b;
-    c->ffn_bytes_gu += f.bytes_gu;
-    c->ffn_bytes_dn += f.bytes_dn;
-    c->ffn_launches += 1;
+    if (f.fused) {
+      PM_CUDA(cudaEventElapsedTime(&a, f.e0, f.e2));
+      c->ffn_ms_fused += a;
+      c->ffn_bytes_fused += f.bytes_gu + f.bytes_dn;
+      c->ffn_fused_launches += 1;
+    } else {
+      PM_CUDA(cudaEventElapsedTime(&a, f.e0, f.e1));
+      PM_CUDA(cudaEventElapsedTime(&b, f.e1, f.e2));
+      c->ffn_ms_gu += a;
+      c->ffn_ms_dn += b;
+      c->ffn_bytes_gu += f.bytes_gu;
+      c->ffn_bytes_dn += f.bytes_dn;
+      c->ffn_launches += 1;
+      c->ffn_event_pool.push_back(f.e1);
+    }
     c->ffn_event_pool.push_back(f.e0);
-    c->ffn_event_pool.push_back(f.e1);
     c->ffn_event_pool.push_back(f.e2);
   }
   c->ffn_samples.clear();
@@ -400,8 +407,9 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
       }
       return cudaEventCreate(e);
     };
+    sample.fused = c->fused_ffn && info.max_rows <= kSplitMaxRows;
     PM_CUDA(take_event(&sample.e0));
-    PM_CUDA(take_event(&sample.e1));
+    if (!sample.fused) PM_CUDA(take_event(&sample.e1));
     PM_CUDA(take_event(&sample.e2));
     for (const pm_ffn_group& g : seg->groups) {
       int64_t mat = (int64_t)g.inter * w.hidden;
@@ -413,12 +421,12 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
     PM_CUDA(cudaEventRecord(sample.e0, s));
   }
   PM_CUDA(launch_swiglu_ffn(c->d_plan + *desc_used, info, w.quant4, x, w.hidden, c->d_row_token, c->d_hbuf,
-                            c->ws_inter, c->d_yexp, s, c->profile_ffn ? sample.e1 : nullptr));
+                            c->ws_inter, c->d_yexp, s, c->profile_ffn ? sample.e1 : nullptr, c->fused_ffn));
   if (c->profile_ffn) {
     PM_CUDA(cudaEventRecord(sample.e2, s));
     c->ffn_samples.push_back(sample);
   }
-  c->kernel_launches += 2;
+  c->kernel_launches += (c->fused_ffn && info.max_rows <= kSplitMaxRows) ? 1 : 2;
   *desc_used += align_up(info.blob_bytes(), 256);
   if (!seg->lines.empty()) {
     cudaEvent_t ev = next_seg_event(c);
@@ -631,7 +639,7 @@ pm_ctx::~pm_ctx() {
   if (sync_event) cudaEventDestroy(sync_event);
   for (auto& f : ffn_samples) {
     cudaEventDestroy(f.e0);
-    cudaEventDestroy(f.e1);
+    if (f.e1) cudaEventDestroy(f.e1);
     cudaEventDestroy(f.e2);
   }
   for (auto e : ffn_event_pool) cudaEventDestroy(e);

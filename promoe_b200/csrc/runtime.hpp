@@ -96,14 +96,16 @@ struct pm_ctx {
 
   // ---- optional timing of the grouped FFN launches (for the roofline figure) ------------------
   struct FfnSample {
-    cudaEvent_t e0, e1, e2;  // before gate/up, between, after down
+    cudaEvent_t e0, e1, e2;  // before gate/up, between (null for a fused launch), after down
     int64_t bytes_gu, bytes_dn;
+    bool fused;
   };
   bool profile_ffn = false;
+  bool fused_ffn = true;  // one cooperative launch per segment when the chunks are small enough
   std::vector<FfnSample> ffn_samples;      // recorded, not yet read
   std::vector<cudaEvent_t> ffn_event_pool; // free events
-  double ffn_ms_gu = 0, ffn_ms_dn = 0;
-  int64_t ffn_bytes_gu = 0, ffn_bytes_dn = 0, ffn_launches = 0;
+  double ffn_ms_gu = 0, ffn_ms_dn = 0, ffn_ms_fused = 0;
+  int64_t ffn_bytes_gu = 0, ffn_bytes_dn = 0, ffn_launches = 0, ffn_bytes_fused = 0, ffn_fused_launches = 0;
 
   ~pm_ctx();
 };

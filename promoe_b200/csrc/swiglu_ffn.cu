@@ -17,6 +17,8 @@
 // lane loads 16 contiguous bytes (8 bf16) of a weight row and of a token row at
 // the same k offset and feeds pairs {0,1} and {2,3} to one m16n8k16 MMA and pairs
 // {4,5}, {6,7} to a second one. Both operands therefore use full 128-bit loads.
+#include <cooperative_groups.h>
+
 #include "pm_common.cuh"
 
 namespace pm {
@@ -179,23 +181,32 @@ grouped_ffn_kernel(const GroupDesc* __restrict__ groups, const int32_t* __restri
 constexpr int kSplitWarps = 8;
 constexpr int kSplitThreads = kSplitWarps * 32;
 
-template <int NT, int NMAT, int DEPTH>
-__global__ void __launch_bounds__(kSplitThreads, 2)
-grouped_ffn_splitk_kernel(const GroupDesc* __restrict__ groups, const int32_t* __restrict__ tile_group,
-                          const __nv_bfloat16* __restrict__ bsrc, int ldb,
-                          const int32_t* __restrict__ row_token, int hidden,
-                          __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp) {
-  constexpr bool GATEUP = (NMAT == 2);
-  constexpr int kVals = 2 * NT * 4;  // accumulator values per lane
-  __shared__ float red[kSplitWarps][kVals][32];
+// Token-row fragment load. Rows written earlier in the same kernel (the fused variant reads the
+// intermediate rows other CTAs produced before the grid barrier) must not go through the
+// non-coherent path.
+template <bool COHERENT>
+__device__ __forceinline__ uint4 load_b(const unsigned char* p) {
+  uint4 r;
+  if (COHERENT) {
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  } else {
+    r = __ldg(reinterpret_cast<const uint4*>(p));
+  }
+  return r;
+}
 
+// One split-K tile: 16 gate + 16 up rows (GATEUP) or 32 down rows of one chunk, all 8 warps of
+// the CTA. `red` is the CTA's reduction buffer; the caller separates consecutive tiles by a barrier.
+template <int NT, bool GATEUP, int DEPTH, bool COHERENT_B>
+__device__ __forceinline__ void splitk_tile(const GroupDesc& grp, int tile_local,
+                                            const __nv_bfloat16* __restrict__ bsrc, int ldb,
+                                            const int32_t* __restrict__ row_token, int hidden,
+                                            __nv_bfloat16* __restrict__ hbuf, int ld_h,
+                                            float* __restrict__ yexp, float (*red)[2 * NT * 4][32]) {
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int g = lane >> 2;
   const int q = lane & 3;
-
-  const GroupDesc grp = groups[tile_group[blockIdx.x]];
-  const int tile_local = blockIdx.x - (GATEUP ? grp.tile_start_gu : grp.tile_start_dn);
   const int K = GATEUP ? hidden : grp.inter;
   const int rows = grp.row_count;
   const int m0 = tile_local * (GATEUP ? 16 : 32);
@@ -248,7 +259,7 @@ grouped_ffn_splitk_kernel(const GroupDesc* __restrict__ groups, const int32_t* _
         for (int j = 0; j < 4; ++j) a[d][j] = ldg_stream(a_ptr[j] + off);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
-          b[d][nt] = b_ok[nt] ? __ldg(reinterpret_cast<const uint4*>(b_ptr[nt] + off)) : make_uint4(0, 0, 0, 0);
+          b[d][nt] = b_ok[nt] ? load_b<COHERENT_B>(b_ptr[nt] + off) : make_uint4(0, 0, 0, 0);
       }
     }
 #pragma unroll
@@ -298,6 +309,96 @@ grouped_ffn_splitk_kernel(const GroupDesc* __restrict__ groups, const int32_t* _
       yexp[r * hidden + m + 16] = s1v;
     }
   }
+}
+
+template <int NT, int NMAT, int DEPTH>
+__global__ void __launch_bounds__(kSplitThreads, 2)
+grouped_ffn_splitk_kernel(const GroupDesc* __restrict__ groups, const int32_t* __restrict__ tile_group,
+                          const __nv_bfloat16* __restrict__ bsrc, int ldb,
+                          const int32_t* __restrict__ row_token, int hidden,
+                          __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp) {
+  constexpr bool GATEUP = (NMAT == 2);
+  __shared__ float red[kSplitWarps][2 * NT * 4][32];
+  const GroupDesc grp = groups[tile_group[blockIdx.x]];
+  const int tile_local = blockIdx.x - (GATEUP ? grp.tile_start_gu : grp.tile_start_dn);
+  splitk_tile<NT, GATEUP, DEPTH, false>(grp, tile_local, bsrc, ldb, row_token, hidden, hbuf, ld_h, yexp, red);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Fused decode variant: ONE cooperative launch per segment. A fixed grid of resident CTAs pulls
+// gate/up tiles from a counter, meets at a grid barrier (the intermediate rows must be complete
+// before any down tile reads them), then pulls down tiles. Compared with two launches this
+// removes one launch gap and one tail per segment, and dynamic tile pulling evens out the
+// heavier tiles of the wide shared expert.
+// ---------------------------------------------------------------------------------------------
+template <int NT, bool GATEUP, int DEPTH>
+__device__ __forceinline__ void pull_tiles(const GroupDesc* __restrict__ groups,
+                                           const int32_t* __restrict__ tile_group, int n_tiles, int* counter,
+                                           const __nv_bfloat16* __restrict__ bsrc, int ldb,
+                                           const int32_t* __restrict__ row_token, int hidden,
+                                           __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp,
+                                           float (*red)[2 * NT * 4][32], int* s_tile) {
+  while (true) {
+    if (threadIdx.x == 0) *s_tile = atomicAdd(counter, 1);
+    __syncthreads();  // also separates this tile's use of `red` from the previous tile's epilogue
+    const int tile = *s_tile;
+    if (tile >= n_tiles) break;
+    const GroupDesc grp = groups[tile_group[tile]];
+    const int tile_local = tile - (GATEUP ? grp.tile_start_gu : grp.tile_start_dn);
+    splitk_tile<NT, GATEUP, DEPTH, !GATEUP>(grp, tile_local, bsrc, ldb, row_token, hidden, hbuf, ld_h, yexp, red);
+    __syncthreads();  // every thread has read *s_tile and finished with `red`
+  }
+}
+
+template <int NT, int DEPTH>
+__global__ void __launch_bounds__(kSplitThreads, 2)
+grouped_ffn_fused_kernel(const GroupDesc* __restrict__ groups, const int32_t* __restrict__ tile_gu,
+                         const int32_t* __restrict__ tile_dn, int tiles_gu, int tiles_dn, int* counters,
+                         const __nv_bfloat16* __restrict__ x, int hidden,
+                         const int32_t* __restrict__ row_token, __nv_bfloat16* hbuf, int ld_h,
+                         float* __restrict__ yexp) {
+  __shared__ float red[kSplitWarps][2 * NT * 4][32];
+  __shared__ int s_tile;
+  pull_tiles<NT, true, DEPTH>(groups, tile_gu, tiles_gu, counters, x, hidden, row_token, hidden, hbuf, ld_h, yexp,
+                              red, &s_tile);
+  __threadfence();
+  cooperative_groups::this_grid().sync();
+  pull_tiles<NT, false, DEPTH>(groups, tile_dn, tiles_dn, counters + 1, hbuf, ld_h, row_token, hidden, nullptr,
+                               ld_h, yexp, red, &s_tile);
+}
+
+// Resident grid of the fused kernel on the current device (0 if cooperative launch is unavailable).
+template <int NT, int DEPTH>
+int fused_grid_size() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] != 0) return cached[dev] < 0 ? 0 : cached[dev];
+  int coop = 0, sms = 0, per_sm = 0;
+  cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (!coop || sms <= 0 ||
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, grouped_ffn_fused_kernel<NT, DEPTH>, kSplitThreads, 0) !=
+          cudaSuccess ||
+      per_sm <= 0) {
+    cached[dev] = -1;
+    return 0;
+  }
+  cached[dev] = sms * per_sm;
+  return cached[dev];
+}
+
+template <int NT, int DEPTH>
+cudaError_t launch_fused(const GroupDesc* groups, const int32_t* t_gu, const int32_t* t_dn, int tiles_gu,
+                         int tiles_dn, int* counters, const __nv_bfloat16* x, int hidden,
+                         const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s) {
+  int grid = fused_grid_size<NT, DEPTH>();
+  if (grid <= 0) return cudaErrorNotSupported;
+  grid = min(grid, max(tiles_gu, tiles_dn));
+  void* args[] = {(void*)&groups, (void*)&t_gu, (void*)&t_dn, (void*)&tiles_gu, (void*)&tiles_dn, (void*)&counters,
+                  (void*)&x, (void*)&hidden, (void*)&row_token, (void*)&hbuf, (void*)&ld_h, (void*)&yexp};
+  return cudaLaunchCooperativeKernel((const void*)grouped_ffn_fused_kernel<NT, DEPTH>, dim3(grid), dim3(kSplitThreads),
+                                     args, 0, s);
 }
 
 template <int NT, int NMAT>
@@ -350,7 +451,7 @@ cudaError_t dispatch_nt(int max_rows, const GroupDesc* groups, const int32_t* ti
 cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& info, int quant4,
                               const __nv_bfloat16* x, int H, const int32_t* row_token,
                               __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s,
-                              cudaEvent_t mid_event) {
+                              cudaEvent_t mid_event, bool fused) {
   if (info.n_desc <= 0) return cudaSuccess;
   if (quant4) return cudaErrorNotSupported;
   const GroupDesc* groups = reinterpret_cast<const GroupDesc*>(blob_dev);
@@ -358,6 +459,14 @@ cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& 
   const int32_t* t_dn = reinterpret_cast<const int32_t*>(blob_dev + info.off_tile_dn());
   const int max_rows = info.max_rows;
   cudaError_t e;
+  if (fused && max_rows <= kSplitMaxRows && mid_event == nullptr) {
+    int* counters = reinterpret_cast<int*>(const_cast<unsigned char*>(blob_dev) + info.off_counters());
+    e = (max_rows <= 8)
+            ? launch_fused<1, 4>(groups, t_gu, t_dn, info.tiles_gu, info.tiles_dn, counters, x, H, row_token, hbuf, ld_h, yexp, s)
+            : launch_fused<2, 2>(groups, t_gu, t_dn, info.tiles_gu, info.tiles_dn, counters, x, H, row_token, hbuf, ld_h, yexp, s);
+    if (e != cudaErrorNotSupported) return e;
+    (void)cudaGetLastError();  // cooperative launch unavailable: fall through to the two-launch path
+  }
   if (max_rows <= 8) {
     e = launch_splitk<1, 2>(groups, t_gu, info.tiles_gu, x, H, row_token, H, hbuf, ld_h, yexp, s);
   } else if (max_rows <= kSplitMaxRows) {
