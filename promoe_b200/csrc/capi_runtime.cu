@@ -97,6 +97,10 @@ int pm_ctx_set(pm_ctx* ctx, const char* key, const char* value) {
     ctx->seq_len = std::atoi(value);
     return PM_OK;
   }
+  if (k == "device_plan") {
+    ctx->device_plan = (v == "1" || v == "true" || v == "True" || v == "on");
+    return PM_OK;
+  }
   if (k == "fused_ffn") {
     ctx->fused_ffn = (v == "1" || v == "true" || v == "True" || v == "on");
     return PM_OK;

@@ -77,6 +77,37 @@ int plan_groups_into(const pm_ffn_group* groups, int n_groups, int hidden, unsig
 // Size pass of the same planner (blob == nullptr): fills `info` only.
 int plan_groups_size(const pm_ffn_group* groups, int n_groups, int hidden, FfnPlanInfo* info);
 
+// Everything the device-side planner needs to describe the resident experts of one layer.
+struct ResidentPlanArgs {
+  const unsigned char* pool_base;  // first cache line of the layer's pool
+  size_t line_stride;
+  size_t off_gate, off_up, off_down;  // tensor offsets inside a line
+  const void *shared_w_gate, *shared_w_up, *shared_w_down;
+  int32_t num_expert, inter, shared_inter, hidden;
+  int32_t tokens, n_routed_rows;
+  // byte offsets of the sections inside the device blob (header of five int32 at offset 0)
+  size_t off_desc, off_tile_gu, off_tile_dn;
+  // Section sizes for num_expert experts plus the shared expert.
+  static size_t blob_bytes(int num_expert, int inter, int shared_inter, int hidden, size_t* off_desc,
+                           size_t* off_gu, size_t* off_dn) {
+    const size_t n = (size_t)num_expert + 1;
+    const size_t gu = (size_t)num_expert * (inter / kSplitTileGu) + shared_inter / kSplitTileGu;
+    const size_t dn = n * (hidden / kSplitTileDn);
+    *off_desc = 64;
+    *off_gu = *off_desc + n * sizeof(GroupDesc);
+    *off_dn = *off_gu + (gu * 4 + 15) / 16 * 16;
+    return *off_dn + (dn * 4 + 15) / 16 * 16;
+  }
+};
+// Plans (on the device) and launches the fused FFN for the shared expert and every activated
+// expert that the slot table shows resident. start_event (optional) is recorded between the
+// planner and the FFN kernel. Needs cooperative launch and at most kSplitMaxRows rows per expert.
+cudaError_t launch_resident_ffn(const int32_t* counts, const int32_t* offsets, const int32_t* slot_table,
+                                const ResidentPlanArgs& a, unsigned char* blob_dev, int max_rows,
+                                const __nv_bfloat16* x, const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h,
+                                float* yexp, cudaStream_t s, cudaEvent_t start_event);
+bool resident_ffn_available(int max_rows);
+
 // Launches of at most kSplitMaxRows rows per chunk run as ONE cooperative kernel (gate/up tiles,
 // grid barrier, down tiles) unless `fused` is false or a mid_event is wanted; mid_event
 // (optional) is recorded between the gate/up and the down launch of the two-launch path.

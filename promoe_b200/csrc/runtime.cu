@@ -84,7 +84,8 @@ int enqueue_copy(pm_ctx* c, const Action& a) {
 int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
   const int E = c->cfg.num_expert;
   const int max_inter = std::max(w.inter, w.shared_inter);
-  if (T <= c->ws_tokens && w.hidden <= c->ws_hidden && max_inter <= c->ws_inter && w.top_k <= c->ws_topk)
+  if (T <= c->ws_tokens && w.hidden <= c->ws_hidden && max_inter <= c->ws_inter && w.top_k <= c->ws_topk &&
+      w.inter <= c->ws_inter_routed && w.shared_inter <= c->ws_inter_shared)
     return PM_OK;
   if (c->have_last_stream) PM_CUDA(cudaStreamSynchronize(c->last_stream));
   if (c->ws_dev) PM_CUDA(cudaFree(c->ws_dev));
@@ -115,6 +116,9 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
   size_t o_h = take(rows * I * 2), o_y = take(rows * H * 4), o_desc = take(c->plan_cap);
   size_t o_sc = take((size_t)c->cfg.num_layer * E * 4), o_ph = take((size_t)cap * 4096 * 4);
   size_t o_x = take((size_t)cap * H * 2), o_yo = take((size_t)cap * H * 2);
+  const int Ir = std::max(w.inter, c->ws_inter_routed);
+  const int Is = std::max(w.shared_inter, c->ws_inter_shared);
+  size_t o_res = take(ResidentPlanArgs::blob_bytes(E, Ir, Is, H, &c->res_off_desc, &c->res_off_gu, &c->res_off_dn));
   PM_CUDA(cudaMalloc(&c->ws_dev, off));
   PM_CUDA(cudaMemset(c->ws_dev, 0, off));
   c->ws_bytes = off;
@@ -135,6 +139,9 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
   c->d_pred_hidden = (float*)(b + o_ph);
   c->d_xin = (__nv_bfloat16*)(b + o_x);
   c->d_yout = (__nv_bfloat16*)(b + o_yo);
+  c->d_res_plan = b + o_res;
+  c->ws_inter_routed = Ir;
+  c->ws_inter_shared = Is;
   // pinned staging: [counts+offsets | scores | routing ids | routing weights | descriptors]
   c->h_stage_bytes = align_up((size_t)(2 * E + 1) * 4, 256) + align_up((size_t)c->cfg.num_layer * E * 4, 256) +
                      2 * align_up(R * 4, 256) + align_up(c->plan_cap, 256) +
@@ -358,6 +365,8 @@ int rt_build_slab(pm_ctx* c) {
   c->seg_events.resize(64);
   for (auto& e : c->seg_events) PM_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   PM_CUDA(cudaEventCreateWithFlags(&c->sync_event, cudaEventDisableTiming));
+  PM_CUDA(cudaEventCreateWithFlags(&c->routed_event, cudaEventDisableTiming));
+  PM_CUDA(cudaStreamCreateWithFlags(&c->readback_stream, cudaStreamNonBlocking));
   for (auto& l : c->layers) {
     PM_CUDA(cudaMalloc((void**)&l.slot_table_dev, (size_t)c->cfg.num_expert * 4));
     PM_CUDA(cudaMemset(l.slot_table_dev, 0xff, (size_t)c->cfg.num_expert * 4));
@@ -478,15 +487,77 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
   if (c->cfg.predict_from_moe_input && c->seq_len == 1) {
     rc = launch_predictors(c, layer, x, T, H, s, &pred_dsts);
     if (rc != PM_OK) return rc;
-    if (!pred_dsts.empty())
-      PM_CUDA(cudaMemcpyAsync(st.scores, c->d_scores, (size_t)c->cfg.num_layer * E * 4, cudaMemcpyDeviceToHost, s));
   }
-  PM_CUDA(cudaMemcpyAsync(st.counts, c->d_counts, (size_t)(2 * E + 1) * 4, cudaMemcpyDeviceToHost, s));
+  // The router's results travel to the host on a side stream, so the resident experts can start on
+  // the compute stream at once instead of waiting for the host's decisions about the misses.
+  PM_CUDA(cudaEventRecord(c->routed_event, s));
+  cudaStream_t rb = c->readback_stream;
+  PM_CUDA(cudaStreamWaitEvent(rb, c->routed_event, 0));
+  if (!pred_dsts.empty())
+    PM_CUDA(cudaMemcpyAsync(st.scores, c->d_scores, (size_t)c->cfg.num_layer * E * 4, cudaMemcpyDeviceToHost, rb));
+  PM_CUDA(cudaMemcpyAsync(st.counts, c->d_counts, (size_t)(2 * E + 1) * 4, cudaMemcpyDeviceToHost, rb));
   if (c->keep_routing) {
-    PM_CUDA(cudaMemcpyAsync(st.ids, c->d_topk_ids, (size_t)R * 4, cudaMemcpyDeviceToHost, s));
-    PM_CUDA(cudaMemcpyAsync(st.w, c->d_topk_w, (size_t)R * 4, cudaMemcpyDeviceToHost, s));
+    PM_CUDA(cudaMemcpyAsync(st.ids, c->d_topk_ids, (size_t)R * 4, cudaMemcpyDeviceToHost, rb));
+    PM_CUDA(cudaMemcpyAsync(st.w, c->d_topk_w, (size_t)R * 4, cudaMemcpyDeviceToHost, rb));
   }
-  PM_CUDA(cudaEventRecord(c->sync_event, s));
+  PM_CUDA(cudaEventRecord(c->sync_event, rb));
+
+  // Experts resident right now (the device slot table shows the same state).
+  std::vector<int> resident_line(E, -1);
+  const bool spec = c->device_plan && c->fused_ffn && !w.quant4 && resident_ffn_available(T);
+  pm_ctx::FfnSample spec_sample{};
+  if (spec) {
+    for (int e = 0; e < E; ++e) {
+      const int line = c->eng->expert(layer, e).line;
+      resident_line[e] = line;
+      if (line < 0) continue;
+      if (c->line_pending[line] || (c->line_waiter[line] != nullptr && c->line_waiter[line] != s)) {
+        PM_CUDA(cudaStreamWaitEvent(s, c->line_ready[line], 0));  // a prefetch into the line may be in flight
+        c->line_pending[line] = 0;
+        c->line_waiter[line] = s;
+      }
+    }
+    ResidentPlanArgs a{};
+    const Pool& pool = c->eng->pools()[c->eng->pool_index(layer)];
+    a.pool_base = line_ptr(c, pool.base);
+    a.line_stride = c->line_stride;
+    a.off_gate = c->param_offset[c->role_gate];
+    a.off_up = c->param_offset[c->role_up];
+    a.off_down = c->param_offset[c->role_down];
+    a.shared_w_gate = w.shared_w_gate;
+    a.shared_w_up = w.shared_w_up;
+    a.shared_w_down = w.shared_w_down;
+    a.num_expert = E;
+    a.inter = w.inter;
+    a.shared_inter = w.shared_inter;
+    a.hidden = H;
+    a.tokens = T;
+    a.n_routed_rows = R;
+    a.off_desc = c->res_off_desc;
+    a.off_tile_gu = c->res_off_gu;
+    a.off_tile_dn = c->res_off_dn;
+    if (c->profile_ffn) {
+      auto take_event = [&](cudaEvent_t* e) -> cudaError_t {
+        if (!c->ffn_event_pool.empty()) {
+          *e = c->ffn_event_pool.back();
+          c->ffn_event_pool.pop_back();
+          return cudaSuccess;
+        }
+        return cudaEventCreate(e);
+      };
+      spec_sample.fused = true;
+      PM_CUDA(take_event(&spec_sample.e0));
+      PM_CUDA(take_event(&spec_sample.e2));
+    }
+    PM_CUDA(launch_resident_ffn(c->d_counts, c->d_offsets, ly.slot_table_dev, a, c->d_res_plan, T, x, c->d_row_token,
+                                c->d_hbuf, c->ws_inter, c->d_yexp, s, c->profile_ffn ? spec_sample.e0 : nullptr));
+    if (c->profile_ffn) PM_CUDA(cudaEventRecord(spec_sample.e2, s));
+    c->kernel_launches += 2;
+    cudaEvent_t ev = next_seg_event(c);
+    PM_CUDA(cudaEventRecord(ev, s));
+    for (int e = 0; e < E; ++e)
+      if (resident_line[e] >= 0) c->line_read[resident_line[e]] = ev;
+  }
   rc = wait_event(c->sync_event, 30.0);
   if (rc != PM_OK) return rc;
 
@@ -535,9 +606,19 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
     return g;
   };
 
+  if (spec && c->profile_ffn) {  // weight bytes the device-planned launch read: shared + activated residents
+    const int64_t routed = (int64_t)w.inter * H * 2, sh = (int64_t)w.shared_inter * H * 2;
+    int64_t n_res = 0;
+    for (int e = 0; e < E; ++e)
+      if (counts[e] > 0 && resident_line[e] >= 0) ++n_res;
+    spec_sample.bytes_gu = 2 * (n_res * routed + sh);
+    spec_sample.bytes_dn = n_res * routed + sh;
+    c->ffn_samples.push_back(spec_sample);
+  }
+
   Segment seg;
   size_t desc_used = 0;
-  if (n_shared) {
+  if (n_shared && !spec) {
     pm_ffn_group g{};
     g.w_gate = w.shared_w_gate;
     g.w_up = w.shared_w_up;
@@ -556,6 +637,8 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
       rc = enqueue_copy(c, a);
       if (rc != PM_OK) return rc;
     } else {
+      // Already computed by the device-planned launch from the line it occupied at that time.
+      if (spec && resident_line[a.expert] >= 0) continue;
       const bool must_wait = c->line_pending[a.line] || (c->line_waiter[a.line] != nullptr && c->line_waiter[a.line] != s);
       if (must_wait && seg.waits.empty() && !seg.empty()) {
         // let everything that is already resident run while the copies are in flight
@@ -637,6 +720,11 @@ pm_ctx::~pm_ctx() {
   for (auto e : line_ready) cudaEventDestroy(e);
   for (auto e : seg_events) cudaEventDestroy(e);
   if (sync_event) cudaEventDestroy(sync_event);
+  if (routed_event) cudaEventDestroy(routed_event);
+  if (readback_stream) {
+    cudaStreamSynchronize(readback_stream);
+    cudaStreamDestroy(readback_stream);
+  }
   for (auto& f : ffn_samples) {
     cudaEventDestroy(f.e0);
     if (f.e1) cudaEventDestroy(f.e1);

@@ -54,6 +54,11 @@ struct pm_ctx {
   std::vector<cudaEvent_t> seg_events;    // ring of read events
   size_t seg_next = 0;
   cudaEvent_t sync_event = nullptr;
+  cudaStream_t readback_stream = nullptr;  // carries the router's counts to the host beside the FFN
+  cudaEvent_t routed_event = nullptr;      // router + permute done on the compute stream
+  bool device_plan = true;                 // plan and launch the resident experts without a host round trip
+  unsigned char* d_res_plan = nullptr;     // device blob of that plan
+  size_t res_off_desc = 0, res_off_gu = 0, res_off_dn = 0;
 
   // ---- per-layer model weights ----------------------------------------------------------
   struct Layer {
@@ -74,7 +79,7 @@ struct pm_ctx {
 
   // ---- forward workspace ------------------------------------------------------------------
   int ws_tokens = 0;  // capacity in tokens
-  int ws_hidden = 0, ws_inter = 0, ws_topk = 0;
+  int ws_hidden = 0, ws_inter = 0, ws_topk = 0, ws_inter_routed = 0, ws_inter_shared = 0;
   unsigned char* ws_dev = nullptr;
   size_t ws_bytes = 0;
   int32_t *d_topk_ids = nullptr, *d_topk_slot = nullptr, *d_counts = nullptr, *d_offsets = nullptr;

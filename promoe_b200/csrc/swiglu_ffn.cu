@@ -356,9 +356,13 @@ grouped_ffn_fused_kernel(const GroupDesc* __restrict__ groups, const int32_t* __
                          const int32_t* __restrict__ tile_dn, int tiles_gu, int tiles_dn, int* counters,
                          const __nv_bfloat16* __restrict__ x, int hidden,
                          const int32_t* __restrict__ row_token, __nv_bfloat16* hbuf, int ld_h,
-                         float* __restrict__ yexp) {
+                         float* __restrict__ yexp, const int32_t* __restrict__ dev_tiles) {
   __shared__ float red[kSplitWarps][2 * NT * 4][32];
   __shared__ int s_tile;
+  if (dev_tiles != nullptr) {  // plan built on the device: the tile counts live there too
+    tiles_gu = dev_tiles[0];
+    tiles_dn = dev_tiles[1];
+  }
   pull_tiles<NT, true, DEPTH>(groups, tile_gu, tiles_gu, counters, x, hidden, row_token, hidden, hbuf, ld_h, yexp,
                               red, &s_tile);
   __threadfence();
@@ -391,12 +395,14 @@ int fused_grid_size() {
 template <int NT, int DEPTH>
 cudaError_t launch_fused(const GroupDesc* groups, const int32_t* t_gu, const int32_t* t_dn, int tiles_gu,
                          int tiles_dn, int* counters, const __nv_bfloat16* x, int hidden,
-                         const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s) {
+                         const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s,
+                         const int32_t* dev_tiles = nullptr) {
   int grid = fused_grid_size<NT, DEPTH>();
   if (grid <= 0) return cudaErrorNotSupported;
-  grid = min(grid, max(tiles_gu, tiles_dn));
+  if (dev_tiles == nullptr) grid = min(grid, max(tiles_gu, tiles_dn));
   void* args[] = {(void*)&groups, (void*)&t_gu, (void*)&t_dn, (void*)&tiles_gu, (void*)&tiles_dn, (void*)&counters,
-                  (void*)&x, (void*)&hidden, (void*)&row_token, (void*)&hbuf, (void*)&ld_h, (void*)&yexp};
+                  (void*)&x, (void*)&hidden, (void*)&row_token, (void*)&hbuf, (void*)&ld_h, (void*)&yexp,
+                  (void*)&dev_tiles};
   return cudaLaunchCooperativeKernel((const void*)grouped_ffn_fused_kernel<NT, DEPTH>, dim3(grid), dim3(kSplitThreads),
                                      args, 0, s);
 }
@@ -447,6 +453,83 @@ cudaError_t dispatch_nt(int max_rows, const GroupDesc* groups, const int32_t* ti
 }
 
 }  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// Device-side planner for the experts that are already resident. It turns the router's per-expert
+// row counts and the layer's expert -> slot table into a launch plan (descriptors, tile tables,
+// zeroed counters) without a host round trip, so the fused kernel for the resident experts and
+// the shared expert can be enqueued right behind the router while the host is still reading the
+// counts back to decide about the misses.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+plan_resident_kernel(const int32_t* __restrict__ counts, const int32_t* __restrict__ offsets,
+                     const int32_t* __restrict__ slot_table, ResidentPlanArgs a, unsigned char* blob) {
+  __shared__ int s_n, s_tg, s_td;
+  GroupDesc* desc = reinterpret_cast<GroupDesc*>(blob + a.off_desc);
+  int32_t* t_gu = reinterpret_cast<int32_t*>(blob + a.off_tile_gu);
+  int32_t* t_dn = reinterpret_cast<int32_t*>(blob + a.off_tile_dn);
+  int32_t* header = reinterpret_cast<int32_t*>(blob);  // [tiles_gu, tiles_dn, counter_gu, counter_dn, n_desc]
+  if (threadIdx.x == 0) {
+    int n = 0, tg = 0, td = 0;
+    const int dn_tiles = a.hidden / kSplitTileDn;
+    if (a.shared_inter > 0) {  // heaviest tiles first
+      GroupDesc d{};
+      d.w_gate = a.shared_w_gate; d.w_up = a.shared_w_up; d.w_down = a.shared_w_down;
+      d.row_start = a.n_routed_rows; d.row_count = a.tokens; d.inter = a.shared_inter;
+      d.tile_start_gu = tg; d.tile_start_dn = td;
+      desc[n++] = d;
+      tg += a.shared_inter / kSplitTileGu;
+      td += dn_tiles;
+    }
+    for (int e = 0; e < a.num_expert; ++e) {
+      const int slot = slot_table[e];
+      if (counts[e] <= 0 || slot < 0) continue;
+      const unsigned char* line = a.pool_base + (size_t)slot * a.line_stride;
+      GroupDesc d{};
+      d.w_gate = line + a.off_gate; d.w_up = line + a.off_up; d.w_down = line + a.off_down;
+      d.row_start = offsets[e]; d.row_count = counts[e]; d.inter = a.inter;
+      d.tile_start_gu = tg; d.tile_start_dn = td;
+      desc[n++] = d;
+      tg += a.inter / kSplitTileGu;
+      td += dn_tiles;
+    }
+    s_n = n; s_tg = tg; s_td = td;
+    header[0] = tg; header[1] = td; header[2] = 0; header[3] = 0; header[4] = n;
+  }
+  __syncthreads();
+  for (int d = 0; d < s_n; ++d) {
+    const int g0 = desc[d].tile_start_gu, g1 = (d + 1 < s_n) ? desc[d + 1].tile_start_gu : s_tg;
+    const int d0 = desc[d].tile_start_dn, d1 = (d + 1 < s_n) ? desc[d + 1].tile_start_dn : s_td;
+    for (int t = g0 + threadIdx.x; t < g1; t += blockDim.x) t_gu[t] = d;
+    for (int t = d0 + threadIdx.x; t < d1; t += blockDim.x) t_dn[t] = d;
+  }
+}
+
+cudaError_t launch_resident_ffn(const int32_t* counts, const int32_t* offsets, const int32_t* slot_table,
+                                const ResidentPlanArgs& a, unsigned char* blob_dev, int max_rows,
+                                const __nv_bfloat16* x, const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h,
+                                float* yexp, cudaStream_t s, cudaEvent_t start_event) {
+  if (max_rows > kSplitMaxRows) return cudaErrorNotSupported;
+  plan_resident_kernel<<<1, 256, 0, s>>>(counts, offsets, slot_table, a, blob_dev);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  if (start_event != nullptr) {
+    e = cudaEventRecord(start_event, s);
+    if (e != cudaSuccess) return e;
+  }
+  const GroupDesc* groups = reinterpret_cast<const GroupDesc*>(blob_dev + a.off_desc);
+  const int32_t* t_gu = reinterpret_cast<const int32_t*>(blob_dev + a.off_tile_gu);
+  const int32_t* t_dn = reinterpret_cast<const int32_t*>(blob_dev + a.off_tile_dn);
+  int32_t* header = reinterpret_cast<int32_t*>(blob_dev);
+  if (max_rows <= 8)
+    return launch_fused<1, 4>(groups, t_gu, t_dn, 0, 0, header + 2, x, a.hidden, row_token, hbuf, ld_h, yexp, s, header);
+  return launch_fused<2, 2>(groups, t_gu, t_dn, 0, 0, header + 2, x, a.hidden, row_token, hbuf, ld_h, yexp, s, header);
+}
+
+bool resident_ffn_available(int max_rows) {
+  if (max_rows > kSplitMaxRows) return false;
+  return (max_rows <= 8 ? fused_grid_size<1, 4>() : fused_grid_size<2, 2>()) > 0;
+}
 
 cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& info, int quant4,
                               const __nv_bfloat16* x, int H, const int32_t* row_token,
