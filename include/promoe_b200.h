@@ -166,6 +166,14 @@ int pm_layer_set_weights(pm_ctx* ctx, int layer, const pm_layer_weights* w);
  * (src/sparse_llm_cache/utils/__init__.py:82-89) plus the ExpertHook / MoeLayerHook calls
  * around it (src/sparse_llm_cache/utils/hooks.py:187-223). */
 int pm_moe_forward(pm_ctx* ctx, int layer, const void* x_dev, int T, void* y_dev, void* stream);
+/* Expert-parallel receive side: the rows were routed elsewhere. x_rows [n_rows, hidden] bf16 and
+ * row_expert [n_rows] int32 (expert ids local to this context) are device buffers; rows_out
+ * [n_rows, hidden] f32 receives each row's unweighted expert output, in row order. Cache
+ * bookkeeping, copies and the grouped FFN are those of pm_moe_forward; there is no router, no
+ * shared expert and no combine (gate_w of the layer may be NULL). No counterpart in the
+ * reference, which is single-GPU (src/cpp_worker/model_loader.cpp:75-79). */
+int pm_moe_forward_routed(pm_ctx* ctx, int layer, const void* x_rows, int n_rows, const int32_t* row_expert,
+                          float* rows_out, void* stream);
 /* Same with host buffers (pinned or pageable): copies x in and y out on the stream and waits. */
 int pm_moe_forward_host(pm_ctx* ctx, int layer, const void* x_host, int T, void* y_host, void* stream);
 /* Routing of the most recent pm_moe_forward on `layer` (host copies): ids/weights [T, k]. */
@@ -189,6 +197,11 @@ int pm_k_gate_topk(const void* x, const void* gate_w, const float* gate_bias, co
                    float* shared_scale, float* logits_out, void* stream);
 int pm_k_permute(const int32_t* topk_ids, int R, int k, int E, int32_t* counts, int32_t* offsets,
                  int32_t* row_token, int32_t* pos, int32_t* err_flag, void* stream);
+
+/* dst row r = src row row_index[r]; rows are row_bytes long (a multiple of 16). Used to lay token
+ * rows out per expert (dispatch) and to put expert outputs back in arrival order. */
+int pm_k_gather_rows(const void* src, const int32_t* row_index, int n_rows, size_t row_bytes, void* dst,
+                     void* stream);
 
 /* One group of rows sharing one set of FFN weights (device pointers). */
 typedef struct pm_ffn_group {

@@ -86,12 +86,14 @@ SIGNATURES = {
     "pm_profile_read": (_i, [_vp, C.POINTER(pm_profile), _i]),
     "pm_layer_set_weights": (_i, [_vp, _i, C.POINTER(pm_layer_weights)]),
     "pm_moe_forward": (_i, [_vp, _i, _vp, _i, _vp, _vp]),
+    "pm_moe_forward_routed": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
     "pm_moe_forward_host": (_i, [_vp, _i, _vp, _i, _vp, _vp]),
     "pm_last_routing": (_i, [_vp, _i, C.POINTER(C.c_int32), C.POINTER(_f), _i]),
     "pm_predictor_set": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp]),
     "pm_report_hidden": (_i, [_vp, _i, _vp, _i, _i, _vp]),
     "pm_k_gate_topk": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "pm_k_permute": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "pm_k_gather_rows": (_i, [_vp, _vp, _i, _sz, _vp, _vp]),
     "pm_k_swiglu_ffn_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "pm_k_swiglu_ffn": (_i, [C.POINTER(pm_ffn_group), _i, _i, _vp, _i, _vp, _i, _vp, _vp, _sz, _vp]),
     "pm_k_swiglu_ffn_static_capacity": (_sz, []),

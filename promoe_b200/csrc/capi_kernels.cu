@@ -116,6 +116,15 @@ int pm_k_permute(const int32_t* topk_ids, int R, int k, int E, int32_t* counts, 
   return PM_OK;
 }
 
+int pm_k_gather_rows(const void* src, const int32_t* row_index, int n_rows, size_t row_bytes, void* dst,
+                     void* stream) {
+  if (n_rows < 0 || row_bytes == 0 || row_bytes % 16 != 0) return fail(PM_ERR_INVALID, "gather_rows: row_bytes must be a positive multiple of 16");
+  if (n_rows == 0) return PM_OK;
+  if (!src || !row_index || !dst) return fail(PM_ERR_INVALID, "gather_rows: null pointer");
+  PM_CUDA(launch_gather_rows(src, row_index, n_rows, row_bytes, dst, (cudaStream_t)stream));
+  return PM_OK;
+}
+
 size_t pm_k_swiglu_ffn_scratch_bytes(int n_groups, int n_rows, int max_inter, int hidden) {
   if (n_groups < 0 || n_rows < 0 || max_inter < 0 || hidden < 0) return 0;
   // worst case: every group split into chunks of kMaxChunkRows rows, smallest tiles

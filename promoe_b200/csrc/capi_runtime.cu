@@ -328,7 +328,6 @@ int pm_profile_read(pm_ctx* ctx, pm_profile* out, int reset) {
 int pm_layer_set_weights(pm_ctx* ctx, int layer, const pm_layer_weights* w) {
   if (need(ctx)) return PM_ERR_INVALID;
   if (!w || layer < 0 || layer >= ctx->cfg.num_layer) return fail(PM_ERR_INVALID, "layer out of range");
-  if (!w->gate_w) return fail(PM_ERR_INVALID, "gate weights missing");
   if (w->hidden <= 0 || w->hidden % 64 != 0) return fail(PM_ERR_INVALID, "hidden must be a positive multiple of 64");
   if (w->inter <= 0 || w->inter % 32 != 0) return fail(PM_ERR_INVALID, "inter must be a positive multiple of 32");
   if (w->shared_inter < 0 || w->shared_inter % 32 != 0) return fail(PM_ERR_INVALID, "shared_inter must be a multiple of 32");
@@ -345,6 +344,15 @@ int pm_layer_set_weights(pm_ctx* ctx, int layer, const pm_layer_weights* w) {
 int pm_moe_forward(pm_ctx* ctx, int layer, const void* x_dev, int T, void* y_dev, void* stream) {
   if (need(ctx)) return PM_ERR_INVALID;
   return rt_forward(ctx, layer, x_dev, T, y_dev, (cudaStream_t)stream);
+}
+
+int pm_moe_forward_routed(pm_ctx* ctx, int layer, const void* x_rows, int n_rows, const int32_t* row_expert,
+                          float* rows_out, void* stream) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  RoutedRows r;
+  r.row_expert = row_expert;
+  r.rows_out = rows_out;
+  return rt_forward(ctx, layer, x_rows, n_rows, nullptr, (cudaStream_t)stream, &r);
 }
 
 int pm_moe_forward_host(pm_ctx* ctx, int layer, const void* x_host, int T, void* y_host, void* stream) {

@@ -69,7 +69,26 @@ permute_kernel(const int32_t* __restrict__ topk_ids, int R, int k, int E, int32_
   }
 }
 
+// dst row r = src row index[r]; rows are row_vec 16-byte vectors long.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ index, int n_rows, int row_vec,
+                   uint4* __restrict__ dst) {
+  for (int r = blockIdx.x; r < n_rows; r += gridDim.x) {
+    const uint4* s = src + (size_t)index[r] * row_vec;
+    uint4* d = dst + (size_t)r * row_vec;
+    for (int v = threadIdx.x; v < row_vec; v += blockDim.x) d[v] = s[v];
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst,
+                               cudaStream_t s) {
+  if (n_rows <= 0) return cudaSuccess;
+  const int grid = n_rows < 1184 ? n_rows : 1184;  // 8 x 148 SMs
+  gather_rows_kernel<<<grid, 256, 0, s>>>((const uint4*)src, index, n_rows, (int)(row_bytes / 16), (uint4*)dst);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_permute(const int32_t* topk_ids, int R, int k, int E, int32_t* counts,
                            int32_t* offsets, int32_t* row_token, int32_t* pos, int32_t* err_flag,

@@ -116,6 +116,9 @@ cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& 
                               __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s,
                               cudaEvent_t mid_event = nullptr, bool fused = true);
 
+cudaError_t launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst,
+                               cudaStream_t s);
+
 cudaError_t launch_combine(const float* yexp, const int32_t* pos, const float* topk_w, int T, int H,
                            int k, int R, int n_shared, const float* shared_scale,
                            __nv_bfloat16* y, cudaStream_t s);

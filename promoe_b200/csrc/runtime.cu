@@ -451,18 +451,20 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
 
 }  // namespace
 
-int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream_t s) {
+int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream_t s, const RoutedRows* routed) {
   if (!c->slab_built) return fail(PM_ERR_STATE, "moe_forward before build_slab");
   if (layer < 0 || layer >= c->cfg.num_layer) return fail(PM_ERR_INVALID, "layer out of range");
   pm_ctx::Layer& ly = c->layers[layer];
   if (!ly.set) return fail(PM_ERR_STATE, "moe_forward before layer_set_weights");
   if (T < 0) return fail(PM_ERR_INVALID, "negative token count");
   if (T == 0) return PM_OK;
-  if (!xv || !yv) return fail(PM_ERR_INVALID, "null activation pointer");
+  if (!xv || (!yv && !routed)) return fail(PM_ERR_INVALID, "null activation pointer");
+  if (routed && (!routed->row_expert || !routed->rows_out)) return fail(PM_ERR_INVALID, "null routed-row pointer");
   const pm_layer_weights& w = ly.w;
-  const int E = c->cfg.num_expert, k = w.top_k, H = w.hidden, N = c->cfg.num_per_expert_param();
+  if (!routed && w.gate_w == nullptr) return fail(PM_ERR_STATE, "this layer has no router weights (routed rows only)");
+  const int E = c->cfg.num_expert, k = routed ? 1 : w.top_k, H = w.hidden, N = c->cfg.num_per_expert_param();
   const int R = T * k;
-  const int n_shared = w.shared_inter > 0 ? 1 : 0;
+  const int n_shared = (!routed && w.shared_inter > 0) ? 1 : 0;
   int rc = ensure_workspace(c, T, w);
   if (rc != PM_OK) return rc;
   if (c->have_last_stream && c->last_stream != s) PM_CUDA(cudaStreamSynchronize(c->last_stream));
@@ -477,14 +479,20 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
     PM_CUDA(cudaMemcpyAsync(ly.slot_table_dev, st.slot_table, (size_t)E * 4, cudaMemcpyHostToDevice, s));
     ly.slot_table_dirty = false;
   }
-  PM_CUDA(launch_gate_topk(x, (const __nv_bfloat16*)w.gate_w, w.gate_bias, (const __nv_bfloat16*)w.shared_gate_w,
-                           T, H, E, k, w.norm_topk, w.routed_scale, ly.slot_table_dev, c->d_topk_ids,
-                           c->d_topk_w, c->d_topk_slot, c->d_shared_scale, nullptr, s));
-  PM_CUDA(launch_permute(c->d_topk_ids, R, k, E, c->d_counts, c->d_offsets, c->d_row_token, c->d_pos, c->d_err,
+  const int32_t* ids_dev = c->d_topk_ids;
+  if (routed) {
+    ids_dev = routed->row_expert;
+  } else {
+    PM_CUDA(launch_gate_topk(x, (const __nv_bfloat16*)w.gate_w, w.gate_bias, (const __nv_bfloat16*)w.shared_gate_w,
+                             T, H, E, k, w.norm_topk, w.routed_scale, ly.slot_table_dev, c->d_topk_ids,
+                             c->d_topk_w, c->d_topk_slot, c->d_shared_scale, nullptr, s));
+    c->kernel_launches += 1;
+  }
+  PM_CUDA(launch_permute(ids_dev, R, k, E, c->d_counts, c->d_offsets, c->d_row_token, c->d_pos, c->d_err,
                          n_shared * T, T, s));
-  c->kernel_launches += 2;
+  c->kernel_launches += 1;
   std::vector<int> pred_dsts;
-  if (c->cfg.predict_from_moe_input && c->seq_len == 1) {
+  if (!routed && c->cfg.predict_from_moe_input && c->seq_len == 1) {
     rc = launch_predictors(c, layer, x, T, H, s, &pred_dsts);
     if (rc != PM_OK) return rc;
   }
@@ -496,7 +504,8 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
   if (!pred_dsts.empty())
     PM_CUDA(cudaMemcpyAsync(st.scores, c->d_scores, (size_t)c->cfg.num_layer * E * 4, cudaMemcpyDeviceToHost, rb));
   PM_CUDA(cudaMemcpyAsync(st.counts, c->d_counts, (size_t)(2 * E + 1) * 4, cudaMemcpyDeviceToHost, rb));
-  if (c->keep_routing) {
+  const bool keep = c->keep_routing && !routed;
+  if (keep) {
     PM_CUDA(cudaMemcpyAsync(st.ids, c->d_topk_ids, (size_t)R * 4, cudaMemcpyDeviceToHost, rb));
     PM_CUDA(cudaMemcpyAsync(st.w, c->d_topk_w, (size_t)R * 4, cudaMemcpyDeviceToHost, rb));
   }
@@ -504,7 +513,7 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
 
   // Experts resident right now (the device slot table shows the same state).
   std::vector<int> resident_line(E, -1);
-  const bool spec = c->device_plan && c->fused_ffn && !w.quant4 && resident_ffn_available(T);
+  const bool spec = c->device_plan && c->fused_ffn && !w.quant4 && resident_ffn_available(T);  // rows per expert <= T
   pm_ctx::FfnSample spec_sample{};
   if (spec) {
     for (int e = 0; e < E; ++e) {
@@ -561,7 +570,7 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
   rc = wait_event(c->sync_event, 30.0);
   if (rc != PM_OK) return rc;
 
-  if (c->keep_routing) {
+  if (keep) {
     c->last_ids[layer].assign(st.ids, st.ids + R);
     c->last_w[layer].assign(st.w, st.w + R);
   }
@@ -653,8 +662,12 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
   rc = flush_segment(c, &seg, w, x, R + n_shared * T, &desc_used, s);
   if (rc != PM_OK) return rc;
 
-  PM_CUDA(launch_combine(c->d_yexp, c->d_pos, c->d_topk_w, T, H, k, R, n_shared,
-                         w.shared_gate_w ? c->d_shared_scale : nullptr, (__nv_bfloat16*)yv, s));
+  if (routed) {
+    PM_CUDA(launch_gather_rows(c->d_yexp, c->d_pos, T, (size_t)H * 4, routed->rows_out, s));
+  } else {
+    PM_CUDA(launch_combine(c->d_yexp, c->d_pos, c->d_topk_w, T, H, k, R, n_shared,
+                           w.shared_gate_w ? c->d_shared_scale : nullptr, (__nv_bfloat16*)yv, s));
+  }
   c->kernel_launches += 1;
   for (int64_t id : ids) c->eng->expert_done(layer, (int)id);
   c->eng->layer_done(layer);

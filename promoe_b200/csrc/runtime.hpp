@@ -120,7 +120,14 @@ namespace pm {
 int rt_pin_all(pm_ctx* c);
 int rt_build_slab(pm_ctx* c);
 int rt_execute_copies(pm_ctx* c, const std::vector<Action>& actions);
-int rt_forward(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStream_t s);
+// routed: the caller supplies one local expert id per row (row_expert, device int32 [T]); there is
+// no router, no shared expert and no weighted combine, and rows_out (device f32 [T, hidden])
+// receives every row's expert output in row order. Used by the expert-parallel receive side.
+struct RoutedRows {
+  const int32_t* row_expert = nullptr;
+  float* rows_out = nullptr;
+};
+int rt_forward(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStream_t s, const RoutedRows* routed = nullptr);
 int rt_forward_host(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStream_t s);
 int rt_report_hidden(pm_ctx* c, int index, const void* hidden, int B, int seq, cudaStream_t s);
 void rt_mark_dirty(pm_ctx* c, const std::vector<Action>& actions);

@@ -176,11 +176,13 @@ class ExpertCache:
         return {name: getattr(p, name) for name, _ in p._fields_}
 
     # ------------------------------------------------------------------ fused layer
-    def set_layer_weights(self, layer: int, gate_w: torch.Tensor, inter: int, top_k: int, norm_topk: bool,
+    def set_layer_weights(self, layer: int, gate_w: torch.Tensor | None, inter: int, top_k: int, norm_topk: bool,
                           routed_scale: float = 1.0, gate_bias: torch.Tensor | None = None,
                           shared: Sequence[torch.Tensor] | None = None,
-                          shared_gate_w: torch.Tensor | None = None, quant4: bool = False) -> None:
-        """gate_w [E, H] bf16 on the device; shared = (w_gate [Is, H], w_up [Is, H], w_down [H, Is])."""
+                          shared_gate_w: torch.Tensor | None = None, quant4: bool = False,
+                          hidden: int | None = None) -> None:
+        """gate_w [E, H] bf16 on the device; shared = (w_gate [Is, H], w_up [Is, H], w_down [H, Is]).
+        gate_w may be None (then pass `hidden`) for a context that only serves pm_moe_forward_routed."""
         def dev(t, dtype):
             if t is None:
                 return None
@@ -192,7 +194,7 @@ class ExpertCache:
         w.gate_w = dev(gate_w, torch.bfloat16)
         w.gate_bias = dev(gate_bias, torch.float32)
         w.shared_gate_w = dev(shared_gate_w, torch.bfloat16)
-        w.hidden = gate_w.shape[1]
+        w.hidden = gate_w.shape[1] if gate_w is not None else int(hidden)
         w.inter = inter
         w.shared_inter = 0
         if shared is not None:
