@@ -138,6 +138,20 @@ class SyntheticStack:
                                          shared=self.shared[l] if cfg.shared_inter else None,
                                          shared_gate_w=self.shared_gate_w[l])
 
+    def install_routed_only(self):
+        """Expert-parallel rank: the cache serves rows routed elsewhere (no router in the context)."""
+        cfg = self.cfg
+        for l in range(self.num_layer):
+            self.cache.set_layer_weights(l, None, cfg.inter, 1, False, 1.0, hidden=cfg.hidden)
+
+    def ep_layers(self):
+        """Per-layer resident weights for promoe_b200.ep.CudaBackend (router over ALL experts)."""
+        cfg = self.cfg
+        return [dict(gate_w=self.gate_w[l], gate_bias=self.gate_bias[l],
+                     shared=self.shared[l] if cfg.shared_inter else None, shared_gate_w=self.shared_gate_w[l],
+                     top_k=cfg.top_k, norm_topk=cfg.norm_topk, routed_scale=1.0, inter=cfg.inter)
+                for l in range(self.num_layer)]
+
     def install_predictors(self):
         """Random-initialised MLPs hidden -> width -> num_expert (ReLU) for every (source, target)
         pair of the reference's default prediction window (predictor.cpp:8-46)."""
