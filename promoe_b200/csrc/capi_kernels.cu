@@ -22,11 +22,11 @@ int fail_cuda(cudaError_t e, const char* what) {
 
 // One planner for both passes: with blob == nullptr it only sizes the launch.
 static int plan_core(const pm_ffn_group* groups, int n_groups, int hidden, unsigned char* blob, size_t cap,
-                     FfnPlanInfo* info) {
+                     FfnPlanInfo* info, int chunk_rows) {
   if (hidden % 64 != 0) return fail(PM_ERR_INVALID, "hidden must be a multiple of 64");
   // The kernel variant, and with it the tile size, follows from the largest chunk of the launch.
   int largest = 0;
-  for (int i = 0; i < n_groups; ++i) largest = std::max(largest, std::min(groups[i].row_count, kMaxChunkRows));
+  for (int i = 0; i < n_groups; ++i) largest = std::max(largest, std::min(groups[i].row_count, chunk_rows));
   const bool split = largest <= kSplitMaxRows;
   const int tile_gu = split ? kSplitTileGu : kTileRows;
   const int tile_dn = split ? kSplitTileDn : kTileRows;
@@ -43,14 +43,14 @@ static int plan_core(const pm_ffn_group* groups, int n_groups, int hidden, unsig
     const pm_ffn_group& g = groups[i];
     if (g.row_count <= 0) continue;
     if (g.inter % 32 != 0 || g.inter <= 0) return fail(PM_ERR_INVALID, "inter must be a positive multiple of 32");
-    for (int r0 = 0; r0 < g.row_count; r0 += kMaxChunkRows) {
+    for (int r0 = 0; r0 < g.row_count; r0 += chunk_rows) {
       const int n_gu = (g.inter + tile_gu - 1) / tile_gu, n_dn = hidden / tile_dn;
       if (blob != nullptr) {
         GroupDesc d{};
         d.w_gate = g.w_gate; d.w_up = g.w_up; d.w_down = g.w_down;
         d.q_gate = g.q_gate; d.q_up = g.q_up; d.q_down = g.q_down;
         d.row_start = g.row_start + r0;
-        d.row_count = std::min(kMaxChunkRows, g.row_count - r0);
+        d.row_count = std::min(chunk_rows, g.row_count - r0);
         d.inter = g.inter;
         d.tile_start_gu = tg;
         d.tile_start_dn = td;
@@ -60,7 +60,7 @@ static int plan_core(const pm_ffn_group* groups, int n_groups, int hidden, unsig
       }
       tg += n_gu;
       td += n_dn;
-      mr = std::max(mr, std::min(kMaxChunkRows, g.row_count - r0));
+      mr = std::max(mr, std::min(chunk_rows, g.row_count - r0));
       mi = std::max(mi, g.inter);
       ++n;
     }
@@ -70,13 +70,13 @@ static int plan_core(const pm_ffn_group* groups, int n_groups, int hidden, unsig
   return PM_OK;
 }
 
-int plan_groups_size(const pm_ffn_group* groups, int n_groups, int hidden, FfnPlanInfo* info) {
-  return plan_core(groups, n_groups, hidden, nullptr, 0, info);
+int plan_groups_size(const pm_ffn_group* groups, int n_groups, int hidden, FfnPlanInfo* info, int chunk_rows) {
+  return plan_core(groups, n_groups, hidden, nullptr, 0, info, chunk_rows);
 }
 
 int plan_groups_into(const pm_ffn_group* groups, int n_groups, int hidden, unsigned char* blob, size_t cap,
-                     FfnPlanInfo* info) {
-  return plan_core(groups, n_groups, hidden, blob, cap, info);
+                     FfnPlanInfo* info, int chunk_rows) {
+  return plan_core(groups, n_groups, hidden, blob, cap, info, chunk_rows);
 }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -129,7 +129,7 @@ size_t pm_k_swiglu_ffn_scratch_bytes(int n_groups, int n_rows, int max_inter, in
   if (n_groups < 0 || n_rows < 0 || max_inter < 0 || hidden < 0) return 0;
   // worst case: every group split into chunks of kMaxChunkRows rows, smallest tiles
   FfnPlanInfo worst;
-  worst.n_desc = n_groups + n_rows / kMaxChunkRows + 1;
+  worst.n_desc = n_groups + n_rows / kSplitMaxRows + 1;
   worst.tiles_gu = worst.n_desc * ((max_inter + kSplitTileGu - 1) / kSplitTileGu);
   worst.tiles_dn = worst.n_desc * ((hidden + kSplitTileDn - 1) / kSplitTileDn);
   return align_up(worst.blob_bytes(), 256) + align_up((size_t)n_rows * max_inter * 2, 256);
@@ -144,15 +144,25 @@ int pm_k_swiglu_ffn(const pm_ffn_group* groups, int n_groups, int quant4, const 
   for (int i = 0; i < n_groups; ++i)
     if (groups[i].row_count > 0 && (groups[i].row_start < 0 || groups[i].row_start + groups[i].row_count > n_rows))
       return fail(PM_ERR_INVALID, "swiglu_ffn: group rows outside [0, n_rows)");
+  if (quant4) {
+    if (hidden % 128 != 0) return fail(PM_ERR_INVALID, "swiglu_ffn: uint4 experts need hidden % 128 == 0");
+    for (int i = 0; i < n_groups; ++i) {
+      if (groups[i].row_count > 0 && groups[i].inter % 128 != 0)
+        return fail(PM_ERR_INVALID, "swiglu_ffn: uint4 experts need inter % 128 == 0");
+      if (groups[i].row_count > 0 && (!groups[i].q_gate || !groups[i].q_up || !groups[i].q_down))
+        return fail(PM_ERR_INVALID, "swiglu_ffn: uint4 experts need scale/zero tensors");
+    }
+  }
+  const int chunk_rows = quant4 ? kSplitMaxRows : kMaxChunkRows;
   FfnPlanInfo info;
-  int rc = plan_groups_size(groups, n_groups, hidden, &info);
+  int rc = plan_groups_size(groups, n_groups, hidden, &info, chunk_rows);
   if (rc != PM_OK) return rc;
   if (info.n_desc == 0) return PM_OK;
   const size_t plan_bytes = align_up(info.blob_bytes(), 256);
   const size_t need = plan_bytes + align_up((size_t)n_rows * info.max_inter * 2, 256);
   if (scratch_bytes < need) return fail(PM_ERR_INVALID, "swiglu_ffn: scratch too small");
   std::vector<unsigned char> blob(info.blob_bytes());
-  rc = plan_groups_into(groups, n_groups, hidden, blob.data(), blob.size(), &info);
+  rc = plan_groups_into(groups, n_groups, hidden, blob.data(), blob.size(), &info, chunk_rows);
   if (rc != PM_OK) return rc;
   cudaStream_t s = (cudaStream_t)stream;
   // The plan upload is from pageable memory, so it is staged before this call returns.

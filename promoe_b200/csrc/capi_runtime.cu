@@ -336,6 +336,8 @@ int pm_layer_set_weights(pm_ctx* ctx, int layer, const pm_layer_weights* w) {
   if (w->top_k <= 0 || w->top_k > 16 || w->top_k > ctx->cfg.num_expert) return fail(PM_ERR_INVALID, "top_k out of range");
   if (w->quant4 && (ctx->role_qgate < 0 || ctx->role_qup < 0 || ctx->role_qdown < 0))
     return fail(PM_ERR_INVALID, "quant4 layer needs scale/zero tensors in the tensor list");
+  if (w->quant4 && (w->hidden % 128 != 0 || w->inter % 128 != 0))
+    return fail(PM_ERR_INVALID, "quant4 layer needs hidden and inter to be multiples of 128");
   ctx->layers[layer].w = *w;
   ctx->layers[layer].set = true;
   return PM_OK;

@@ -19,23 +19,33 @@
 namespace pm {
 namespace {
 
-constexpr int kGateThreads = 256;
+constexpr int kGateThreads = 512;
 constexpr int kMaxExperts = 256;
 
 __device__ __forceinline__ float canonical_dot(const uint4* __restrict__ w, const uint4* xs, int nvec,
                                                int lane) {
   float acc = 0.f;
-  for (int v = lane; v < nvec; v += 32) {
-    uint4 wv = __ldg(w + v);
-    uint4 xv = xs[v];
-    const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
-    const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+  // Four weight vectors are fetched before any is consumed (memory-level parallelism); they are
+  // still accumulated in ascending v, so the documented summation order is unchanged.
+  for (int v0 = lane; v0 < nvec; v0 += 128) {
+    uint4 wv[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 wf = __bfloat1622float2(wp[i]);
-      float2 xf = __bfloat1622float2(xp[i]);
-      acc = __fmaf_rn(wf.x, xf.x, acc);
-      acc = __fmaf_rn(wf.y, xf.y, acc);
+    for (int u = 0; u < 4; ++u)
+      if (v0 + 32 * u < nvec) wv[u] = __ldg(w + v0 + 32 * u);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (v0 + 32 * u < nvec) {
+        uint4 xv = xs[v0 + 32 * u];
+        const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv[u]);
+        const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 wf = __bfloat1622float2(wp[i]);
+          float2 xf = __bfloat1622float2(xp[i]);
+          acc = __fmaf_rn(wf.x, xf.x, acc);
+          acc = __fmaf_rn(wf.y, xf.y, acc);
+        }
+      }
     }
   }
 #pragma unroll

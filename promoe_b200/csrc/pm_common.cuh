@@ -73,9 +73,10 @@ struct FfnPlanInfo {
 // Splits caller groups into chunks of at most kMaxChunkRows rows, assigns CTA tile ranges and
 // writes the blob into `blob` (host memory, `cap` bytes). Allocates nothing.
 int plan_groups_into(const pm_ffn_group* groups, int n_groups, int hidden, unsigned char* blob, size_t cap,
-                     FfnPlanInfo* info);
+                     FfnPlanInfo* info, int chunk_rows = kMaxChunkRows);
 // Size pass of the same planner (blob == nullptr): fills `info` only.
-int plan_groups_size(const pm_ffn_group* groups, int n_groups, int hidden, FfnPlanInfo* info);
+int plan_groups_size(const pm_ffn_group* groups, int n_groups, int hidden, FfnPlanInfo* info,
+                     int chunk_rows = kMaxChunkRows);
 
 // Everything the device-side planner needs to describe the resident experts of one layer.
 struct ResidentPlanArgs {

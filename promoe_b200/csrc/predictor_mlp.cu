@@ -34,7 +34,9 @@ __device__ __forceinline__ float dot_bf16_row(const uint4* __restrict__ w, const
   return acc;
 }
 
-// hidden[b, j] = relu(W1[j, :] . x[b, :] + b1[j]); one warp per hidden unit j.
+// hidden[b, j] = relu(W1[j, :] . x[b, :] + b1[j]); one warp per hidden unit j. The unit's weight
+// row is read once per group of 8 sequences: 8 vectors of it sit in registers while the 8 token
+// rows (L1/L2 resident) stream past.
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 predictor_fc1_kernel(const __nv_bfloat16* __restrict__ x, int B, int H,
                      const __nv_bfloat16* __restrict__ w1, const float* __restrict__ b1, int D,
@@ -44,26 +46,65 @@ predictor_fc1_kernel(const __nv_bfloat16* __restrict__ x, int B, int H,
   if (j >= D) return;
   const uint4* wrow = reinterpret_cast<const uint4*>(w1 + (size_t)j * H);
   const float bias = (b1 != nullptr) ? b1[j] : 0.f;
-  for (int b = 0; b < B; ++b) {
-    float d = dot_bf16_row(wrow, reinterpret_cast<const uint4*>(x + (size_t)b * H), H / 8, lane);
-    if (lane == 0) hidden[(size_t)b * D + j] = fmaxf(d + bias, 0.f);
+  const int nvec = H / 8;
+  for (int b0 = 0; b0 < B; b0 += 8) {
+    float acc[8];
+#pragma unroll
+    for (int bb = 0; bb < 8; ++bb) acc[bb] = 0.f;
+    for (int v0 = lane; v0 < nvec; v0 += 32 * 8) {
+      uint4 wv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (v0 + 32 * u < nvec) wv[u] = __ldg(wrow + v0 + 32 * u);
+#pragma unroll
+      for (int bb = 0; bb < 8; ++bb) {
+        if (b0 + bb >= B) break;
+        const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)(b0 + bb) * H);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (v0 + 32 * u < nvec) {
+            uint4 xv = __ldg(xrow + v0 + 32 * u);
+            const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv[u]);
+            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float2 wf = __bfloat1622float2(wp[i]);
+              float2 xf = __bfloat1622float2(xp[i]);
+              acc[bb] = fmaf(wf.x, xf.x, acc[bb]);
+              acc[bb] = fmaf(wf.y, xf.y, acc[bb]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int bb = 0; bb < 8; ++bb) {
+      float d = acc[bb];
+#pragma unroll
+      for (int m = 16; m >= 1; m >>= 1) d += __shfl_xor_sync(0xffffffffu, d, m);
+      if (lane == 0 && b0 + bb < B) hidden[(size_t)(b0 + bb) * D + j] = fmaxf(d + bias, 0.f);
+    }
   }
 }
 
-// scores[e] = sum_b sum_j W2[e, j] * hidden[b, j] + B * b2[e]; one warp per expert.
+// scores[e] = sum_b sum_j W2[e, j] * hidden[b, j] + B * b2[e]. Every CTA first sums the hidden
+// activations over the batch into shared memory, then one warp per expert takes the dot product.
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 predictor_fc2_kernel(const float* __restrict__ hidden, int B, int D,
                      const __nv_bfloat16* __restrict__ w2, const float* __restrict__ b2, int E,
                      float* __restrict__ scores) {
+  extern __shared__ float hsum[];  // [D]
+  for (int j = threadIdx.x; j < D; j += blockDim.x) {
+    float s = 0.f;
+    for (int b = 0; b < B; ++b) s += hidden[(size_t)b * D + j];
+    hsum[j] = s;
+  }
+  __syncthreads();
   const int lane = threadIdx.x & 31;
   const int e = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
   if (e >= E) return;
   float acc = 0.f;
-  for (int j = lane; j < D; j += 32) {
-    float hs = 0.f;
-    for (int b = 0; b < B; ++b) hs += hidden[(size_t)b * D + j];
-    acc = fmaf(__bfloat162float(w2[(size_t)e * D + j]), hs, acc);
-  }
+  for (int j = lane; j < D; j += 32) acc = fmaf(__bfloat162float(w2[(size_t)e * D + j]), hsum[j], acc);
 #pragma unroll
   for (int m = 16; m >= 1; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
   if (lane == 0) scores[e] = acc + (b2 != nullptr ? (float)B * b2[e] : 0.f);
@@ -79,7 +120,7 @@ cudaError_t launch_predictor_mlp(const __nv_bfloat16* x, int B, int H, const __n
       x, B, H, w1, b1, D, hidden_scratch);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  predictor_fc2_kernel<<<(E + kWarpsPerCta - 1) / kWarpsPerCta, kWarpsPerCta * 32, 0, s>>>(
+  predictor_fc2_kernel<<<(E + kWarpsPerCta - 1) / kWarpsPerCta, kWarpsPerCta * 32, (size_t)D * 4, s>>>(
       hidden_scratch, B, D, w2, b2, E, scores);
   return cudaGetLastError();
 }

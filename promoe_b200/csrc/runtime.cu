@@ -100,7 +100,7 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
     // worst case of one layer call: every expert plus the shared expert, chunks of 64 rows, smallest
     // tiles, and a few extra segments each aligned to 256 bytes
     FfnPlanInfo worst;
-    worst.n_desc = E + (int)(rows / kMaxChunkRows) + 8;
+    worst.n_desc = E + (int)(rows / kSplitMaxRows) + 8;
     worst.tiles_gu = worst.n_desc * ((I + kSplitTileGu - 1) / kSplitTileGu);
     worst.tiles_dn = worst.n_desc * ((H + kSplitTileDn - 1) / kSplitTileDn);
     c->plan_cap = align_up(worst.blob_bytes(), 256) + 64 * 256;
@@ -398,12 +398,13 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
     }
   }
   FfnPlanInfo info;
-  int rc = plan_groups_size(seg->groups.data(), (int)seg->groups.size(), w.hidden, &info);
+  const int chunk_rows = w.quant4 ? kSplitMaxRows : kMaxChunkRows;
+  int rc = plan_groups_size(seg->groups.data(), (int)seg->groups.size(), w.hidden, &info, chunk_rows);
   if (rc != PM_OK) return rc;
   if (*desc_used + info.blob_bytes() > c->plan_cap) return fail(PM_ERR_STATE, "launch plan buffer overflow");
   Stage st = stage_of(c);
   rc = plan_groups_into(seg->groups.data(), (int)seg->groups.size(), w.hidden, st.plan + *desc_used,
-                        c->plan_cap - *desc_used, &info);
+                        c->plan_cap - *desc_used, &info, chunk_rows);
   if (rc != PM_OK) return rc;
   PM_CUDA(cudaMemcpyAsync(c->d_plan + *desc_used, st.plan + *desc_used, info.blob_bytes(), cudaMemcpyHostToDevice, s));
   pm_ctx::FfnSample sample{};

@@ -311,6 +311,177 @@ __device__ __forceinline__ void splitk_tile(const GroupDesc& grp, int tile_local
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// uint4 group-128 experts (asymmetric: w = (q - zero) * scale, fp16 scale and zero per 128
+// weights of a row). Dequantisation is fused into the load path without touching the weights
+// one by one: a 32-bit word holds 8 weights of one row, the even-k nibbles in its low half and
+// the odd-k nibbles in its high half, so `((word >> 4j) & 0x000F000F) | 0x43004300` is the bf16
+// pair (128 + q[2j], 128 + q[2j+1]) ready to be an MMA A register. One lane load of 16 bytes
+// covers 32 weights, the four lanes of a row cover exactly one quantisation group, and per group
+//     sum_k (q_k - z) s x_k = s * ( sum_k (128 + q_k) x_k  -  (128 + z) * sum_k x_k ),
+// where both sums come out of the tensor core (the second from an all-ones A fragment).
+// Layout of the metadata: per matrix an array [rows, K/128] of {scale, zero} fp16 pairs.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t q4_pair(uint32_t word, int j) {
+  return ((word >> (4 * j)) & 0x000F000Fu) | 0x43004300u;
+}
+
+template <int NT, bool GATEUP, int DEPTH, bool COHERENT_B>
+__device__ __forceinline__ void splitk_tile_q4(const GroupDesc& grp, int tile_local,
+                                               const __nv_bfloat16* __restrict__ bsrc, int ldb,
+                                               const int32_t* __restrict__ row_token, int hidden,
+                                               __nv_bfloat16* __restrict__ hbuf, int ld_h,
+                                               float* __restrict__ yexp, float (*red)[2 * NT * 4][32]) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int g = lane >> 2;
+  const int q = lane & 3;
+  const int K = GATEUP ? hidden : grp.inter;
+  const int rows = grp.row_count;
+  const int m0 = tile_local * (GATEUP ? 16 : 32);
+  const size_t row_bytes = (size_t)K / 2;   // packed nibbles
+  const int n_grp = K / 128;                // quantisation groups per row = k-steps
+
+  const unsigned char* a_ptr[4];
+  const uint32_t* sz_ptr[4];  // {scale, zero} fp16 pairs of the same four rows
+  {
+    const unsigned char* w0 = reinterpret_cast<const unsigned char*>(GATEUP ? grp.w_gate : grp.w_down);
+    const unsigned char* w1 = reinterpret_cast<const unsigned char*>(GATEUP ? grp.w_up : grp.w_down);
+    const uint32_t* z0 = reinterpret_cast<const uint32_t*>(GATEUP ? grp.q_gate : grp.q_down);
+    const uint32_t* z1 = reinterpret_cast<const uint32_t*>(GATEUP ? grp.q_up : grp.q_down);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int row = GATEUP ? (m0 + g + 8 * (j & 1)) : (m0 + g + 8 * j);
+      const unsigned char* w = (GATEUP && j >= 2) ? w1 : w0;
+      const uint32_t* z = (GATEUP && j >= 2) ? z1 : z0;
+      a_ptr[j] = w + (size_t)row * row_bytes + q * 16;
+      sz_ptr[j] = z + (size_t)row * n_grp;
+    }
+  }
+  const unsigned char* b_ptr[NT];
+  bool b_ok[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int n = nt * 8 + g;
+    b_ok[nt] = n < rows;
+    const int src_row = b_ok[nt] ? (GATEUP ? row_token[grp.row_start + n] : grp.row_start + n) : 0;
+    b_ptr[nt] = reinterpret_cast<const unsigned char*>(bsrc + (size_t)src_row * ldb) + q * 64;
+  }
+
+  float acc[2][NT][4];
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[m][nt][i] = 0.f;
+
+  const int s_begin = (warp * n_grp) / kSplitWarps;
+  const int s_end = ((warp + 1) * n_grp) / kSplitWarps;
+  constexpr uint32_t kOnes = 0x3F803F80u;  // bf16 (1, 1)
+  for (int s0 = s_begin; s0 < s_end; s0 += DEPTH) {
+    uint4 a[DEPTH][4];
+    uint32_t sz[DEPTH][4];
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      if (s0 + d < s_end) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          a[d][j] = ldg_stream(a_ptr[j] + (size_t)(s0 + d) * 64);
+          sz[d][j] = __ldg(sz_ptr[j] + (s0 + d));
+        }
+      }
+    }
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      if (s0 + d < s_end) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          float raw[2][4], xs[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) raw[0][i] = raw[1][i] = xs[i] = 0.f;
+          // this lane's 32 token values of the group: four 16-byte vectors
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint4 b = b_ok[nt] ? load_b<COHERENT_B>(b_ptr[nt] + (size_t)(s0 + d) * 256 + v * 16)
+                                     : make_uint4(0, 0, 0, 0);
+            const uint32_t w00 = (&a[d][0].x)[v], w01 = (&a[d][1].x)[v];  // matrix 0: rows g, g+8
+            const uint32_t w10 = (&a[d][2].x)[v], w11 = (&a[d][3].x)[v];  // matrix 1
+            mma_bf16(raw[0], q4_pair(w00, 0), q4_pair(w01, 0), q4_pair(w00, 1), q4_pair(w01, 1), b.x, b.y);
+            mma_bf16(raw[0], q4_pair(w00, 2), q4_pair(w01, 2), q4_pair(w00, 3), q4_pair(w01, 3), b.z, b.w);
+            mma_bf16(raw[1], q4_pair(w10, 0), q4_pair(w11, 0), q4_pair(w10, 1), q4_pair(w11, 1), b.x, b.y);
+            mma_bf16(raw[1], q4_pair(w10, 2), q4_pair(w11, 2), q4_pair(w10, 3), q4_pair(w11, 3), b.z, b.w);
+            mma_bf16(xs, kOnes, kOnes, kOnes, kOnes, b.x, b.y);
+            mma_bf16(xs, kOnes, kOnes, kOnes, kOnes, b.z, b.w);
+          }
+#pragma unroll
+          for (int m = 0; m < 2; ++m) {
+            const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&sz[d][2 * m]));      // row g
+            const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&sz[d][2 * m + 1]));  // row g+8
+            acc[m][nt][0] += lo.x * (raw[m][0] - (128.f + lo.y) * xs[0]);
+            acc[m][nt][1] += lo.x * (raw[m][1] - (128.f + lo.y) * xs[1]);
+            acc[m][nt][2] += hi.x * (raw[m][2] - (128.f + hi.y) * xs[0]);
+            acc[m][nt][3] += hi.x * (raw[m][3] - (128.f + hi.y) * xs[1]);
+          }
+        }
+      }
+    }
+  }
+
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) red[warp][(m * NT + nt) * 4 + i][lane] = acc[m][nt][i];
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < NT * 4 * 32; idx += kSplitThreads) {
+    const int l = idx & 31;
+    const int v = idx >> 5;
+    const int nt = v >> 2, i = v & 3;
+    float s0v = 0.f, s1v = 0.f;
+#pragma unroll
+    for (int w = 0; w < kSplitWarps; ++w) {
+      s0v += red[w][v][l];
+      s1v += red[w][NT * 4 + v][l];
+    }
+    const int lg = l >> 2, lq = l & 3;
+    const int n = nt * 8 + 2 * lq + (i & 1);
+    if (n >= rows) continue;
+    const int m = m0 + lg + ((i & 2) ? 8 : 0);
+    const size_t r = (size_t)(grp.row_start + n);
+    if (GATEUP) {
+      hbuf[r * ld_h + m] = __float2bfloat16_rn(silu(s0v) * s1v);
+    } else {
+      yexp[r * hidden + m] = s0v;
+      yexp[r * hidden + m + 16] = s1v;
+    }
+  }
+}
+
+template <int NT, int NMAT, int DEPTH>
+__global__ void __launch_bounds__(kSplitThreads, 2)
+grouped_ffn_q4_kernel(const GroupDesc* __restrict__ groups, const int32_t* __restrict__ tile_group,
+                      const __nv_bfloat16* __restrict__ bsrc, int ldb,
+                      const int32_t* __restrict__ row_token, int hidden,
+                      __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp) {
+  constexpr bool GATEUP = (NMAT == 2);
+  __shared__ float red[kSplitWarps][2 * NT * 4][32];
+  const GroupDesc grp = groups[tile_group[blockIdx.x]];
+  const int tile_local = blockIdx.x - (GATEUP ? grp.tile_start_gu : grp.tile_start_dn);
+  splitk_tile_q4<NT, GATEUP, DEPTH, false>(grp, tile_local, bsrc, ldb, row_token, hidden, hbuf, ld_h, yexp, red);
+}
+
+template <int NT, int NMAT>
+cudaError_t launch_q4(const GroupDesc* groups, const int32_t* tile_group, int tiles, const __nv_bfloat16* bsrc,
+                      int ldb, const int32_t* row_token, int hidden, __nv_bfloat16* hbuf, int ld_h, float* yexp,
+                      cudaStream_t s) {
+  grouped_ffn_q4_kernel<NT, NMAT, 2><<<tiles, kSplitThreads, 0, s>>>(groups, tile_group, bsrc, ldb, row_token,
+                                                                     hidden, hbuf, ld_h, yexp);
+  return cudaGetLastError();
+}
+
 template <int NT, int NMAT, int DEPTH>
 __global__ void __launch_bounds__(kSplitThreads, 2)
 grouped_ffn_splitk_kernel(const GroupDesc* __restrict__ groups, const int32_t* __restrict__ tile_group,
@@ -536,12 +707,25 @@ cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& 
                               __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s,
                               cudaEvent_t mid_event, bool fused) {
   if (info.n_desc <= 0) return cudaSuccess;
-  if (quant4) return cudaErrorNotSupported;
   const GroupDesc* groups = reinterpret_cast<const GroupDesc*>(blob_dev);
   const int32_t* t_gu = reinterpret_cast<const int32_t*>(blob_dev + info.off_tile_gu());
   const int32_t* t_dn = reinterpret_cast<const int32_t*>(blob_dev + info.off_tile_dn());
   const int max_rows = info.max_rows;
   cudaError_t e;
+  if (quant4) {
+    // uint4 experts: split-K decode tiles only (the planner keeps chunks at kSplitMaxRows rows)
+    if (max_rows > kSplitMaxRows) return cudaErrorNotSupported;
+    e = (max_rows <= 8) ? launch_q4<1, 2>(groups, t_gu, info.tiles_gu, x, H, row_token, H, hbuf, ld_h, yexp, s)
+                        : launch_q4<2, 2>(groups, t_gu, info.tiles_gu, x, H, row_token, H, hbuf, ld_h, yexp, s);
+    if (e != cudaSuccess) return e;
+    if (mid_event != nullptr) {
+      e = cudaEventRecord(mid_event, s);
+      if (e != cudaSuccess) return e;
+    }
+    return (max_rows <= 8)
+               ? launch_q4<1, 1>(groups, t_dn, info.tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s)
+               : launch_q4<2, 1>(groups, t_dn, info.tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s);
+  }
   if (fused && max_rows <= kSplitMaxRows && mid_event == nullptr) {
     int* counters = reinterpret_cast<int*>(const_cast<unsigned char*>(blob_dev) + info.off_counters());
     e = (max_rows <= 8)

@@ -17,17 +17,28 @@ import torch
 from . import _lib
 
 
-def run(groups: int, rows: int, hidden: int, inter: int, iters: int, warmup: int = 3) -> dict:
+def run(groups: int, rows: int, hidden: int, inter: int, iters: int, warmup: int = 3, quant4: bool = False) -> dict:
     _lib.load()
     dev = torch.device("cuda")
-    weights = [(torch.randn(3 * inter * hidden, device=dev) * 0.02).to(torch.bfloat16) for _ in range(groups)]
     tokens = 64
     x = torch.randn((tokens, hidden), device=dev).to(torch.bfloat16)
     arr = (_lib.pm_ffn_group * groups)()
-    for i, w in enumerate(weights):
-        p = w.data_ptr()
-        arr[i] = _lib.pm_ffn_group(p, p + inter * hidden * 2, p + 2 * inter * hidden * 2, None, None, None,
-                                   i * rows, rows, inter, 0)
+    mat = inter * hidden
+    if quant4:
+        # random nibbles and {scale, zero} pairs: timing does not depend on the values
+        weights = [torch.randint(0, 256, (3 * mat // 2,), dtype=torch.uint8, device=dev) for _ in range(groups)]
+        meta = [torch.full((3 * mat // 128, 2), 0.01, dtype=torch.float16, device=dev) for _ in range(groups)]
+        for i, (w, m) in enumerate(zip(weights, meta)):
+            p, z = w.data_ptr(), m.data_ptr()
+            arr[i] = _lib.pm_ffn_group(p, p + mat // 2, p + mat, z, z + mat // 128 * 4, z + 2 * (mat // 128) * 4,
+                                       i * rows, rows, inter, 0)
+        weight_bytes = groups * 3 * (mat // 2 + mat // 128 * 4)
+    else:
+        weights = [(torch.randn(3 * mat, device=dev) * 0.02).to(torch.bfloat16) for _ in range(groups)]
+        for i, w in enumerate(weights):
+            p = w.data_ptr()
+            arr[i] = _lib.pm_ffn_group(p, p + mat * 2, p + 2 * mat * 2, None, None, None, i * rows, rows, inter, 0)
+        weight_bytes = groups * 3 * mat * 2
     n_rows = groups * rows
     row_token = torch.randint(0, tokens, (n_rows,), dtype=torch.int32, device=dev)
     nbytes = _lib.call("pm_k_swiglu_ffn_scratch_bytes", groups, n_rows, inter, hidden)
@@ -35,7 +46,7 @@ def run(groups: int, rows: int, hidden: int, inter: int, iters: int, warmup: int
     yexp = torch.empty((n_rows, hidden), dtype=torch.float32, device=dev)
 
     def once():
-        _lib.call("pm_k_swiglu_ffn", arr, groups, 0, x.data_ptr(), hidden, row_token.data_ptr(), n_rows,
+        _lib.call("pm_k_swiglu_ffn", arr, groups, int(quant4), x.data_ptr(), hidden, row_token.data_ptr(), n_rows,
                   yexp.data_ptr(), scratch.data_ptr(), nbytes, None)
 
     for _ in range(warmup):
@@ -48,8 +59,7 @@ def run(groups: int, rows: int, hidden: int, inter: int, iters: int, warmup: int
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / iters
-    weight_bytes = groups * 3 * inter * hidden * 2
-    return {"groups": groups, "rows": rows, "hidden": hidden, "inter": inter, "us_per_launch_pair": ms * 1e3,
+    return {"quant4": quant4, "groups": groups, "rows": rows, "hidden": hidden, "inter": inter, "us_per_launch_pair": ms * 1e3,
             "weight_mb": weight_bytes / 1e6, "gb_per_s": weight_bytes / ms / 1e6}
 
 
@@ -61,8 +71,9 @@ def main():
     ap.add_argument("--inter", type=int, default=1408)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--quant4", action="store_true", help="uint4 group-128 experts")
     a = ap.parse_args()
-    print(json.dumps(run(a.groups, a.rows, a.hidden, a.inter, a.iters, a.warmup)))
+    print(json.dumps(run(a.groups, a.rows, a.hidden, a.inter, a.iters, a.warmup, a.quant4)))
 
 
 if __name__ == "__main__":
