@@ -75,6 +75,11 @@ int pm_ctx_get(pm_ctx* ctx, const char* key, char* buf, size_t cap) {
   std::string k(key);
   if (k == "keep_routing") v = ctx->keep_routing ? "true" : "false";
   else if (k == "seq_len") v = std::to_string(ctx->seq_len);
+  else if (k == "tc_launches") v = std::to_string(ctx->tc_launches);
+  else if (k == "tc_error") {
+    if (ctx->have_last_stream) cudaStreamSynchronize(ctx->last_stream);
+    v = std::to_string(ctx->h_tc_err ? *ctx->h_tc_err : 0);
+  }
   else if (k == "slab_impl") v = !ctx->slab_built ? "none" : (ctx->slab_vmm ? "vmm" : "cudamalloc");
   else if (k == "line_stride") v = std::to_string(ctx->line_stride);
   else if (k == "num_lines") v = std::to_string(ctx->n_lines);
@@ -95,6 +100,10 @@ int pm_ctx_set(pm_ctx* ctx, const char* key, const char* value) {
   }
   if (k == "seq_len") {
     ctx->seq_len = std::atoi(value);
+    return PM_OK;
+  }
+  if (k == "tc_prefill") {
+    ctx->tc_prefill = (v == "1" || v == "true" || v == "True" || v == "on");
     return PM_OK;
   }
   if (k == "device_plan") {

@@ -1,5 +1,6 @@
 // Shared declarations for the sm_100a kernels and the host runtime of the MoE hot path.
 #pragma once
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -123,6 +124,23 @@ cudaError_t launch_gather_rows(const void* src, const int32_t* index, int n_rows
 cudaError_t launch_combine(const float* yexp, const int32_t* pos, const float* topk_w, int T, int H,
                            int k, int R, int n_shared, const float* shared_scale,
                            __nv_bfloat16* y, cudaStream_t s);
+
+// ---- prefill path (tcgen05) ---------------------------------------------------------------------
+// Tensor maps of one launch pair: token rows (expert-sorted x, intermediate h), the slab (3-D:
+// k, weight row, cache line) per projection, and the layer's shared expert (2-D).
+struct TcMaps {
+  CUtensorMap a_x, a_h, slab_gate, slab_up, slab_down, sh_gate, sh_up, sh_down;
+};
+struct TcGroup {
+  int32_t row_start, row_count, inter;
+  int32_t line;  // global cache line of the expert, -1 = the shared expert
+};
+struct TcTile {
+  int32_t group, m0, n0, pad;
+};
+cudaError_t launch_prefill_ffn(const TcMaps& maps, const TcGroup* groups_dev, const TcTile* tiles_gu_dev, int n_gu,
+                               const TcTile* tiles_dn_dev, int n_dn, int hidden, __nv_bfloat16* hbuf, int ld_h,
+                               float* yexp, int32_t* err_dev, cudaStream_t s, cudaEvent_t mid_event);
 
 cudaError_t launch_predictor_mlp(const __nv_bfloat16* x, int B, int H, const __nv_bfloat16* w1,
                                  const float* b1, int D, const __nv_bfloat16* w2, const float* b2,

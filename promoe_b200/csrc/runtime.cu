@@ -119,6 +119,13 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
   const int Ir = std::max(w.inter, c->ws_inter_routed);
   const int Is = std::max(w.shared_inter, c->ws_inter_shared);
   size_t o_res = take(ResidentPlanArgs::blob_bytes(E, Ir, Is, H, &c->res_off_desc, &c->res_off_gu, &c->res_off_dn));
+  size_t o_xp = take(rows * H * 2);
+  {
+    const size_t m_tiles = rows / 128 + (size_t)E + 2;
+    c->tc_plan_cap = 16 * ((size_t)E + 2) + 16 * m_tiles * ((size_t)(std::max(I, Is) + 127) / 128 + (size_t)(H + 127) / 128) + 1024 +
+                     768 * ((size_t)E + 2);  // three 256-byte roundings per segment, at most one segment per expert
+  }
+  size_t o_tcp = take(c->tc_plan_cap), o_tce = take(16);
   PM_CUDA(cudaMalloc(&c->ws_dev, off));
   PM_CUDA(cudaMemset(c->ws_dev, 0, off));
   c->ws_bytes = off;
@@ -140,6 +147,13 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
   c->d_xin = (__nv_bfloat16*)(b + o_x);
   c->d_yout = (__nv_bfloat16*)(b + o_yo);
   c->d_res_plan = b + o_res;
+  c->d_xperm = (__nv_bfloat16*)(b + o_xp);
+  c->d_tc_plan = b + o_tcp;
+  c->d_tc_err = (int32_t*)(b + o_tce);
+  if (c->h_tc_plan) PM_CUDA(cudaFreeHost(c->h_tc_plan));
+  PM_CUDA(cudaHostAlloc((void**)&c->h_tc_plan, c->tc_plan_cap + 64, cudaHostAllocDefault));
+  c->h_tc_err = (int32_t*)(c->h_tc_plan + c->tc_plan_cap);
+  *c->h_tc_err = 0;
   c->ws_inter_routed = Ir;
   c->ws_inter_shared = Is;
   // pinned staging: [counts+offsets | scores | routing ids | routing weights | descriptors]
@@ -381,11 +395,68 @@ namespace {
 // One grouped FFN launch: the experts in it, and the lines whose copies it has to wait for.
 struct Segment {
   std::vector<pm_ffn_group> groups;
+  std::vector<int> group_line;  // cache line of each group, -1 = shared expert
   std::vector<int> lines;
   std::vector<int> waits;
   bool has_line(int line) const { return std::find(lines.begin(), lines.end(), line) != lines.end(); }
   bool empty() const { return groups.empty(); }
 };
+
+// Prefill-size segment on the tcgen05 path: gather the token rows once per layer call, plan the
+// 128 x 128 tiles, upload groups and tiles, launch the gate/up and the down kernel.
+int flush_segment_tc(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv_bfloat16* x, int n_rows,
+                     cudaStream_t s) {
+  if (!c->xperm_ready) {
+    PM_CUDA(launch_gather_rows(x, c->d_row_token, n_rows, (size_t)w.hidden * 2, c->d_xperm, s));
+    c->kernel_launches += 1;
+    c->xperm_ready = true;
+  }
+  if (!c->tc_maps_ready) {
+    int rc = tc_build_maps(c, w, c->ws_tokens * (c->ws_topk + 1), &c->tc_maps);
+    if (rc != PM_OK) return rc;
+    c->tc_maps_ready = true;
+  }
+  std::vector<TcGroup> groups;
+  for (size_t i = 0; i < seg->groups.size(); ++i) {
+    const pm_ffn_group& g = seg->groups[i];
+    if (g.row_count <= 0) continue;
+    groups.push_back(TcGroup{g.row_start, g.row_count, g.inter, seg->group_line[i]});
+  }
+  std::vector<TcTile> gu, dn;
+  tc_plan(groups, w.hidden, &gu, &dn);
+  const size_t g_bytes = align_up(groups.size() * sizeof(TcGroup), 256);
+  const size_t gu_bytes = align_up(gu.size() * sizeof(TcTile), 256), dn_bytes = align_up(dn.size() * sizeof(TcTile), 256);
+  const size_t total = g_bytes + gu_bytes + dn_bytes;
+  if (c->tc_plan_used + total > c->tc_plan_cap) return fail(PM_ERR_STATE, "prefill plan buffer overflow");
+  unsigned char* h = c->h_tc_plan + c->tc_plan_used;
+  unsigned char* d = c->d_tc_plan + c->tc_plan_used;
+  std::memcpy(h, groups.data(), groups.size() * sizeof(TcGroup));
+  std::memcpy(h + g_bytes, gu.data(), gu.size() * sizeof(TcTile));
+  std::memcpy(h + g_bytes + gu_bytes, dn.data(), dn.size() * sizeof(TcTile));
+  PM_CUDA(cudaMemcpyAsync(d, h, total, cudaMemcpyHostToDevice, s));
+  c->tc_plan_used += total;
+  pm_ctx::FfnSample sample{};
+  if (c->profile_ffn) {
+    PM_CUDA(cudaEventCreate(&sample.e0));
+    PM_CUDA(cudaEventCreate(&sample.e1));
+    PM_CUDA(cudaEventCreate(&sample.e2));
+    for (const TcGroup& g : groups) {
+      sample.bytes_gu += 4ll * g.inter * w.hidden;
+      sample.bytes_dn += 2ll * g.inter * w.hidden;
+    }
+    PM_CUDA(cudaEventRecord(sample.e0, s));
+  }
+  PM_CUDA(launch_prefill_ffn(c->tc_maps, (const TcGroup*)d, (const TcTile*)(d + g_bytes), (int)gu.size(),
+                             (const TcTile*)(d + g_bytes + gu_bytes), (int)dn.size(), w.hidden, c->d_hbuf, c->ws_inter,
+                             c->d_yexp, c->d_tc_err, s, c->profile_ffn ? sample.e1 : nullptr));
+  if (c->profile_ffn) {
+    PM_CUDA(cudaEventRecord(sample.e2, s));
+    c->ffn_samples.push_back(sample);
+  }
+  c->kernel_launches += 2;
+  c->tc_launches += 1;
+  return PM_OK;
+}
 
 int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv_bfloat16* x, int n_rows,
                   size_t* desc_used, cudaStream_t s) {
@@ -396,6 +467,22 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
       c->line_pending[line] = 0;
       c->line_waiter[line] = s;
     }
+  }
+  int seg_max_rows = 0;
+  for (const pm_ffn_group& g : seg->groups) seg_max_rows = std::max(seg_max_rows, g.row_count);
+  if (seg_max_rows > kSplitMaxRows && tc_prefill_usable(c, w)) {
+    int rc = flush_segment_tc(c, seg, w, x, n_rows, s);
+    if (rc != PM_OK) return rc;
+    if (!seg->lines.empty()) {
+      cudaEvent_t ev = next_seg_event(c);
+      PM_CUDA(cudaEventRecord(ev, s));
+      for (int line : seg->lines) c->line_read[line] = ev;
+    }
+    seg->groups.clear();
+    seg->group_line.clear();
+    seg->lines.clear();
+    seg->waits.clear();
+    return PM_OK;
   }
   FfnPlanInfo info;
   const int chunk_rows = w.quant4 ? kSplitMaxRows : kMaxChunkRows;
@@ -444,6 +531,7 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
     for (int line : seg->lines) c->line_read[line] = ev;
   }
   seg->groups.clear();
+  seg->group_line.clear();
   seg->lines.clear();
   seg->waits.clear();
   (void)n_rows;
@@ -570,6 +658,20 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
   }
   rc = wait_event(c->sync_event, 30.0);
   if (rc != PM_OK) return rc;
+  // everything enqueued by earlier layer calls has finished: the staging buffers may be reused, and
+  // an error the prefill kernel of an earlier call recorded is visible now
+  c->tc_plan_used = 0;
+  c->xperm_ready = false;
+  c->tc_maps_ready = false;
+  if (c->tc_err_pending) {
+    c->tc_err_pending = false;
+    if (*c->h_tc_err != 0) {
+      const int code = *c->h_tc_err;
+      *c->h_tc_err = 0;
+      return fail(PM_ERR_TIMEOUT, "the prefill kernel of the previous layer call gave up a bounded wait (code " +
+                                      std::to_string(code) + ")");
+    }
+  }
 
   if (keep) {
     c->last_ids[layer].assign(st.ids, st.ids + R);
@@ -637,6 +739,7 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
     g.row_count = T;
     g.inter = w.shared_inter;
     seg.groups.push_back(g);
+    seg.group_line.push_back(-1);
   }
   for (const Action& a : acts) {
     if (a.type == Action::kCopy) {
@@ -656,6 +759,7 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
         if (rc != PM_OK) return rc;
       }
       seg.groups.push_back(group_of(a.expert, a.line));
+      seg.group_line.push_back(a.line);
       seg.lines.push_back(a.line);
       if (must_wait) seg.waits.push_back(a.line);
     }
@@ -670,6 +774,10 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
                            w.shared_gate_w ? c->d_shared_scale : nullptr, (__nv_bfloat16*)yv, s));
   }
   c->kernel_launches += 1;
+  if (c->xperm_ready) {  // the prefill path ran in this call
+    PM_CUDA(cudaMemcpyAsync(c->h_tc_err, c->d_tc_err, 4, cudaMemcpyDeviceToHost, s));
+    c->tc_err_pending = true;
+  }
   for (int64_t id : ids) c->eng->expert_done(layer, (int)id);
   c->eng->layer_done(layer);
   (void)N;
@@ -749,6 +857,7 @@ pm_ctx::~pm_ctx() {
     if (l.slot_table_dev) cudaFree(l.slot_table_dev);
   if (ws_dev) cudaFree(ws_dev);
   if (h_stage) cudaFreeHost(h_stage);
+  if (h_tc_plan) cudaFreeHost(h_tc_plan);
   if (slab_built) {
     if (slab_vmm) {
       pm::Driver& d = pm::driver();

@@ -92,6 +92,19 @@ struct pm_ctx {
   unsigned char* h_stage = nullptr;  // pinned: counts+offsets, scores, descriptors, slot tables, routing
   size_t h_stage_bytes = 0;
 
+  // ---- prefill (tcgen05) path ---------------------------------------------------------------------
+  bool tc_prefill = true;             // use it for segments with more than 16 rows per expert
+  __nv_bfloat16* d_xperm = nullptr;   // expert-sorted copy of the token rows [rows, hidden]
+  unsigned char* d_tc_plan = nullptr; // groups + tiles of the segments of one layer call
+  unsigned char* h_tc_plan = nullptr; // pinned staging of the same
+  size_t tc_plan_cap = 0, tc_plan_used = 0;
+  int32_t* d_tc_err = nullptr;        // set by the kernel when a bounded wait gave up
+  int32_t* h_tc_err = nullptr;        // pinned copy, checked at the next layer call
+  bool tc_err_pending = false;
+  bool xperm_ready = false, tc_maps_ready = false;  // per layer call
+  pm::TcMaps tc_maps;
+  int64_t tc_launches = 0;
+
   bool keep_routing = false;
   int seq_len = 1;
   std::vector<std::vector<int32_t>> last_ids;  // per layer routing copies (keep_routing)
@@ -132,5 +145,8 @@ int rt_forward_host(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStr
 int rt_report_hidden(pm_ctx* c, int index, const void* hidden, int B, int seq, cudaStream_t s);
 void rt_mark_dirty(pm_ctx* c, const std::vector<Action>& actions);
 int rt_profile_collect(pm_ctx* c);
+bool tc_prefill_usable(const pm_ctx* c, const pm_layer_weights& w);
+int tc_build_maps(pm_ctx* c, const pm_layer_weights& w, int rows_cap, TcMaps* m);
+void tc_plan(const std::vector<TcGroup>& groups, int hidden, std::vector<TcTile>* gu, std::vector<TcTile>* dn);
 
 }  // namespace pm

@@ -496,28 +496,173 @@ grouped_ffn_splitk_kernel(const GroupDesc* __restrict__ groups, const int32_t* _
 }
 
 // ---------------------------------------------------------------------------------------------
-// Fused decode variant: ONE cooperative launch per segment. A fixed grid of resident CTAs pulls
-// gate/up tiles from a counter, meets at a grid barrier (the intermediate rows must be complete
-// before any down tile reads them), then pulls down tiles. Compared with two launches this
-// removes one launch gap and one tail per segment, and dynamic tile pulling evens out the
-// heavier tiles of the wide shared expert.
+// Fused decode variant: ONE cooperative launch per segment. A fixed grid of resident CTAs strides
+// over the gate/up tiles, meets at a grid barrier (the intermediate rows must be complete before
+// any down tile reads them), then strides over the down tiles. Compared with two launches this
+// removes one launch gap and one tail per segment.
 // ---------------------------------------------------------------------------------------------
+// The same split-K tile cut into stages, so that a resident CTA can have the first loads of its
+// NEXT tile in flight while it reduces and stores the current one.
+template <int NT>
+struct TileCtx {
+  const unsigned char* a_ptr[4];
+  const unsigned char* b_ptr[NT];
+  bool b_ok[NT];
+  int rows, m0, row_start, s_begin, s_end;
+};
+
+template <int NT, bool GATEUP>
+__device__ __forceinline__ void tile_setup(TileCtx<NT>& t, const GroupDesc* __restrict__ groups,
+                                           const int32_t* __restrict__ tile_group, int tile,
+                                           const __nv_bfloat16* bsrc, int ldb,
+                                           const int32_t* __restrict__ row_token, int hidden) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, q = lane & 3;
+  const GroupDesc grp = groups[tile_group[tile]];
+  const int tile_local = tile - (GATEUP ? grp.tile_start_gu : grp.tile_start_dn);
+  const int K = GATEUP ? hidden : grp.inter;
+  const size_t row_bytes = (size_t)K * 2;
+  t.rows = grp.row_count;
+  t.row_start = grp.row_start;
+  t.m0 = tile_local * (GATEUP ? 16 : 32);
+  if (GATEUP) {
+    const unsigned char* w0 = reinterpret_cast<const unsigned char*>(grp.w_gate);
+    const unsigned char* w1 = reinterpret_cast<const unsigned char*>(grp.w_up);
+    t.a_ptr[0] = w0 + (size_t)(t.m0 + g) * row_bytes + q * 16;
+    t.a_ptr[1] = w0 + (size_t)(t.m0 + g + 8) * row_bytes + q * 16;
+    t.a_ptr[2] = w1 + (size_t)(t.m0 + g) * row_bytes + q * 16;
+    t.a_ptr[3] = w1 + (size_t)(t.m0 + g + 8) * row_bytes + q * 16;
+  } else {
+    const unsigned char* w0 = reinterpret_cast<const unsigned char*>(grp.w_down);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) t.a_ptr[j] = w0 + (size_t)(t.m0 + g + 8 * j) * row_bytes + q * 16;
+  }
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int n = nt * 8 + g;
+    t.b_ok[nt] = n < t.rows;
+    const int src_row = t.b_ok[nt] ? (GATEUP ? row_token[grp.row_start + n] : grp.row_start + n) : 0;
+    t.b_ptr[nt] = reinterpret_cast<const unsigned char*>(bsrc + (size_t)src_row * ldb) + q * 16;
+  }
+  const int steps = K / 32;
+  t.s_begin = (warp * steps) / kSplitWarps;
+  t.s_end = ((warp + 1) * steps) / kSplitWarps;
+}
+
+template <int NT, int DEPTH, bool COHERENT_B>
+__device__ __forceinline__ void tile_issue(const TileCtx<NT>& t, int s0, uint4 (&a)[DEPTH][4], uint4 (&b)[DEPTH][NT]) {
+#pragma unroll
+  for (int d = 0; d < DEPTH; ++d) {
+    if (s0 + d < t.s_end) {
+      const size_t off = (size_t)(s0 + d) * 64;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) a[d][j] = ldg_stream(t.a_ptr[j] + off);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+        b[d][nt] = t.b_ok[nt] ? load_b<COHERENT_B>(t.b_ptr[nt] + off) : make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
+template <int NT, int DEPTH>
+__device__ __forceinline__ void tile_compute(const TileCtx<NT>& t, int s0, const uint4 (&a)[DEPTH][4],
+                                             const uint4 (&b)[DEPTH][NT], float (&acc)[2][NT][4]) {
+#pragma unroll
+  for (int d = 0; d < DEPTH; ++d) {
+    if (s0 + d < t.s_end) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+          const uint4& lo = a[d][2 * m];
+          const uint4& hi = a[d][2 * m + 1];
+          mma_bf16(acc[m][nt], lo.x, hi.x, lo.y, hi.y, b[d][nt].x, b[d][nt].y);
+          mma_bf16(acc[m][nt], lo.z, hi.z, lo.w, hi.w, b[d][nt].z, b[d][nt].w);
+        }
+      }
+    }
+  }
+}
+
+template <int NT, bool GATEUP>
+__device__ __forceinline__ void tile_finish(int rows, int m0, int row_start, float (&acc)[2][NT][4],
+                                            float (*red)[2 * NT * 4][32], __nv_bfloat16* __restrict__ hbuf, int ld_h,
+                                            float* __restrict__ yexp, int hidden) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        red[warp][(m * NT + nt) * 4 + i][lane] = acc[m][nt][i];
+        acc[m][nt][i] = 0.f;
+      }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < NT * 4 * 32; idx += kSplitThreads) {
+    const int l = idx & 31, v = idx >> 5;
+    const int nt = v >> 2, i = v & 3;
+    float s0v = 0.f, s1v = 0.f;
+#pragma unroll
+    for (int w = 0; w < kSplitWarps; ++w) {
+      s0v += red[w][v][l];
+      s1v += red[w][NT * 4 + v][l];
+    }
+    const int lg = l >> 2, lq = l & 3;
+    const int n = nt * 8 + 2 * lq + (i & 1);
+    if (n >= rows) continue;
+    const int m = m0 + lg + ((i & 2) ? 8 : 0);
+    const size_t r = (size_t)(row_start + n);
+    if (GATEUP) {
+      hbuf[r * ld_h + m] = __float2bfloat16_rn(silu(s0v) * s1v);
+    } else {
+      yexp[r * hidden + m] = s0v;
+      yexp[r * hidden + m + 16] = s1v;
+    }
+  }
+  __syncthreads();  // `red` is free again before the next tile's partial sums arrive
+}
+
+// Tiles blockIdx.x, blockIdx.x + gridDim.x, ... of one phase. The assignment is static, so the
+// next tile is known early: its first batch of loads is issued before the current tile is
+// reduced, which keeps DRAM requests in flight across tile boundaries.
 template <int NT, bool GATEUP, int DEPTH>
-__device__ __forceinline__ void pull_tiles(const GroupDesc* __restrict__ groups,
-                                           const int32_t* __restrict__ tile_group, int n_tiles, int* counter,
-                                           const __nv_bfloat16* __restrict__ bsrc, int ldb,
-                                           const int32_t* __restrict__ row_token, int hidden,
-                                           __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp,
-                                           float (*red)[2 * NT * 4][32], int* s_tile) {
+__device__ __forceinline__ void stream_tiles(const GroupDesc* __restrict__ groups,
+                                             const int32_t* __restrict__ tile_group, int n_tiles,
+                                             const __nv_bfloat16* bsrc, int ldb,
+                                             const int32_t* __restrict__ row_token, int hidden,
+                                             __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp,
+                                             float (*red)[2 * NT * 4][32]) {
+  constexpr bool COH = !GATEUP;  // the down phase reads rows other CTAs wrote in this kernel
+  int tile = blockIdx.x;
+  if (tile >= n_tiles) return;
+  TileCtx<NT> t;
+  uint4 a[DEPTH][4];
+  uint4 b[DEPTH][NT];
+  float acc[2][NT][4];
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[m][nt][i] = 0.f;
+  tile_setup<NT, GATEUP>(t, groups, tile_group, tile, bsrc, ldb, row_token, hidden);
+  tile_issue<NT, DEPTH, COH>(t, t.s_begin, a, b);
   while (true) {
-    if (threadIdx.x == 0) *s_tile = atomicAdd(counter, 1);
-    __syncthreads();  // also separates this tile's use of `red` from the previous tile's epilogue
-    const int tile = *s_tile;
-    if (tile >= n_tiles) break;
-    const GroupDesc grp = groups[tile_group[tile]];
-    const int tile_local = tile - (GATEUP ? grp.tile_start_gu : grp.tile_start_dn);
-    splitk_tile<NT, GATEUP, DEPTH, !GATEUP>(grp, tile_local, bsrc, ldb, row_token, hidden, hbuf, ld_h, yexp, red);
-    __syncthreads();  // every thread has read *s_tile and finished with `red`
+    for (int s0 = t.s_begin; s0 < t.s_end;) {
+      tile_compute<NT, DEPTH>(t, s0, a, b, acc);
+      s0 += DEPTH;
+      if (s0 < t.s_end) tile_issue<NT, DEPTH, COH>(t, s0, a, b);
+    }
+    const int rows = t.rows, m0 = t.m0, row_start = t.row_start;
+    const int next = tile + gridDim.x;
+    const bool has_next = next < n_tiles;
+    if (has_next) {
+      tile_setup<NT, GATEUP>(t, groups, tile_group, next, bsrc, ldb, row_token, hidden);
+      tile_issue<NT, DEPTH, COH>(t, t.s_begin, a, b);
+    }
+    tile_finish<NT, GATEUP>(rows, m0, row_start, acc, red, hbuf, ld_h, yexp, hidden);
+    if (!has_next) break;
+    tile = next;
   }
 }
 
@@ -529,17 +674,15 @@ grouped_ffn_fused_kernel(const GroupDesc* __restrict__ groups, const int32_t* __
                          const int32_t* __restrict__ row_token, __nv_bfloat16* hbuf, int ld_h,
                          float* __restrict__ yexp, const int32_t* __restrict__ dev_tiles) {
   __shared__ float red[kSplitWarps][2 * NT * 4][32];
-  __shared__ int s_tile;
+  (void)counters;
   if (dev_tiles != nullptr) {  // plan built on the device: the tile counts live there too
     tiles_gu = dev_tiles[0];
     tiles_dn = dev_tiles[1];
   }
-  pull_tiles<NT, true, DEPTH>(groups, tile_gu, tiles_gu, counters, x, hidden, row_token, hidden, hbuf, ld_h, yexp,
-                              red, &s_tile);
+  stream_tiles<NT, true, DEPTH>(groups, tile_gu, tiles_gu, x, hidden, row_token, hidden, hbuf, ld_h, yexp, red);
   __threadfence();
   cooperative_groups::this_grid().sync();
-  pull_tiles<NT, false, DEPTH>(groups, tile_dn, tiles_dn, counters + 1, hbuf, ld_h, row_token, hidden, nullptr,
-                               ld_h, yexp, red, &s_tile);
+  stream_tiles<NT, false, DEPTH>(groups, tile_dn, tiles_dn, hbuf, ld_h, row_token, hidden, nullptr, ld_h, yexp, red);
 }
 
 // Resident grid of the fused kernel on the current device (0 if cooperative launch is unavailable).

@@ -63,6 +63,40 @@ def run(groups: int, rows: int, hidden: int, inter: int, iters: int, warmup: int
             "weight_mb": weight_bytes / 1e6, "gb_per_s": weight_bytes / ms / 1e6}
 
 
+def run_prefill(config: str, tokens: int, iters: int, tc: bool) -> dict:
+    """Times one fused layer call of a prefill-size batch (all experts resident) and reports the
+    FFN rate: flop = tokens * (k * 6 * H * I + 6 * H * I_shared)."""
+    from . import synth
+    cfg = synth.CONFIGS[config]
+    stack = synth.SyntheticStack(cfg, "cuda", num_layer=1, cache_rate="1.0", num_predict_expert_per_layer=0)
+    stack.install_layers()
+    cache = stack.cache
+    cache.set("tc_prefill", int(tc))
+    cache.set("seq_len", tokens)
+    x = torch.randn((tokens, cfg.hidden), device="cuda").to(torch.bfloat16)
+    y = torch.empty_like(x)
+    for _ in range(2):
+        cache.forward(0, x, out=y)
+    torch.cuda.synchronize()
+    cache.set("profile_ffn", 1)
+    cache.profile(reset=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        cache.forward(0, x, out=y)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    prof = cache.profile(reset=True)
+    flop = tokens * 6.0 * cfg.hidden * (cfg.top_k * cfg.inter + cfg.shared_inter)
+    ffn_ms = (prof["gateup_ms"] + prof["down_ms"] + prof["fused_ms"]) / iters
+    out = {"config": config, "tokens": tokens, "tensor_core_path": tc, "tc_launches": int(cache.get("tc_launches")),
+           "tc_error": cache.get("tc_error"), "layer_ms": ms, "ffn_ms": ffn_ms, "ffn_tflops": flop / ffn_ms / 1e9,
+           "layer_tflops": flop / ms / 1e9, "gateup_ms": prof["gateup_ms"] / iters, "down_ms": prof["down_ms"] / iters}
+    cache.close()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--groups", type=int, default=60)
@@ -72,7 +106,13 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--quant4", action="store_true", help="uint4 group-128 experts")
+    ap.add_argument("--prefill-tokens", type=int, default=0, help="time one prefill-size layer call instead")
+    ap.add_argument("--config", default="c5")
+    ap.add_argument("--no-tc", action="store_true", help="prefill through the staged mma.sync kernel")
     a = ap.parse_args()
+    if a.prefill_tokens:
+        print(json.dumps(run_prefill(a.config, a.prefill_tokens, a.iters, not a.no_tc)))
+        return
     print(json.dumps(run(a.groups, a.rows, a.hidden, a.inter, a.iters, a.warmup, a.quant4)))
 
 
