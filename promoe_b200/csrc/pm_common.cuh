@@ -58,7 +58,8 @@ cudaError_t launch_gate_topk(const __nv_bfloat16* x, const __nv_bfloat16* w_gate
 
 cudaError_t launch_permute(const int32_t* topk_ids, int R, int k, int E, int32_t* counts,
                            int32_t* offsets, int32_t* row_token, int32_t* pos, int32_t* err_flag,
-                           int tail_rows, int T, cudaStream_t s);
+                           int tail_rows, int T, cudaStream_t s, int32_t* scratch = nullptr,
+                           size_t scratch_ints = 0);
 
 // Geometry of one grouped FFN launch pair. The device blob it describes holds, 16-byte aligned
 // and in this order: n_desc GroupDesc, tiles_gu int32 (chunk index of every gate/up CTA tile),

@@ -126,6 +126,8 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
                      768 * ((size_t)E + 2);  // three 256-byte roundings per segment, at most one segment per expert
   }
   size_t o_tcp = take(c->tc_plan_cap), o_tce = take(16);
+  c->perm_scratch_ints = (R / 4096 + 2) * (size_t)E;
+  size_t o_ps = take(c->perm_scratch_ints * 4);
   PM_CUDA(cudaMalloc(&c->ws_dev, off));
   PM_CUDA(cudaMemset(c->ws_dev, 0, off));
   c->ws_bytes = off;
@@ -150,6 +152,7 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
   c->d_xperm = (__nv_bfloat16*)(b + o_xp);
   c->d_tc_plan = b + o_tcp;
   c->d_tc_err = (int32_t*)(b + o_tce);
+  c->d_perm_scratch = (int32_t*)(b + o_ps);
   if (c->h_tc_plan) PM_CUDA(cudaFreeHost(c->h_tc_plan));
   PM_CUDA(cudaHostAlloc((void**)&c->h_tc_plan, c->tc_plan_cap + 64, cudaHostAllocDefault));
   c->h_tc_err = (int32_t*)(c->h_tc_plan + c->tc_plan_cap);
@@ -578,7 +581,7 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
     c->kernel_launches += 1;
   }
   PM_CUDA(launch_permute(ids_dev, R, k, E, c->d_counts, c->d_offsets, c->d_row_token, c->d_pos, c->d_err,
-                         n_shared * T, T, s));
+                         n_shared * T, T, s, c->d_perm_scratch, c->perm_scratch_ints));
   c->kernel_launches += 1;
   std::vector<int> pred_dsts;
   if (!routed && c->cfg.predict_from_moe_input && c->seq_len == 1) {

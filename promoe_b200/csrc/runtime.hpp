@@ -98,6 +98,8 @@ struct pm_ctx {
   unsigned char* d_tc_plan = nullptr; // groups + tiles of the segments of one layer call
   unsigned char* h_tc_plan = nullptr; // pinned staging of the same
   size_t tc_plan_cap = 0, tc_plan_used = 0;
+  int32_t* d_perm_scratch = nullptr;  // per-chunk expert counts of the multi-CTA permutation
+  size_t perm_scratch_ints = 0;
   int32_t* d_tc_err = nullptr;        // set by the kernel when a bounded wait gave up
   int32_t* h_tc_err = nullptr;        // pinned copy, checked at the next layer call
   bool tc_err_pending = false;
