@@ -1,7 +1,7 @@
 // K3b: grouped SwiGLU expert FFN for prefill-size batches on the 5th-generation tensor cores.
 // One CTA computes a 128-row x 128-column tile of one expert's gate AND up projections (two f32
 // accumulators in tensor memory), or of its down projection, with tcgen05.mma issued by one
-// thread, operands staged in shared memory by TMA (128-byte swizzle, 4-stage mbarrier ring) and
+// thread, operands staged in shared memory by TMA (128-byte swizzle, 2- or 3-stage mbarrier ring) and
 // the accumulators read back with tcgen05.ld for the epilogue (SwiGLU -> bf16, or f32 rows).
 //
 // Rows are the expert-sorted token rows (gathered once per layer call), so an expert's rows are
@@ -26,22 +26,27 @@ using namespace sm100;
 
 constexpr int kTcThreads = 128;
 constexpr int kBM = 128, kBN = 128, kBK = 64;  // tile rows, tile columns, k per stage (128 bytes of bf16)
-constexpr int kStages = 4;
 constexpr int kTileBytes = kBM * kBK * 2;  // 16 KB: one operand tile of one stage
+
+// Two CTAs share an SM (96 KB of operand stages and 256 / 128 TMEM columns each), so that one CTA's
+// epilogue overlaps the other's main loop: 2 stages of 3 tiles for gate/up, 3 stages of 2 for down.
+template <bool GATEUP>
+constexpr int tc_stages() { return GATEUP ? 2 : 3; }
 
 template <bool GATEUP>
 constexpr size_t tc_smem_bytes() {
-  return 1024 /*alignment slack*/ + (size_t)kStages * (GATEUP ? 3 : 2) * kTileBytes + 256;
+  return 1024 /*alignment slack*/ + (size_t)tc_stages<GATEUP>() * (GATEUP ? 3 : 2) * kTileBytes + 256;
 }
 
 template <bool GATEUP>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcThreads, 2)
 prefill_ffn_kernel(const __grid_constant__ TcMaps maps, const TcGroup* __restrict__ groups,
                    const TcTile* __restrict__ tiles, int hidden, __nv_bfloat16* __restrict__ hbuf, int ld_h,
                    float* __restrict__ yexp, int32_t* __restrict__ err) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int kOperands = GATEUP ? 3 : 2;
+  constexpr int kStages = tc_stages<GATEUP>();
   unsigned char* stage_base = smem;  // [stage][operand][16 KB]
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * kOperands * kTileBytes);
   uint64_t* empty_bar = full_bar + kStages;

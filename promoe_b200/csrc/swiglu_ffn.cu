@@ -19,6 +19,8 @@
 // {4,5}, {6,7} to a second one. Both operands therefore use full 128-bit loads.
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+
 #include "pm_common.cuh"
 
 namespace pm {
@@ -501,6 +503,9 @@ grouped_ffn_splitk_kernel(const GroupDesc* __restrict__ groups, const int32_t* _
 // any down tile reads them), then strides over the down tiles. Compared with two launches this
 // removes one launch gap and one tail per segment.
 // ---------------------------------------------------------------------------------------------
+// How the 8 warps of a CTA share the reduction dimension (set from PM_FFN_INTERLEAVE_K at start-up).
+__device__ int g_interleave_k = 0;
+
 // The same split-K tile cut into stages, so that a resident CTA can have the first loads of its
 // NEXT tile in flight while it reduces and stores the current one.
 template <int NT>
@@ -508,7 +513,8 @@ struct TileCtx {
   const unsigned char* a_ptr[4];
   const unsigned char* b_ptr[NT];
   bool b_ok[NT];
-  int rows, m0, row_start, s_begin, s_end;
+  int rows, m0, row_start, s_begin, s_end;  // s_* count this warp's k-steps: 0 .. s_end
+  int step_bytes;                            // distance between two of them
 };
 
 template <int NT, bool GATEUP>
@@ -544,8 +550,22 @@ __device__ __forceinline__ void tile_setup(TileCtx<NT>& t, const GroupDesc* __re
     t.b_ptr[nt] = reinterpret_cast<const unsigned char*>(bsrc + (size_t)src_row * ldb) + q * 16;
   }
   const int steps = K / 32;
-  t.s_begin = (warp * steps) / kSplitWarps;
-  t.s_end = ((warp + 1) * steps) / kSplitWarps;
+  int first;  // this warp's first k-step
+  if (g_interleave_k) {
+    // warp w takes k-steps w, w+8, ...: at any moment the 8 warps read neighbouring 64-byte pieces
+    first = warp;
+    t.s_end = (steps - warp + kSplitWarps - 1) / kSplitWarps;
+    t.step_bytes = 64 * kSplitWarps;
+  } else {
+    first = (warp * steps) / kSplitWarps;
+    t.s_end = ((warp + 1) * steps) / kSplitWarps - first;
+    t.step_bytes = 64;
+  }
+  t.s_begin = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) t.a_ptr[j] += (size_t)first * 64;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) t.b_ptr[nt] += (size_t)first * 64;
 }
 
 template <int NT, int DEPTH, bool COHERENT_B>
@@ -553,7 +573,7 @@ __device__ __forceinline__ void tile_issue(const TileCtx<NT>& t, int s0, uint4 (
 #pragma unroll
   for (int d = 0; d < DEPTH; ++d) {
     if (s0 + d < t.s_end) {
-      const size_t off = (size_t)(s0 + d) * 64;
+      const size_t off = (size_t)(s0 + d) * t.step_bytes;
 #pragma unroll
       for (int j = 0; j < 4; ++j) a[d][j] = ldg_stream(t.a_ptr[j] + off);
 #pragma unroll
@@ -713,6 +733,14 @@ cudaError_t launch_fused(const GroupDesc* groups, const int32_t* t_gu, const int
                          const int32_t* dev_tiles = nullptr) {
   int grid = fused_grid_size<NT, DEPTH>();
   if (grid <= 0) return cudaErrorNotSupported;
+  static bool flag_set = false;
+  if (!flag_set) {
+    const char* env = std::getenv("PM_FFN_INTERLEAVE_K");
+    const int v = (env != nullptr && env[0] == '1') ? 1 : 0;
+    cudaError_t fe = cudaMemcpyToSymbol(g_interleave_k, &v, sizeof(int));
+    if (fe != cudaSuccess) return fe;
+    flag_set = true;
+  }
   if (dev_tiles == nullptr) grid = min(grid, max(tiles_gu, tiles_dn));
   void* args[] = {(void*)&groups, (void*)&t_gu, (void*)&t_dn, (void*)&tiles_gu, (void*)&tiles_dn, (void*)&counters,
                   (void*)&x, (void*)&hidden, (void*)&row_token, (void*)&hbuf, (void*)&ld_h, (void*)&yexp,
