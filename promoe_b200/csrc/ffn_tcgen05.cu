@@ -25,17 +25,21 @@ namespace {
 using namespace sm100;
 
 constexpr int kTcThreads = 128;
-constexpr int kBM = 128, kBN = 128, kBK = 64;  // tile rows, tile columns, k per stage (128 bytes of bf16)
+constexpr int kBM = 128, kBK = 64;  // tile rows, k per stage (128 bytes of bf16)
+// Tile columns: 128 for gate/up (two accumulators = 256 TMEM columns), 256 for down (one).
+template <bool GATEUP>
+constexpr int tc_bn() { return GATEUP ? 128 : 256; }
 constexpr int kTileBytes = kBM * kBK * 2;  // 16 KB: one operand tile of one stage
 
 // Two CTAs share an SM (96 KB of operand stages and 256 / 128 TMEM columns each), so that one CTA's
 // epilogue overlaps the other's main loop: 2 stages of 3 tiles for gate/up, 3 stages of 2 for down.
+// Both passes stage 3 x 16 KB per k-step (token tile + two 128-row weight tiles) in 2 stages.
 template <bool GATEUP>
-constexpr int tc_stages() { return GATEUP ? 2 : 3; }
+constexpr int tc_stages() { return 2; }
 
 template <bool GATEUP>
 constexpr size_t tc_smem_bytes() {
-  return 1024 /*alignment slack*/ + (size_t)tc_stages<GATEUP>() * (GATEUP ? 3 : 2) * kTileBytes + 256;
+  return 1024 /*alignment slack*/ + (size_t)tc_stages<GATEUP>() * 3 * kTileBytes + 256;
 }
 
 template <bool GATEUP>
@@ -45,8 +49,9 @@ prefill_ffn_kernel(const __grid_constant__ TcMaps maps, const TcGroup* __restric
                    float* __restrict__ yexp, int32_t* __restrict__ err) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  constexpr int kOperands = GATEUP ? 3 : 2;
+  constexpr int kOperands = 3;  // token tile, then gate + up tiles or the two halves of a 256-row down tile
   constexpr int kStages = tc_stages<GATEUP>();
+  constexpr int kBN = tc_bn<GATEUP>();
   unsigned char* stage_base = smem;  // [stage][operand][16 KB]
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * kOperands * kTileBytes);
   uint64_t* empty_bar = full_bar + kStages;
@@ -60,7 +65,7 @@ prefill_ffn_kernel(const __grid_constant__ TcMaps maps, const TcGroup* __restric
   const int K = GATEUP ? hidden : grp.inter;
   const int n_total = GATEUP ? grp.inter : hidden;
   const int k_tiles = K / kBK;
-  constexpr uint32_t kCols = GATEUP ? 256 : 128;
+  constexpr uint32_t kCols = 256;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -101,12 +106,15 @@ prefill_ffn_kernel(const __grid_constant__ TcMaps maps, const TcGroup* __restric
       mbar_arrive_expect_tx(&full_bar[s], kOperands * kTileBytes);
       const int k0 = kt * kBK;
       tma_load_2d(st, map_a, &full_bar[s], k0, row0);
+      // second weight tile: the up projection, or rows n0+128.. of the same down tile
+      const CUtensorMap* map_b_second = GATEUP ? map_b1 : map_b0;
+      const int n_second = GATEUP ? tile.n0 : tile.n0 + 128;
       if (shared_expert) {
         tma_load_2d(st + kTileBytes, map_b0, &full_bar[s], k0, tile.n0);
-        if (GATEUP) tma_load_2d(st + 2 * kTileBytes, map_b1, &full_bar[s], k0, tile.n0);
+        tma_load_2d(st + 2 * kTileBytes, map_b_second, &full_bar[s], k0, n_second);
       } else {
         tma_load_3d(st + kTileBytes, map_b0, &full_bar[s], k0, tile.n0, grp.line);
-        if (GATEUP) tma_load_3d(st + 2 * kTileBytes, map_b1, &full_bar[s], k0, tile.n0, grp.line);
+        tma_load_3d(st + 2 * kTileBytes, map_b_second, &full_bar[s], k0, n_second, grp.line);
       }
     }
   } else if (warp == 1 && lane == 0) {
@@ -128,7 +136,7 @@ prefill_ffn_kernel(const __grid_constant__ TcMaps maps, const TcGroup* __restric
         const uint64_t da = umma_desc_k_sw128(a_addr + k * 32);
         const uint64_t db0 = umma_desc_k_sw128(a_addr + kTileBytes + k * 32);
         const uint32_t accumulate = (kt > 0 || k > 0) ? 1u : 0u;
-        umma_bf16(tmem_base, da, db0, idesc, accumulate);
+        umma_bf16(tmem_base, da, db0, idesc, accumulate);  // down: one N = 256 MMA over both weight tiles
         if (GATEUP) {
           const uint64_t db1 = umma_desc_k_sw128(a_addr + 2 * kTileBytes + k * 32);
           umma_bf16(tmem_base + kBN, da, db1, idesc, accumulate);

@@ -34,55 +34,55 @@ __device__ __forceinline__ float dot_bf16_row(const uint4* __restrict__ w, const
   return acc;
 }
 
-// hidden[b, j] = relu(W1[j, :] . x[b, :] + b1[j]); one warp per hidden unit j. The unit's weight
-// row is read once per group of 8 sequences: 8 vectors of it sit in registers while the 8 token
-// rows (L1/L2 resident) stream past.
+// hidden[b, j] = relu(W1[j, :] . x[b, :] + b1[j]); one warp per hidden unit j. Up to 8 token rows
+// are staged in shared memory per pass, so a unit's weight row is read once per 8 sequences and
+// every inner load is a shared-memory read.
+constexpr int kFc1Tok = 8;
+
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 predictor_fc1_kernel(const __nv_bfloat16* __restrict__ x, int B, int H,
                      const __nv_bfloat16* __restrict__ w1, const float* __restrict__ b1, int D,
                      float* __restrict__ hidden) {
+  extern __shared__ __align__(16) unsigned char fc1_smem[];
+  uint4* xs = reinterpret_cast<uint4*>(fc1_smem);  // [kFc1Tok][H / 8]
   const int lane = threadIdx.x & 31;
   const int j = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
-  if (j >= D) return;
-  const uint4* wrow = reinterpret_cast<const uint4*>(w1 + (size_t)j * H);
-  const float bias = (b1 != nullptr) ? b1[j] : 0.f;
   const int nvec = H / 8;
-  for (int b0 = 0; b0 < B; b0 += 8) {
-    float acc[8];
+  const uint4* wrow = reinterpret_cast<const uint4*>(w1 + (size_t)min(j, D - 1) * H);
+  const float bias = (b1 != nullptr && j < D) ? b1[j] : 0.f;
+  for (int b0 = 0; b0 < B; b0 += kFc1Tok) {
+    const int nb = min(kFc1Tok, B - b0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nb * nvec; idx += blockDim.x)
+      xs[idx] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b0 * H) + idx);
+    __syncthreads();
+    float acc[kFc1Tok];
 #pragma unroll
-    for (int bb = 0; bb < 8; ++bb) acc[bb] = 0.f;
-    for (int v0 = lane; v0 < nvec; v0 += 32 * 8) {
-      uint4 wv[8];
+    for (int bb = 0; bb < kFc1Tok; ++bb) acc[bb] = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 wv = __ldg(wrow + v);
+      const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
-        if (v0 + 32 * u < nvec) wv[u] = __ldg(wrow + v0 + 32 * u);
+      for (int bb = 0; bb < kFc1Tok; ++bb) {
+        if (bb < nb) {
+          const uint4 xv = xs[bb * nvec + v];
+          const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
 #pragma unroll
-      for (int bb = 0; bb < 8; ++bb) {
-        if (b0 + bb >= B) break;
-        const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)(b0 + bb) * H);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          if (v0 + 32 * u < nvec) {
-            uint4 xv = __ldg(xrow + v0 + 32 * u);
-            const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv[u]);
-            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              float2 wf = __bfloat1622float2(wp[i]);
-              float2 xf = __bfloat1622float2(xp[i]);
-              acc[bb] = fmaf(wf.x, xf.x, acc[bb]);
-              acc[bb] = fmaf(wf.y, xf.y, acc[bb]);
-            }
+          for (int i = 0; i < 4; ++i) {
+            float2 wf = __bfloat1622float2(wp[i]);
+            float2 xf = __bfloat1622float2(xp[i]);
+            acc[bb] = fmaf(wf.x, xf.x, acc[bb]);
+            acc[bb] = fmaf(wf.y, xf.y, acc[bb]);
           }
         }
       }
     }
 #pragma unroll
-    for (int bb = 0; bb < 8; ++bb) {
+    for (int bb = 0; bb < kFc1Tok; ++bb) {
       float d = acc[bb];
 #pragma unroll
       for (int m = 16; m >= 1; m >>= 1) d += __shfl_xor_sync(0xffffffffu, d, m);
-      if (lane == 0 && b0 + bb < B) hidden[(size_t)(b0 + bb) * D + j] = fmaxf(d + bias, 0.f);
+      if (lane == 0 && bb < nb && j < D) hidden[(size_t)(b0 + bb) * D + j] = fmaxf(d + bias, 0.f);
     }
   }
 }
@@ -116,7 +116,12 @@ cudaError_t launch_predictor_mlp(const __nv_bfloat16* x, int B, int H, const __n
                                  const float* b1, int D, const __nv_bfloat16* w2, const float* b2,
                                  int E, float* hidden_scratch, float* scores, cudaStream_t s) {
   if (B <= 0) return cudaSuccess;
-  predictor_fc1_kernel<<<(D + kWarpsPerCta - 1) / kWarpsPerCta, kWarpsPerCta * 32, 0, s>>>(
+  const size_t fc1_smem = (size_t)kFc1Tok * H * 2;
+  if (fc1_smem > 48 * 1024) {
+    cudaError_t ae = cudaFuncSetAttribute(predictor_fc1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fc1_smem);
+    if (ae != cudaSuccess) return ae;
+  }
+  predictor_fc1_kernel<<<(D + kWarpsPerCta - 1) / kWarpsPerCta, kWarpsPerCta * 32, fc1_smem, s>>>(
       x, B, H, w1, b1, D, hidden_scratch);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;

@@ -807,6 +807,13 @@ __global__ void __launch_bounds__(256)
 plan_resident_kernel(const int32_t* __restrict__ counts, const int32_t* __restrict__ offsets,
                      const int32_t* __restrict__ slot_table, ResidentPlanArgs a, unsigned char* blob) {
   __shared__ int s_n, s_tg, s_td;
+  __shared__ int s_cnt[256], s_off[256], s_slot[256];  // staged so that the serial pass reads no global memory
+  for (int e = threadIdx.x; e < a.num_expert; e += blockDim.x) {
+    s_cnt[e] = counts[e];
+    s_off[e] = offsets[e];
+    s_slot[e] = slot_table[e];
+  }
+  __syncthreads();
   GroupDesc* desc = reinterpret_cast<GroupDesc*>(blob + a.off_desc);
   int32_t* t_gu = reinterpret_cast<int32_t*>(blob + a.off_tile_gu);
   int32_t* t_dn = reinterpret_cast<int32_t*>(blob + a.off_tile_dn);
@@ -824,12 +831,12 @@ plan_resident_kernel(const int32_t* __restrict__ counts, const int32_t* __restri
       td += dn_tiles;
     }
     for (int e = 0; e < a.num_expert; ++e) {
-      const int slot = slot_table[e];
-      if (counts[e] <= 0 || slot < 0) continue;
+      const int slot = s_slot[e];
+      if (s_cnt[e] <= 0 || slot < 0) continue;
       const unsigned char* line = a.pool_base + (size_t)slot * a.line_stride;
       GroupDesc d{};
       d.w_gate = line + a.off_gate; d.w_up = line + a.off_up; d.w_down = line + a.off_down;
-      d.row_start = offsets[e]; d.row_count = counts[e]; d.inter = a.inter;
+      d.row_start = s_off[e]; d.row_count = s_cnt[e]; d.inter = a.inter;
       d.tile_start_gu = tg; d.tile_start_dn = td;
       desc[n++] = d;
       tg += a.inter / kSplitTileGu;

@@ -89,7 +89,8 @@ int tc_build_maps(pm_ctx* c, const pm_layer_weights& w, int rows_cap, TcMaps* m)
   return PM_OK;
 }
 
-// Tiles of one segment: every 128-row block of every group times every 128-column block.
+// Tiles of one segment: every 128-row block of every group times every 128-column block of the
+// gate/up projections and every 256-column block of the down projection.
 void tc_plan(const std::vector<TcGroup>& groups, int hidden, std::vector<TcTile>* gu, std::vector<TcTile>* dn) {
   gu->clear();
   dn->clear();
@@ -97,7 +98,7 @@ void tc_plan(const std::vector<TcGroup>& groups, int hidden, std::vector<TcTile>
     const TcGroup& grp = groups[g];
     for (int m0 = 0; m0 < grp.row_count; m0 += 128) {
       for (int n0 = 0; n0 < grp.inter; n0 += 128) gu->push_back(TcTile{g, m0, n0, 0});
-      for (int n0 = 0; n0 < hidden; n0 += 128) dn->push_back(TcTile{g, m0, n0, 0});
+      for (int n0 = 0; n0 < hidden; n0 += 256) dn->push_back(TcTile{g, m0, n0, 0});
     }
   }
 }
