@@ -33,8 +33,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2")
     ap.add_argument("--num-predict", type=int, default=None, help="experts prefetched per predicted layer (0 = off)")
-    ap.add_argument("--cpu-sample-layers", type=int, default=2)
-    ap.add_argument("--cpu-sample-steps", type=int, default=12)
+    ap.add_argument("--cpu-sample-layers", type=int, default=4)
+    ap.add_argument("--cpu-sample-steps", type=int, default=96)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 

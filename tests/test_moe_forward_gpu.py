@@ -163,3 +163,35 @@ def test_forward_host_round_trip_and_errors(lib):
     with pytest.raises(_lib.PromoeError):
         c2.forward(0, dev_bf16(x))
     c2.close()
+
+
+def test_report_hidden_hook_path(lib):
+    """The hook route of the predictor (MoeLayerHook -> report_moe_layer_logits -> pm_report_hidden):
+    hidden states entering index l are given to the library, which runs the MLPs of that index on
+    the device, ranks on the host and prefetches; prefill-shaped input (seq > 1) is ignored."""
+    model = TinyModel(seed=12, L=4, E=12, H=128, I=64, k=3)
+    cache = model.make_cache(cache_rate=0.5, num_predict_expert_per_layer=3)
+    rng = np.random.default_rng(6)
+    D = 32
+    preds = {}
+    for src, dst in [(0, 0), (1, 1), (1, 2), (1, 3)]:  # default window for 4 layers
+        w1 = om.bf16_round((rng.standard_normal((D, model.H)) * 0.1).astype(np.float32))
+        w2 = om.bf16_round((rng.standard_normal((model.E, D)) * 0.3).astype(np.float32))
+        preds[(src, dst)] = (w1, None, w2, None)
+        cache.set_predictor(src, dst, dev_bf16(w1), None, dev_bf16(w2), None)
+    oc = sp.SequentialCache(model.L, model.E, model.k, cache_rate=0.5, num_predict=3)
+    cache.enable_event_log(True)
+    for x in model.hidden_stream(3, 4):
+        xd = dev_bf16(x)
+        cache.report_hidden(0, torch.zeros((3, 5, model.H), dtype=torch.bfloat16, device="cuda"))  # prefill: ignored
+        for l in range(model.L):
+            cache.report_hidden(l, xd.view(3, 1, model.H))
+            for (src, dst), (w1, b1, w2, b2) in sorted(preds.items()):
+                if src == l:
+                    oc.prefetch_layer(dst, om.rank_experts(om.predictor_scores(x, w1, b1, w2, b2), oc.num_predict))
+            y = cache.forward(l, xd)
+            ref_y, _, _ = model.oracle_forward(l, x, report_experts=lambda u: np.asarray(oc.report_layer(l, u)))
+            check_output(y, ref_y)
+    assert cache.events() == oc.events
+    assert cache.stats()["prefetch_miss"] > 0
+    cache.close()
