@@ -319,7 +319,10 @@ def run_ours(args, cfg):
     }
     if rank == 0 and not args.no_cpu_baseline and world == 1:
         threads = min(8, os.cpu_count() or 1)  # the reference pins torch to 8 threads (utils/__init__.py:343)
-        res = cpu_baseline(cfg, args.cpu_sample_layers, args.cpu_sample_steps, threads, stack=stack)
+        if cfg.quant4:  # the CPU path computes on the dequantised float32 masters: one layer is 5.6 GB
+            res = cpu_baseline(cfg, 1, min(args.cpu_sample_steps, 24), threads, stack=None)
+        else:
+            res = cpu_baseline(cfg, args.cpu_sample_layers, args.cpu_sample_steps, threads, stack=stack)
         line["cpu_baseline"] = {"value": res["tokens_per_s"], "unit": UNIT, "cores": threads, "kind": "port",
                                 "sample": res["sample"], "host_cores": os.cpu_count(), "torch": torch.__version__,
                                 "hit_rate": res["hit_rate"], "cpu_seconds": res["cpu_seconds"]}

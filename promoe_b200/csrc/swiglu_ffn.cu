@@ -517,7 +517,7 @@ struct TileCtx {
   int step_bytes;                            // distance between two of them
 };
 
-template <int NT, bool GATEUP>
+template <int NT, bool GATEUP, int WARPS>
 __device__ __forceinline__ void tile_setup(TileCtx<NT>& t, const GroupDesc* __restrict__ groups,
                                            const int32_t* __restrict__ tile_group, int tile,
                                            const __nv_bfloat16* bsrc, int ldb,
@@ -554,11 +554,11 @@ __device__ __forceinline__ void tile_setup(TileCtx<NT>& t, const GroupDesc* __re
   if (g_interleave_k) {
     // warp w takes k-steps w, w+8, ...: at any moment the 8 warps read neighbouring 64-byte pieces
     first = warp;
-    t.s_end = (steps - warp + kSplitWarps - 1) / kSplitWarps;
-    t.step_bytes = 64 * kSplitWarps;
+    t.s_end = (steps - warp + WARPS - 1) / WARPS;
+    t.step_bytes = 64 * WARPS;
   } else {
-    first = (warp * steps) / kSplitWarps;
-    t.s_end = ((warp + 1) * steps) / kSplitWarps - first;
+    first = (warp * steps) / WARPS;
+    t.s_end = ((warp + 1) * steps) / WARPS - first;
     t.step_bytes = 64;
   }
   t.s_begin = 0;
@@ -603,7 +603,7 @@ __device__ __forceinline__ void tile_compute(const TileCtx<NT>& t, int s0, const
   }
 }
 
-template <int NT, bool GATEUP>
+template <int NT, bool GATEUP, int WARPS>
 __device__ __forceinline__ void tile_finish(int rows, int m0, int row_start, float (&acc)[2][NT][4],
                                             float (*red)[2 * NT * 4][32], __nv_bfloat16* __restrict__ hbuf, int ld_h,
                                             float* __restrict__ yexp, int hidden) {
@@ -618,12 +618,12 @@ __device__ __forceinline__ void tile_finish(int rows, int m0, int row_start, flo
         acc[m][nt][i] = 0.f;
       }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < NT * 4 * 32; idx += kSplitThreads) {
+  for (int idx = threadIdx.x; idx < NT * 4 * 32; idx += WARPS * 32) {
     const int l = idx & 31, v = idx >> 5;
     const int nt = v >> 2, i = v & 3;
     float s0v = 0.f, s1v = 0.f;
 #pragma unroll
-    for (int w = 0; w < kSplitWarps; ++w) {
+    for (int w = 0; w < WARPS; ++w) {
       s0v += red[w][v][l];
       s1v += red[w][NT * 4 + v][l];
     }
@@ -645,7 +645,7 @@ __device__ __forceinline__ void tile_finish(int rows, int m0, int row_start, flo
 // Tiles blockIdx.x, blockIdx.x + gridDim.x, ... of one phase. The assignment is static, so the
 // next tile is known early: its first batch of loads is issued before the current tile is
 // reduced, which keeps DRAM requests in flight across tile boundaries.
-template <int NT, bool GATEUP, int DEPTH>
+template <int NT, bool GATEUP, int DEPTH, int WARPS>
 __device__ __forceinline__ void stream_tiles(const GroupDesc* __restrict__ groups,
                                              const int32_t* __restrict__ tile_group, int n_tiles,
                                              const __nv_bfloat16* bsrc, int ldb,
@@ -665,7 +665,7 @@ __device__ __forceinline__ void stream_tiles(const GroupDesc* __restrict__ group
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[m][nt][i] = 0.f;
-  tile_setup<NT, GATEUP>(t, groups, tile_group, tile, bsrc, ldb, row_token, hidden);
+  tile_setup<NT, GATEUP, WARPS>(t, groups, tile_group, tile, bsrc, ldb, row_token, hidden);
   tile_issue<NT, DEPTH, COH>(t, t.s_begin, a, b);
   while (true) {
     for (int s0 = t.s_begin; s0 < t.s_end;) {
@@ -677,36 +677,36 @@ __device__ __forceinline__ void stream_tiles(const GroupDesc* __restrict__ group
     const int next = tile + gridDim.x;
     const bool has_next = next < n_tiles;
     if (has_next) {
-      tile_setup<NT, GATEUP>(t, groups, tile_group, next, bsrc, ldb, row_token, hidden);
+      tile_setup<NT, GATEUP, WARPS>(t, groups, tile_group, next, bsrc, ldb, row_token, hidden);
       tile_issue<NT, DEPTH, COH>(t, t.s_begin, a, b);
     }
-    tile_finish<NT, GATEUP>(rows, m0, row_start, acc, red, hbuf, ld_h, yexp, hidden);
+    tile_finish<NT, GATEUP, WARPS>(rows, m0, row_start, acc, red, hbuf, ld_h, yexp, hidden);
     if (!has_next) break;
     tile = next;
   }
 }
 
-template <int NT, int DEPTH>
-__global__ void __launch_bounds__(kSplitThreads, 2)
+template <int NT, int DEPTH, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 16 / WARPS)
 grouped_ffn_fused_kernel(const GroupDesc* __restrict__ groups, const int32_t* __restrict__ tile_gu,
                          const int32_t* __restrict__ tile_dn, int tiles_gu, int tiles_dn, int* counters,
                          const __nv_bfloat16* __restrict__ x, int hidden,
                          const int32_t* __restrict__ row_token, __nv_bfloat16* hbuf, int ld_h,
                          float* __restrict__ yexp, const int32_t* __restrict__ dev_tiles) {
-  __shared__ float red[kSplitWarps][2 * NT * 4][32];
+  __shared__ float red[WARPS][2 * NT * 4][32];
   (void)counters;
   if (dev_tiles != nullptr) {  // plan built on the device: the tile counts live there too
     tiles_gu = dev_tiles[0];
     tiles_dn = dev_tiles[1];
   }
-  stream_tiles<NT, true, DEPTH>(groups, tile_gu, tiles_gu, x, hidden, row_token, hidden, hbuf, ld_h, yexp, red);
+  stream_tiles<NT, true, DEPTH, WARPS>(groups, tile_gu, tiles_gu, x, hidden, row_token, hidden, hbuf, ld_h, yexp, red);
   __threadfence();
   cooperative_groups::this_grid().sync();
-  stream_tiles<NT, false, DEPTH>(groups, tile_dn, tiles_dn, hbuf, ld_h, row_token, hidden, nullptr, ld_h, yexp, red);
+  stream_tiles<NT, false, DEPTH, WARPS>(groups, tile_dn, tiles_dn, hbuf, ld_h, row_token, hidden, nullptr, ld_h, yexp, red);
 }
 
 // Resident grid of the fused kernel on the current device (0 if cooperative launch is unavailable).
-template <int NT, int DEPTH>
+template <int NT, int DEPTH, int WARPS>
 int fused_grid_size() {
   static int cached[64] = {};
   int dev = 0;
@@ -716,7 +716,7 @@ int fused_grid_size() {
   cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (!coop || sms <= 0 ||
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, grouped_ffn_fused_kernel<NT, DEPTH>, kSplitThreads, 0) !=
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, grouped_ffn_fused_kernel<NT, DEPTH, WARPS>, WARPS * 32, 0) !=
           cudaSuccess ||
       per_sm <= 0) {
     cached[dev] = -1;
@@ -726,12 +726,12 @@ int fused_grid_size() {
   return cached[dev];
 }
 
-template <int NT, int DEPTH>
-cudaError_t launch_fused(const GroupDesc* groups, const int32_t* t_gu, const int32_t* t_dn, int tiles_gu,
+template <int NT, int DEPTH, int WARPS>
+cudaError_t launch_fused_w(const GroupDesc* groups, const int32_t* t_gu, const int32_t* t_dn, int tiles_gu,
                          int tiles_dn, int* counters, const __nv_bfloat16* x, int hidden,
                          const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s,
                          const int32_t* dev_tiles = nullptr) {
-  int grid = fused_grid_size<NT, DEPTH>();
+  int grid = fused_grid_size<NT, DEPTH, WARPS>();
   if (grid <= 0) return cudaErrorNotSupported;
   static bool flag_set = false;
   if (!flag_set) {
@@ -745,8 +745,35 @@ cudaError_t launch_fused(const GroupDesc* groups, const int32_t* t_gu, const int
   void* args[] = {(void*)&groups, (void*)&t_gu, (void*)&t_dn, (void*)&tiles_gu, (void*)&tiles_dn, (void*)&counters,
                   (void*)&x, (void*)&hidden, (void*)&row_token, (void*)&hbuf, (void*)&ld_h, (void*)&yexp,
                   (void*)&dev_tiles};
-  return cudaLaunchCooperativeKernel((const void*)grouped_ffn_fused_kernel<NT, DEPTH>, dim3(grid), dim3(kSplitThreads),
-                                     args, 0, s);
+  return cudaLaunchCooperativeKernel((const void*)grouped_ffn_fused_kernel<NT, DEPTH, WARPS>, dim3(grid),
+                                     dim3(WARPS * 32), args, 0, s);
+}
+
+// CTA width of the fused kernel: 8 warps x 2 CTAs per SM, or (PM_FFN_WARPS=16) 16 warps x 1.
+inline int fused_warps() {
+  static int w = 0;
+  if (w == 0) {
+    const char* env = std::getenv("PM_FFN_WARPS");
+    w = (env != nullptr && std::atoi(env) == 16) ? 16 : 8;
+  }
+  return w;
+}
+
+template <int NT, int DEPTH>
+cudaError_t launch_fused(const GroupDesc* groups, const int32_t* t_gu, const int32_t* t_dn, int tiles_gu,
+                         int tiles_dn, int* counters, const __nv_bfloat16* x, int hidden,
+                         const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s,
+                         const int32_t* dev_tiles = nullptr) {
+  if (fused_warps() == 16)
+    return launch_fused_w<NT, DEPTH, 16>(groups, t_gu, t_dn, tiles_gu, tiles_dn, counters, x, hidden, row_token, hbuf,
+                                         ld_h, yexp, s, dev_tiles);
+  return launch_fused_w<NT, DEPTH, 8>(groups, t_gu, t_dn, tiles_gu, tiles_dn, counters, x, hidden, row_token, hbuf,
+                                      ld_h, yexp, s, dev_tiles);
+}
+
+template <int NT, int DEPTH>
+int fused_grid_size_any() {
+  return fused_warps() == 16 ? fused_grid_size<NT, DEPTH, 16>() : fused_grid_size<NT, DEPTH, 8>();
 }
 
 template <int NT, int NMAT>
@@ -877,7 +904,7 @@ cudaError_t launch_resident_ffn(const int32_t* counts, const int32_t* offsets, c
 
 bool resident_ffn_available(int max_rows) {
   if (max_rows > kSplitMaxRows) return false;
-  return (max_rows <= 8 ? fused_grid_size<1, 4>() : fused_grid_size<2, 2>()) > 0;
+  return (max_rows <= 8 ? fused_grid_size_any<1, 4>() : fused_grid_size_any<2, 2>()) > 0;
 }
 
 cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& info, int quant4,

@@ -38,6 +38,7 @@ class StackConfig:
     cache_rate: float
     predictor_width: int = 0   # 0 = no predictor
     model_id: str = ""
+    quant4: bool = False       # routed experts stored as uint4 group-128 (scale/zero fp16)
 
 
 CONFIGS = {
@@ -47,6 +48,9 @@ CONFIGS = {
     # configs[1]: Qwen1.5-MoE-A2.7B-shaped 24-layer stack with the next-layer predictor
     "c2": StackConfig("qwen1.5-moe-a2.7b-stack", 24, 60, 4, 2048, 1408, 5632, True, False, 8, 128, 0.375,
                       predictor_width=512, model_id="Qwen/Qwen1.5-MoE-A2.7B-Chat"),
+    # configs[2]: Mixtral-8x7B-shaped 32-layer stack with uint4 group-128 experts
+    "c3": StackConfig("mixtral-8x7b-int4-stack", 32, 8, 2, 4096, 14336, 0, False, True, 16, 128, 0.5,
+                      model_id="mistralai/Mixtral-8x7B-Instruct-v0.1", quant4=True),
     # configs[3]: Qwen2-57B-A14B-shaped 28-layer stack (expert parallel over 2/4/8 GPUs)
     "c4": StackConfig("qwen2-57b-a14b-stack", 28, 64, 8, 3584, 2560, 20480, True, False, 64, 64, 0.375,
                       model_id="Qwen/Qwen2-57B-A14B-Instruct"),
@@ -103,9 +107,14 @@ class SyntheticStack:
         conf = dict(num_expert_per_token=cfg.top_k, cache_rate=repr(cfg.cache_rate), model_arch_string=cfg.model_id)
         conf.update(cache_config)
         self.cache = ExpertCache(L, self.n_local, **conf)
-        self.cache.set_param_list(["gate_proj.weight", "up_proj.weight", "down_proj.weight"])
         H, I = cfg.hidden, cfg.inter
-        sizes = [I * H * 2, I * H * 2, H * I * 2]
+        if cfg.quant4:
+            self.cache.set_param_list(["w1.qweight", "w1.scale_zero", "w3.qweight", "w3.scale_zero",
+                                       "w2.qweight", "w2.scale_zero"])
+            sizes = [I * H // 2, I * H // 128 * 4] * 3
+        else:
+            self.cache.set_param_list(["gate_proj.weight", "up_proj.weight", "down_proj.weight"])
+            sizes = [I * H * 2, I * H * 2, H * I * 2]
         for l in range(L):
             for e in range(self.n_local):
                 self.cache.register_expert_sizes(l, e, sizes)
@@ -113,6 +122,9 @@ class SyntheticStack:
         self.gate_w, self.gate_bias, self.shared, self.shared_gate_w = [], [], [], []
         for l in range(L):
             for e in range(self.n_local):
+                if cfg.quant4:
+                    self._fill_quant4_expert(l, e)
+                    continue
                 for p, (name, shape) in enumerate((("gate", (I, H)), ("up", (I, H)), ("down", (H, I)))):
                     w = _randn(shape, seed_for(cfg.name, l, self.e0 + e, name), self.device)
                     addr, n = self.cache.host_record(l, e, p)
@@ -129,6 +141,29 @@ class SyntheticStack:
         self.cache.build_slab()
         self.predictors = {}
 
+    def _fill_quant4_expert(self, l: int, e: int):
+        """uint4 experts of the synthetic stack: N(0, 0.02) masters quantised on the GPU per group of
+        128 (asymmetric, fp16 scale and zero) and packed in the layout of promoe_b200/quant4.py."""
+        cfg = self.cfg
+        for m, (name, shape) in enumerate((("gate", (cfg.inter, cfg.hidden)), ("up", (cfg.inter, cfg.hidden)),
+                                           ("down", (cfg.hidden, cfg.inter)))):
+            w = _randn(shape, seed_for(cfg.name, l, self.e0 + e, name), self.device, dtype=torch.float32)
+            g = w.view(shape[0], shape[1] // 128, 128)
+            lo, hi = g.amin(dim=2), g.amax(dim=2)
+            scale = ((hi - lo) / 15.0).clamp_min(1e-8).to(torch.float16)
+            zero = (-lo / scale.float()).to(torch.float16)
+            q = torch.clamp(torch.round(g / scale.float()[..., None] + zero.float()[..., None]), 0, 15).to(torch.int32)
+            q8 = q.view(shape[0], shape[1] // 8, 8)
+            word = torch.zeros((shape[0], shape[1] // 8), dtype=torch.int32, device=self.device)
+            for j in range(4):
+                word |= q8[:, :, 2 * j] << (4 * j)
+                word |= q8[:, :, 2 * j + 1] << (4 * j + 16)
+            sz = torch.stack([scale, zero], dim=-1).contiguous()
+            addr, n = self.cache.host_record(l, e, 2 * m)
+            _host_tensor(addr, n).copy_(word.view(torch.int16).reshape(-1))
+            addr, n = self.cache.host_record(l, e, 2 * m + 1)
+            _host_tensor(addr, n).copy_(sz.view(torch.int16).reshape(-1))
+
     def install_layers(self):
         """Full-width routing on this GPU (single-GPU use: local experts == all experts)."""
         cfg = self.cfg
@@ -136,7 +171,7 @@ class SyntheticStack:
             self.cache.set_layer_weights(l, self.gate_w[l], cfg.inter, cfg.top_k, cfg.norm_topk, 1.0,
                                          gate_bias=self.gate_bias[l],
                                          shared=self.shared[l] if cfg.shared_inter else None,
-                                         shared_gate_w=self.shared_gate_w[l])
+                                         shared_gate_w=self.shared_gate_w[l], quant4=cfg.quant4)
 
     def install_routed_only(self):
         """Expert-parallel rank: the cache serves rows routed elsewhere (no router in the context)."""
