@@ -16,7 +16,7 @@ It restates, in plain Python, the single-threaded core of the reference's cache:
     always keeps up.
 
 Pinning. tests/golden/policy_ref_*.json hold event logs produced by the reference's own
-compiled classes (oracle/ref_build builds them from /root/reference into oracle/_ref/);
+compiled classes (oracle/ref_build builds them from the reference checkout into oracle/_ref/);
 tests/test_oracle_policy.py replays them through this file.
 """
 from __future__ import annotations

@@ -1,9 +1,9 @@
 """Writes tests/golden/policy_ref_*.json: cache event logs produced by the REFERENCE's own
-compiled classes (oracle/_ref/ref_policy, built by `make -C oracle/ref_build` from
-/root/reference) on seeded synthetic request streams. The fixtures pin oracle/srs_policy.py
+compiled classes (oracle/_ref/ref_policy, built by `make -C oracle/ref_build` from the
+reference checkout) on seeded synthetic request streams. The fixtures pin oracle/srs_policy.py
 (tests/test_oracle_policy.py) and, through it, the product's cache engine.
 
-Run from the repository root, in the container that holds /root/reference:
+Run from the repository root, on a machine that holds the reference checkout:
     make -C oracle/ref_build && python tests/golden/make_policy_golden.py
 """
 from __future__ import annotations
