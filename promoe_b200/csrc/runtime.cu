@@ -507,7 +507,7 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
       }
       return cudaEventCreate(e);
     };
-    sample.fused = c->fused_ffn && info.max_rows <= kSplitMaxRows;
+    sample.fused = c->fused_ffn && !w.quant4 && info.max_rows <= kSplitMaxRows;
     PM_CUDA(take_event(&sample.e0));
     if (!sample.fused) PM_CUDA(take_event(&sample.e1));
     PM_CUDA(take_event(&sample.e2));
@@ -526,7 +526,7 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
     PM_CUDA(cudaEventRecord(sample.e2, s));
     c->ffn_samples.push_back(sample);
   }
-  c->kernel_launches += (c->fused_ffn && info.max_rows <= kSplitMaxRows) ? 1 : 2;
+  c->kernel_launches += (c->fused_ffn && !w.quant4 && info.max_rows <= kSplitMaxRows) ? 1 : 2;
   *desc_used += align_up(info.blob_bytes(), 256);
   if (!seg->lines.empty()) {
     cudaEvent_t ev = next_seg_event(c);
