@@ -514,49 +514,69 @@ struct TileCtx {
   int step_bytes;                            // distance between two of them
 };
 
-template <int NT, bool GATEUP, int WARPS>
-__device__ __forceinline__ void tile_setup(TileCtx<NT>& t, const GroupDesc* __restrict__ groups,
-                                           const int32_t* __restrict__ tile_group, int tile,
-                                           const __nv_bfloat16* bsrc, int ldb,
-                                           const int32_t* __restrict__ row_token, int hidden) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, q = lane & 3;
-  const GroupDesc grp = groups[tile_group[tile]];
-  const int tile_local = tile - (GATEUP ? grp.tile_start_gu : grp.tile_start_dn);
-  const int K = GATEUP ? hidden : grp.inter;
-  const size_t row_bytes = (size_t)K * 2;
-  t.rows = grp.row_count;
-  t.row_start = grp.row_start;
-  t.m0 = tile_local * (GATEUP ? 16 : 32);
-  if (GATEUP) {
-    const unsigned char* w0 = reinterpret_cast<const unsigned char*>(grp.w_gate);
-    const unsigned char* w1 = reinterpret_cast<const unsigned char*>(grp.w_up);
-    t.a_ptr[0] = w0 + (size_t)(t.m0 + g) * row_bytes + q * 16;
-    t.a_ptr[1] = w0 + (size_t)(t.m0 + g + 8) * row_bytes + q * 16;
-    t.a_ptr[2] = w1 + (size_t)(t.m0 + g) * row_bytes + q * 16;
-    t.a_ptr[3] = w1 + (size_t)(t.m0 + g + 8) * row_bytes + q * 16;
-  } else {
-    const unsigned char* w0 = reinterpret_cast<const unsigned char*>(grp.w_down);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) t.a_ptr[j] = w0 + (size_t)(t.m0 + g + 8 * j) * row_bytes + q * 16;
-  }
+// What a tile needs from its chunk descriptor and the row table. It is fetched one tile ahead, so
+// that the two dependent loads (descriptor, then token row numbers) never stall the load stream.
+template <int NT>
+struct TileMeta {
+  const unsigned char* w0;
+  const unsigned char* w1;
+  int row_start, rows, inter, tile_start;
+  int src_row[NT];
+};
+
+template <int NT, bool GATEUP>
+__device__ __forceinline__ void meta_load_desc(TileMeta<NT>& m, const GroupDesc* __restrict__ groups, int gi) {
+  const GroupDesc* d = groups + gi;
+  m.w0 = reinterpret_cast<const unsigned char*>(GATEUP ? d->w_gate : d->w_down);
+  m.w1 = reinterpret_cast<const unsigned char*>(GATEUP ? d->w_up : d->w_down);
+  m.row_start = d->row_start;
+  m.rows = d->row_count;
+  m.inter = d->inter;
+  m.tile_start = GATEUP ? d->tile_start_gu : d->tile_start_dn;
+}
+
+template <int NT, bool GATEUP>
+__device__ __forceinline__ void meta_load_rows(TileMeta<NT>& m, const int32_t* __restrict__ row_token) {
+  const int g = (threadIdx.x & 31) >> 2;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int n = nt * 8 + g;
-    t.b_ok[nt] = n < t.rows;
-    const int src_row = t.b_ok[nt] ? (GATEUP ? row_token[grp.row_start + n] : grp.row_start + n) : 0;
-    t.b_ptr[nt] = reinterpret_cast<const unsigned char*>(bsrc + (size_t)src_row * ldb) + q * 16;
+    m.src_row[nt] = (n < m.rows) ? (GATEUP ? row_token[m.row_start + n] : m.row_start + n) : -1;
   }
-  const int steps = K / 32;
+}
+
+template <int NT, bool GATEUP, int WARPS>
+__device__ __forceinline__ void tile_setup(TileCtx<NT>& t, const TileMeta<NT>& m, int tile,
+                                           const __nv_bfloat16* bsrc, int ldb, int hidden) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, q = lane & 3;
+  const int tile_local = tile - m.tile_start;
+  const int K = GATEUP ? hidden : m.inter;
+  const size_t row_bytes = (size_t)K * 2;
+  t.rows = m.rows;
+  t.row_start = m.row_start;
+  t.m0 = tile_local * (GATEUP ? 16 : 32);
   // Every warp takes a contiguous range of k-steps (interleaving them across warps, w, w+8, ...,
   // measured 6 % slower: longer contiguous runs per warp suit DRAM better).
+  const int steps = K / 32;
   const int first = (warp * steps) / WARPS;
   t.s_end = ((warp + 1) * steps) / WARPS - first;
-  t.step_bytes = 64;
   t.s_begin = 0;
+  t.step_bytes = 64;
+  const size_t col = (size_t)first * 64 + q * 16;
+  if (GATEUP) {
+    t.a_ptr[0] = m.w0 + (size_t)(t.m0 + g) * row_bytes + col;
+    t.a_ptr[1] = m.w0 + (size_t)(t.m0 + g + 8) * row_bytes + col;
+    t.a_ptr[2] = m.w1 + (size_t)(t.m0 + g) * row_bytes + col;
+    t.a_ptr[3] = m.w1 + (size_t)(t.m0 + g + 8) * row_bytes + col;
+  } else {
 #pragma unroll
-  for (int j = 0; j < 4; ++j) t.a_ptr[j] += (size_t)first * 64;
+    for (int j = 0; j < 4; ++j) t.a_ptr[j] = m.w0 + (size_t)(t.m0 + g + 8 * j) * row_bytes + col;
+  }
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) t.b_ptr[nt] += (size_t)first * 64;
+  for (int nt = 0; nt < NT; ++nt) {
+    t.b_ok[nt] = m.src_row[nt] >= 0;
+    t.b_ptr[nt] = reinterpret_cast<const unsigned char*>(bsrc + (size_t)max(m.src_row[nt], 0) * ldb) + col;
+  }
 }
 
 template <int NT, int DEPTH, bool COHERENT_B>
@@ -656,24 +676,40 @@ __device__ __forceinline__ void stream_tiles(const GroupDesc* __restrict__ group
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[m][nt][i] = 0.f;
-  tile_setup<NT, GATEUP, WARPS>(t, groups, tile_group, tile, bsrc, ldb, row_token, hidden);
+  const int stride = gridDim.x;
+  TileMeta<NT> m;
+  meta_load_desc<NT, GATEUP>(m, groups, tile_group[tile]);  // only the first tile pays for these round trips
+  meta_load_rows<NT, GATEUP>(m, row_token);
+  tile_setup<NT, GATEUP, WARPS>(t, m, tile, bsrc, ldb, hidden);
   tile_issue<NT, DEPTH, COH>(t, t.s_begin, a, b);
+  int next = tile + stride;
+  int gi_next = (next < n_tiles) ? tile_group[next] : 0;
   while (true) {
+    const bool has_next = next < n_tiles;
+    if (has_next) meta_load_desc<NT, GATEUP>(m, groups, gi_next);  // arrives while this tile streams
+    const int next2 = next + stride;
+    const int gi_next2 = (next2 < n_tiles) ? tile_group[next2] : 0;
+    bool rows_loaded = false;
     for (int s0 = t.s_begin; s0 < t.s_end;) {
       tile_compute<NT, DEPTH>(t, s0, a, b, acc);
+      if (has_next && !rows_loaded) {  // the descriptor is here by now: fetch the token row numbers
+        meta_load_rows<NT, GATEUP>(m, row_token);
+        rows_loaded = true;
+      }
       s0 += DEPTH;
       if (s0 < t.s_end) tile_issue<NT, DEPTH, COH>(t, s0, a, b);
     }
+    if (has_next && !rows_loaded) meta_load_rows<NT, GATEUP>(m, row_token);
     const int rows = t.rows, m0 = t.m0, row_start = t.row_start;
-    const int next = tile + gridDim.x;
-    const bool has_next = next < n_tiles;
     if (has_next) {
-      tile_setup<NT, GATEUP, WARPS>(t, groups, tile_group, next, bsrc, ldb, row_token, hidden);
+      tile_setup<NT, GATEUP, WARPS>(t, m, next, bsrc, ldb, hidden);
       tile_issue<NT, DEPTH, COH>(t, t.s_begin, a, b);
     }
     tile_finish<NT, GATEUP, WARPS>(rows, m0, row_start, acc, red, hbuf, ld_h, yexp, hidden);
     if (!has_next) break;
     tile = next;
+    next = next2;
+    gi_next = gi_next2;
   }
 }
 
