@@ -210,6 +210,8 @@ def run_ours(args, cfg):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the MoE path has no CPU fallback")
     torch.cuda.set_device(local_rank)
+    from promoe_b200.numa import bind_to_gpu_numa_node
+    numa = bind_to_gpu_numa_node(local_rank)  # before any pinned memory is allocated
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     dev = torch.device("cuda", local_rank)
@@ -321,7 +323,7 @@ def run_ours(args, cfg):
                   "prefetch_miss": s1["prefetch_miss"] - s0["prefetch_miss"],
                   "h2d_gb_per_step": (s1["h2d_bytes"] - s0["h2d_bytes"]) / K / 1e9,
                   "h2d_gbs_effective": (s1["h2d_bytes"] - s0["h2d_bytes"]) / (ms_total / 1e3) / 1e9,
-                  "slab_impl": cache.get("slab_impl")},
+                  "slab_impl": cache.get("slab_impl"), "numa": numa},
     }
     if rank == 0 and not args.no_cpu_baseline and world == 1:
         threads = min(8, os.cpu_count() or 1)  # the reference pins torch to 8 threads (utils/__init__.py:343)

@@ -650,7 +650,8 @@ __device__ __forceinline__ void tile_finish(int rows, int m0, int row_start, flo
       yexp[r * hidden + m + 16] = s1v;
     }
   }
-  __syncthreads();  // `red` is free again before the next tile's partial sums arrive
+  // no trailing barrier: the caller alternates between two reduction buffers, and the barrier above of
+  // the NEXT tile orders this tile's reads before the writes of the tile after it
 }
 
 // Tiles blockIdx.x, blockIdx.x + gridDim.x, ... of one phase. The assignment is static, so the
@@ -662,8 +663,9 @@ __device__ __forceinline__ void stream_tiles(const GroupDesc* __restrict__ group
                                              const __nv_bfloat16* bsrc, int ldb,
                                              const int32_t* __restrict__ row_token, int hidden,
                                              __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp,
-                                             float (*red)[2 * NT * 4][32]) {
+                                             float (*red2)[WARPS][2 * NT * 4][32]) {
   constexpr bool COH = !GATEUP;  // the down phase reads rows other CTAs wrote in this kernel
+  int buf = 0;
   int tile = blockIdx.x;
   if (tile >= n_tiles) return;
   TileCtx<NT> t;
@@ -705,7 +707,8 @@ __device__ __forceinline__ void stream_tiles(const GroupDesc* __restrict__ group
       tile_setup<NT, GATEUP, WARPS>(t, m, next, bsrc, ldb, hidden);
       tile_issue<NT, DEPTH, COH>(t, t.s_begin, a, b);
     }
-    tile_finish<NT, GATEUP, WARPS>(rows, m0, row_start, acc, red, hbuf, ld_h, yexp, hidden);
+    tile_finish<NT, GATEUP, WARPS>(rows, m0, row_start, acc, red2[buf], hbuf, ld_h, yexp, hidden);
+    buf ^= 1;
     if (!has_next) break;
     tile = next;
     next = next2;
@@ -720,7 +723,7 @@ grouped_ffn_fused_kernel(const GroupDesc* __restrict__ groups, const int32_t* __
                          const __nv_bfloat16* __restrict__ x, int hidden,
                          const int32_t* __restrict__ row_token, __nv_bfloat16* hbuf, int ld_h,
                          float* __restrict__ yexp, const int32_t* __restrict__ dev_tiles) {
-  __shared__ float red[WARPS][2 * NT * 4][32];
+  __shared__ float red[2][WARPS][2 * NT * 4][32];  // two reduction buffers, used alternately
   (void)counters;
   if (dev_tiles != nullptr) {  // plan built on the device: the tile counts live there too
     tiles_gu = dev_tiles[0];

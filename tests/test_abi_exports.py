@@ -46,3 +46,10 @@ def test_product_never_imports_the_oracle():
         assert not re.search(r"^\s*(from|import)\s+oracle\b", p.read_text(), flags=re.M), p
     for p in (ROOT / "promoe_b200" / "csrc").glob("*"):
         assert "oracle/" not in p.read_text(), p
+
+
+def test_numa_helpers():
+    from promoe_b200 import numa
+    assert numa._cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert numa._cpulist("") == set()
+    assert numa.gpu_numa_node(0) is None or isinstance(numa.gpu_numa_node(0), int)  # no GPU here: None
