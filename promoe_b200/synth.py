@@ -93,6 +93,24 @@ def _host_tensor(addr: int, nbytes: int) -> torch.Tensor:
     return torch.from_numpy(np.ctypeslib.as_array(buf))
 
 
+def quantize_pack_torch(w: torch.Tensor):
+    """Same quantiser and packing as promoe_b200.quant4.quantize_pack, on whatever device `w` lives:
+    returns (int32 words [rows, K/8], float16 {scale, zero} [rows, K/128, 2])."""
+    rows, K = w.shape
+    g = w.float().view(rows, K // 128, 128)
+    lo, hi = g.amin(dim=2), g.amax(dim=2)
+    scale = ((hi - lo) / 15.0).clamp_min(1e-8).to(torch.float16)
+    zero = (-lo / scale.float()).to(torch.float16)
+    q = torch.clamp(torch.round(g / scale.float()[..., None] + zero.float()[..., None]), 0, 15).to(torch.int64)
+    q8 = q.view(rows, K // 8, 8)
+    word = torch.zeros((rows, K // 8), dtype=torch.int64, device=w.device)
+    for j in range(4):
+        word |= q8[:, :, 2 * j] << (4 * j)
+        word |= q8[:, :, 2 * j + 1] << (4 * j + 16)
+    word = torch.where(word >= 2 ** 31, word - 2 ** 32, word).to(torch.int32)  # same bits, signed container
+    return word, torch.stack([scale, zero], dim=-1).contiguous()
+
+
 class SyntheticStack:
     """Builds the cache, the pinned expert records and the resident weights of one config."""
 
@@ -142,23 +160,13 @@ class SyntheticStack:
         self.predictors = {}
 
     def _fill_quant4_expert(self, l: int, e: int):
-        """uint4 experts of the synthetic stack: N(0, 0.02) masters quantised on the GPU per group of
-        128 (asymmetric, fp16 scale and zero) and packed in the layout of promoe_b200/quant4.py."""
+        """uint4 experts of the synthetic stack: N(0, 0.02) masters quantised on the GPU and packed in the
+        layout of promoe_b200/quant4.py, written straight into the pinned record."""
         cfg = self.cfg
         for m, (name, shape) in enumerate((("gate", (cfg.inter, cfg.hidden)), ("up", (cfg.inter, cfg.hidden)),
                                            ("down", (cfg.hidden, cfg.inter)))):
             w = _randn(shape, seed_for(cfg.name, l, self.e0 + e, name), self.device, dtype=torch.float32)
-            g = w.view(shape[0], shape[1] // 128, 128)
-            lo, hi = g.amin(dim=2), g.amax(dim=2)
-            scale = ((hi - lo) / 15.0).clamp_min(1e-8).to(torch.float16)
-            zero = (-lo / scale.float()).to(torch.float16)
-            q = torch.clamp(torch.round(g / scale.float()[..., None] + zero.float()[..., None]), 0, 15).to(torch.int32)
-            q8 = q.view(shape[0], shape[1] // 8, 8)
-            word = torch.zeros((shape[0], shape[1] // 8), dtype=torch.int32, device=self.device)
-            for j in range(4):
-                word |= q8[:, :, 2 * j] << (4 * j)
-                word |= q8[:, :, 2 * j + 1] << (4 * j + 16)
-            sz = torch.stack([scale, zero], dim=-1).contiguous()
+            word, sz = quantize_pack_torch(w)
             addr, n = self.cache.host_record(l, e, 2 * m)
             _host_tensor(addr, n).copy_(word.view(torch.int16).reshape(-1))
             addr, n = self.cache.host_record(l, e, 2 * m + 1)

@@ -91,3 +91,23 @@ def test_bf16_round_trip():
     assert np.all(np.abs(r - a) <= np.abs(a) * 2.0 ** -8)
     import torch
     assert np.array_equal(r, torch.from_numpy(a).to(torch.bfloat16).float().numpy())
+
+
+def test_uint4_packers_agree():
+    """The numpy packer, the torch packer of the synthetic stacks and the oracle's independent unpacker
+    describe the same layout."""
+    import torch
+    from oracle import quant4 as oq
+    from promoe_b200 import quant4 as pq
+    from promoe_b200.synth import quantize_pack_torch
+    rng = np.random.default_rng(5)
+    w = (rng.standard_normal((12, 384)) * 0.02).astype(np.float32)
+    packed, sz = pq.quantize_pack(w)
+    word, sz_t = quantize_pack_torch(torch.from_numpy(w))
+    assert np.array_equal(word.numpy().view(np.uint8).reshape(12, -1), packed)
+    assert np.array_equal(sz_t.numpy(), sz)
+    deq = oq.dequantize(packed, sz)
+    assert np.abs(deq - w).max() <= np.abs(w).max() / 15 + 1e-6      # within one quantisation step
+    q, s, z = pq.quantize(w)
+    ref = (q.reshape(12, 3, 128).astype(np.float32) - z.astype(np.float32)[..., None]) * s.astype(np.float32)[..., None]
+    assert np.array_equal(deq, ref.reshape(12, 384))
