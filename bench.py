@@ -39,6 +39,9 @@ def parse_args():
     ap.add_argument("--cpu-sample-layers", type=int, default=4)
     ap.add_argument("--cpu-sample-steps", type=int, default=96)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cache-rate", type=float, default=None, help="override the configuration's cache_rate")
+    ap.add_argument("--prefill-tokens", type=int, default=0,
+                    help="run one prefill of this many tokens through the stack first and report its time")
     return ap.parse_args()
 
 
@@ -260,6 +263,27 @@ def run_ours(args, cfg):
             dist.barrier()
         torch.cuda.synchronize()
 
+    prefill = None
+    if args.prefill_tokens > 0 and ep is None:
+        # one prompt pass: every layer sees prefill_tokens i.i.d. N(0,1) rows (seq_len > 1: no prediction)
+        g = torch.Generator(device=dev).manual_seed(synth.seed_for(cfg.name, "prefill"))
+        xp = torch.randn((args.prefill_tokens, H), generator=g, device=dev).to(torch.bfloat16)
+        yp = torch.empty_like(xp)
+        cache.set("seq_len", args.prefill_tokens)
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        p0.record()
+        for l in range(L):
+            cache.forward(l, xp, out=yp)
+        p1.record()
+        barrier()
+        cache.set("seq_len", 1)
+        pms = p0.elapsed_time(p1)
+        st_p = cache.stats()
+        prefill = {"tokens": args.prefill_tokens, "ms": pms, "tokens_per_s": args.prefill_tokens / (pms / 1e3),
+                   "tensor_core_launches": int(cache.get("tc_launches")),
+                   "precise_miss": st_p["precise_miss"], "precise_hit": st_p["precise_hit"]}
+        del xp, yp
     for t in range(W):
         step_device(t)
     barrier()
@@ -325,6 +349,8 @@ def run_ours(args, cfg):
                   "h2d_gbs_effective": (s1["h2d_bytes"] - s0["h2d_bytes"]) / (ms_total / 1e3) / 1e9,
                   "slab_impl": cache.get("slab_impl"), "numa": numa},
     }
+    if prefill is not None:
+        line["prefill"] = prefill
     if rank == 0 and not args.no_cpu_baseline and world == 1:
         threads = min(8, os.cpu_count() or 1)  # the reference pins torch to 8 threads (utils/__init__.py:343)
         if cfg.quant4:  # the CPU path computes on the dequantised float32 masters: one layer is 5.6 GB
@@ -345,6 +371,9 @@ def main():
     args = parse_args()
     from promoe_b200 import synth
     cfg = synth.CONFIGS[args.config]
+    if args.cache_rate is not None:
+        import dataclasses
+        cfg = dataclasses.replace(cfg, cache_rate=args.cache_rate)
     if args.impl == "reference":
         run_reference(args, cfg)
     else:
