@@ -666,6 +666,10 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
   c->tc_plan_used = 0;
   c->xperm_ready = false;
   c->tc_maps_ready = false;
+  if (c->profile_ffn && !c->ffn_samples.empty()) {  // their events have fired: recycle them now
+    rc = rt_profile_collect(c);
+    if (rc != PM_OK) return rc;
+  }
   if (c->tc_err_pending) {
     c->tc_err_pending = false;
     if (*c->h_tc_err != 0) {
