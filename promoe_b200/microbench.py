@@ -17,6 +17,47 @@ import torch
 from . import _lib
 
 
+def run_rotating(groups: int, rows: int, hidden: int, inter: int, iters: int, sets: int) -> dict:
+    """Like run(), but cycles through `sets` disjoint weight sets (as a layer stack does), so that no
+    launch finds its weights, or their page translations, warm from the previous launch."""
+    _lib.load()
+    dev = torch.device("cuda")
+    mat = inter * hidden
+    x = torch.randn((64, hidden), device=dev).to(torch.bfloat16)
+    n_rows = groups * rows
+    row_token = torch.randint(0, 64, (n_rows,), dtype=torch.int32, device=dev)
+    nbytes = _lib.call("pm_k_swiglu_ffn_scratch_bytes", groups, n_rows, inter, hidden)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    yexp = torch.empty((n_rows, hidden), dtype=torch.float32, device=dev)
+    plans, keep = [], []
+    for _ in range(sets):
+        arr = (_lib.pm_ffn_group * groups)()
+        for i in range(groups):
+            w = torch.empty(3 * mat, dtype=torch.bfloat16, device=dev).normal_(0, 0.02)
+            keep.append(w)
+            p = w.data_ptr()
+            arr[i] = _lib.pm_ffn_group(p, p + mat * 2, p + 2 * mat * 2, None, None, None, i * rows, rows, inter, 0)
+        plans.append(arr)
+
+    def once(arr):
+        _lib.call("pm_k_swiglu_ffn", arr, groups, 0, x.data_ptr(), hidden, row_token.data_ptr(), n_rows,
+                  yexp.data_ptr(), scratch.data_ptr(), nbytes, None)
+
+    for arr in plans:
+        once(arr)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for it in range(iters):
+        once(plans[it % sets])
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    weight_bytes = groups * 3 * mat * 2
+    return {"groups": groups, "rows": rows, "sets": sets, "total_gb": sets * weight_bytes / 1e9,
+            "us_per_launch": ms * 1e3, "gb_per_s": weight_bytes / ms / 1e6}
+
+
 def run(groups: int, rows: int, hidden: int, inter: int, iters: int, warmup: int = 3, quant4: bool = False) -> dict:
     _lib.load()
     dev = torch.device("cuda")
@@ -109,9 +150,13 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=0, help="time one prefill-size layer call instead")
     ap.add_argument("--config", default="c5")
     ap.add_argument("--no-tc", action="store_true", help="prefill through the staged mma.sync kernel")
+    ap.add_argument("--rotate", type=int, default=0, help="cycle through this many disjoint weight sets")
     a = ap.parse_args()
     if a.prefill_tokens:
         print(json.dumps(run_prefill(a.config, a.prefill_tokens, a.iters, not a.no_tc)))
+        return
+    if a.rotate > 1:
+        print(json.dumps(run_rotating(a.groups, a.rows, a.hidden, a.inter, a.iters, a.rotate)))
         return
     print(json.dumps(run(a.groups, a.rows, a.hidden, a.inter, a.iters, a.warmup, a.quant4)))
 
