@@ -181,6 +181,18 @@ def workload_config(cfg, n_gpus, predictor, num_predict=0):
             f"NCCL all-to-all dispatch and combine per layer)"}
 
 
+def launch_kinds(prof):
+    """Fused launches split into the device-planned ones (shared expert + resident experts) and the ones
+    for experts whose copy was issued in the same layer call."""
+    out = {}
+    rn, rms, rb = prof.get("resident_launches", 0), prof.get("resident_ms", 0.0), prof.get("resident_bytes", 0)
+    mn, mms, mb = prof["fused_launches"] - rn, prof["fused_ms"] - rms, prof["fused_bytes"] - rb
+    for name, n, ms, b in (("resident", rn, rms, rb), ("just_copied", mn, mms, mb)):
+        if n > 0 and ms > 0:
+            out[name] = {"launches": n, "avg_us": ms * 1e3 / n, "mb_per_launch": b / n / 1e6, "gbs": b / ms / 1e6}
+    return out
+
+
 def roofline_entry(prof, gu_gbs, dn_gbs, fu_gbs, peak, peak_src):
     """Roofline of the dominant kernel from the library's CUDA-event timing of every FFN launch."""
     if prof["fused_launches"] > 0:  # one cooperative launch does gate/up, grid barrier and down
@@ -192,6 +204,7 @@ def roofline_entry(prof, gu_gbs, dn_gbs, fu_gbs, peak, peak_src):
                                   "(1.043 GB for 1.038 GB of weights), scaled by the weight bytes of a launch",
                 "launches": n, "avg_launch_us": prof["fused_ms"] * 1e3 / n,
                 "bytes_per_launch": prof["fused_bytes"] / n, "frac_of_8tbs_nominal": fu_gbs / 8000.0,
+                "by_launch_kind": launch_kinds(prof),
                 "two_launch_path": {"launches": prof["ffn_launches"], "gateup_gbs": gu_gbs, "down_gbs": dn_gbs}}
     n = max(1, prof["ffn_launches"])
     return {"bound": "hbm", "kernel": "grouped_ffn gate/up (SwiGLU) launch", "achieved": gu_gbs, "peak": peak,

@@ -138,6 +138,9 @@ typedef struct pm_profile {
   int64_t fused_launches; /* single cooperative launches (gate/up, grid barrier, down) */
   double fused_ms;
   int64_t fused_bytes;
+  int64_t resident_launches; /* the part of the fused figures that belongs to device-planned launches */
+  double resident_ms;        /* (shared expert + experts already resident, enqueued behind the router) */
+  int64_t resident_bytes;
 } pm_profile;
 int pm_profile_read(pm_ctx* ctx, pm_profile* out, int reset);
 

@@ -33,7 +33,8 @@ class pm_stats(C.Structure):
 class pm_profile(C.Structure):
     _fields_ = [("ffn_launches", C.c_int64), ("gateup_ms", C.c_double), ("down_ms", C.c_double),
                 ("gateup_bytes", C.c_int64), ("down_bytes", C.c_int64), ("fused_launches", C.c_int64),
-                ("fused_ms", C.c_double), ("fused_bytes", C.c_int64)]
+                ("fused_ms", C.c_double), ("fused_bytes", C.c_int64), ("resident_launches", C.c_int64),
+                ("resident_ms", C.c_double), ("resident_bytes", C.c_int64)]
 
 
 class pm_layer_weights(C.Structure):

@@ -323,10 +323,16 @@ int pm_profile_read(pm_ctx* ctx, pm_profile* out, int reset) {
   out->fused_launches = ctx->ffn_fused_launches;
   out->fused_ms = ctx->ffn_ms_fused;
   out->fused_bytes = ctx->ffn_bytes_fused;
+  out->resident_launches = ctx->ffn_resident_launches;
+  out->resident_ms = ctx->ffn_ms_resident;
+  out->resident_bytes = ctx->ffn_bytes_resident;
   if (reset) {
     ctx->ffn_fused_launches = 0;
     ctx->ffn_ms_fused = 0;
     ctx->ffn_bytes_fused = 0;
+    ctx->ffn_resident_launches = 0;
+    ctx->ffn_ms_resident = 0;
+    ctx->ffn_bytes_resident = 0;
     ctx->ffn_launches = 0;
     ctx->ffn_ms_gu = ctx->ffn_ms_dn = 0;
     ctx->ffn_bytes_gu = ctx->ffn_bytes_dn = 0;

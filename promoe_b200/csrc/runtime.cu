@@ -274,6 +274,11 @@ int rt_profile_collect(pm_ctx* c) {
       c->ffn_ms_fused += a;
       c->ffn_bytes_fused += f.bytes_gu + f.bytes_dn;
       c->ffn_fused_launches += 1;
+      if (f.resident) {
+        c->ffn_ms_resident += a;
+        c->ffn_bytes_resident += f.bytes_gu + f.bytes_dn;
+        c->ffn_resident_launches += 1;
+      }
     } else {
       PM_CUDA(cudaEventElapsedTime(&a, f.e0, f.e1));
       PM_CUDA(cudaEventElapsedTime(&b, f.e1, f.e2));
@@ -647,6 +652,7 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
         return cudaEventCreate(e);
       };
       spec_sample.fused = true;
+      spec_sample.resident = true;
       PM_CUDA(take_event(&spec_sample.e0));
       PM_CUDA(take_event(&spec_sample.e2));
     }

@@ -119,6 +119,7 @@ struct pm_ctx {
     cudaEvent_t e0, e1, e2;  // before gate/up, between (null for a fused launch), after down
     int64_t bytes_gu, bytes_dn;
     bool fused;
+    bool resident;  // the device-planned launch (shared expert + experts already resident)
   };
   bool profile_ffn = false;
   bool fused_ffn = true;  // one cooperative launch per segment when the chunks are small enough
@@ -126,6 +127,8 @@ struct pm_ctx {
   std::vector<cudaEvent_t> ffn_event_pool; // free events
   double ffn_ms_gu = 0, ffn_ms_dn = 0, ffn_ms_fused = 0;
   int64_t ffn_bytes_gu = 0, ffn_bytes_dn = 0, ffn_launches = 0, ffn_bytes_fused = 0, ffn_fused_launches = 0;
+  double ffn_ms_resident = 0;  // part of the fused totals that belongs to device-planned launches
+  int64_t ffn_bytes_resident = 0, ffn_resident_launches = 0;
 
   ~pm_ctx();
 };
