@@ -594,6 +594,32 @@ __device__ __forceinline__ void tile_issue(const TileCtx<NT>& t, int s0, uint4 (
   }
 }
 
+// First batch of a tile in two halves: the weight loads can go out before the token rows exist.
+template <int NT, int DEPTH>
+__device__ __forceinline__ void tile_issue_a(const TileCtx<NT>& t, int s0, uint4 (&a)[DEPTH][4]) {
+#pragma unroll
+  for (int d = 0; d < DEPTH; ++d) {
+    if (s0 + d < t.s_end) {
+      const size_t off = (size_t)(s0 + d) * t.step_bytes;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) a[d][j] = ldg_stream(t.a_ptr[j] + off);
+    }
+  }
+}
+
+template <int NT, int DEPTH, bool COHERENT_B>
+__device__ __forceinline__ void tile_issue_b(const TileCtx<NT>& t, int s0, uint4 (&b)[DEPTH][NT]) {
+#pragma unroll
+  for (int d = 0; d < DEPTH; ++d) {
+    if (s0 + d < t.s_end) {
+      const size_t off = (size_t)(s0 + d) * t.step_bytes;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+        b[d][nt] = t.b_ok[nt] ? load_b<COHERENT_B>(t.b_ptr[nt] + off) : make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
 template <int NT, int DEPTH>
 __device__ __forceinline__ void tile_compute(const TileCtx<NT>& t, int s0, const uint4 (&a)[DEPTH][4],
                                              const uint4 (&b)[DEPTH][NT], float (&acc)[2][NT][4]) {
@@ -655,35 +681,57 @@ __device__ __forceinline__ void tile_finish(int rows, int m0, int row_start, flo
 }
 
 // Tiles blockIdx.x, blockIdx.x + gridDim.x, ... of one phase. The assignment is static, so the
-// next tile is known early: its first batch of loads is issued before the current tile is
-// reduced, which keeps DRAM requests in flight across tile boundaries.
-template <int NT, bool GATEUP, int DEPTH, int WARPS>
-__device__ __forceinline__ void stream_tiles(const GroupDesc* __restrict__ groups,
-                                             const int32_t* __restrict__ tile_group, int n_tiles,
-                                             const __nv_bfloat16* bsrc, int ldb,
-                                             const int32_t* __restrict__ row_token, int hidden,
-                                             __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp,
-                                             float (*red2)[WARPS][2 * NT * 4][32]) {
-  constexpr bool COH = !GATEUP;  // the down phase reads rows other CTAs wrote in this kernel
-  int buf = 0;
-  int tile = blockIdx.x;
-  if (tile >= n_tiles) return;
+// next tile is known early: its descriptor is fetched one tile ahead and its first batch of loads
+// is issued before the current tile is reduced, which keeps DRAM requests in flight across tile
+// boundaries. The phase is cut in two calls so that the fused kernel can start the down phase's
+// first weight loads (which do not depend on the intermediate rows) BEFORE the grid barrier.
+template <int NT, int DEPTH>
+struct StreamState {
   TileCtx<NT> t;
+  TileMeta<NT> m;
   uint4 a[DEPTH][4];
   uint4 b[DEPTH][NT];
+  int tile;
+  bool active;
+};
+
+// Sets the CTA's first tile up and issues its weight loads. Reads only the plan and the weights.
+template <int NT, bool GATEUP, int DEPTH, int WARPS>
+__device__ __forceinline__ void stream_begin(StreamState<NT, DEPTH>& st, const GroupDesc* __restrict__ groups,
+                                             const int32_t* __restrict__ tile_group, int n_tiles,
+                                             const __nv_bfloat16* bsrc, int ldb,
+                                             const int32_t* __restrict__ row_token, int hidden) {
+  st.tile = blockIdx.x;
+  st.active = st.tile < n_tiles;
+  if (!st.active) return;
+  meta_load_desc<NT, GATEUP>(st.m, groups, tile_group[st.tile]);  // only the first tile pays for these round trips
+  meta_load_rows<NT, GATEUP>(st.m, row_token);
+  tile_setup<NT, GATEUP, WARPS>(st.t, st.m, st.tile, bsrc, ldb, hidden);
+  tile_issue_a<NT, DEPTH>(st.t, st.t.s_begin, st.a);
+}
+
+template <int NT, bool GATEUP, int DEPTH, int WARPS>
+__device__ __forceinline__ void stream_run(StreamState<NT, DEPTH>& st, const GroupDesc* __restrict__ groups,
+                                           const int32_t* __restrict__ tile_group, int n_tiles,
+                                           const __nv_bfloat16* bsrc, int ldb,
+                                           const int32_t* __restrict__ row_token, int hidden,
+                                           __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp,
+                                           float (*red2)[WARPS][2 * NT * 4][32]) {
+  constexpr bool COH = !GATEUP;  // the down phase reads rows other CTAs wrote in this kernel
+  if (!st.active) return;
+  TileCtx<NT>& t = st.t;
+  TileMeta<NT>& m = st.m;
+  int buf = 0;
   float acc[2][NT][4];
 #pragma unroll
-  for (int m = 0; m < 2; ++m)
+  for (int mm = 0; mm < 2; ++mm)
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[m][nt][i] = 0.f;
+      for (int i = 0; i < 4; ++i) acc[mm][nt][i] = 0.f;
+  tile_issue_b<NT, DEPTH, COH>(t, t.s_begin, st.b);
   const int stride = gridDim.x;
-  TileMeta<NT> m;
-  meta_load_desc<NT, GATEUP>(m, groups, tile_group[tile]);  // only the first tile pays for these round trips
-  meta_load_rows<NT, GATEUP>(m, row_token);
-  tile_setup<NT, GATEUP, WARPS>(t, m, tile, bsrc, ldb, hidden);
-  tile_issue<NT, DEPTH, COH>(t, t.s_begin, a, b);
+  int tile = st.tile;
   int next = tile + stride;
   int gi_next = (next < n_tiles) ? tile_group[next] : 0;
   while (true) {
@@ -693,19 +741,19 @@ __device__ __forceinline__ void stream_tiles(const GroupDesc* __restrict__ group
     const int gi_next2 = (next2 < n_tiles) ? tile_group[next2] : 0;
     bool rows_loaded = false;
     for (int s0 = t.s_begin; s0 < t.s_end;) {
-      tile_compute<NT, DEPTH>(t, s0, a, b, acc);
+      tile_compute<NT, DEPTH>(t, s0, st.a, st.b, acc);
       if (has_next && !rows_loaded) {  // the descriptor is here by now: fetch the token row numbers
         meta_load_rows<NT, GATEUP>(m, row_token);
         rows_loaded = true;
       }
       s0 += DEPTH;
-      if (s0 < t.s_end) tile_issue<NT, DEPTH, COH>(t, s0, a, b);
+      if (s0 < t.s_end) tile_issue<NT, DEPTH, COH>(t, s0, st.a, st.b);
     }
     if (has_next && !rows_loaded) meta_load_rows<NT, GATEUP>(m, row_token);
     const int rows = t.rows, m0 = t.m0, row_start = t.row_start;
     if (has_next) {
       tile_setup<NT, GATEUP, WARPS>(t, m, next, bsrc, ldb, hidden);
-      tile_issue<NT, DEPTH, COH>(t, t.s_begin, a, b);
+      tile_issue<NT, DEPTH, COH>(t, t.s_begin, st.a, st.b);
     }
     tile_finish<NT, GATEUP, WARPS>(rows, m0, row_start, acc, red2[buf], hbuf, ld_h, yexp, hidden);
     buf ^= 1;
@@ -729,10 +777,16 @@ grouped_ffn_fused_kernel(const GroupDesc* __restrict__ groups, const int32_t* __
     tiles_gu = dev_tiles[0];
     tiles_dn = dev_tiles[1];
   }
-  stream_tiles<NT, true, DEPTH, WARPS>(groups, tile_gu, tiles_gu, x, hidden, row_token, hidden, hbuf, ld_h, yexp, red);
+  StreamState<NT, DEPTH> st;
+  stream_begin<NT, true, DEPTH, WARPS>(st, groups, tile_gu, tiles_gu, x, hidden, row_token, hidden);
+  stream_run<NT, true, DEPTH, WARPS>(st, groups, tile_gu, tiles_gu, x, hidden, row_token, hidden, hbuf, ld_h, yexp, red);
+  // The first down tile's descriptor and weight loads do not depend on the intermediate rows: they go
+  // out before the barrier, so their DRAM latency is hidden behind it.
+  stream_begin<NT, false, DEPTH, WARPS>(st, groups, tile_dn, tiles_dn, hbuf, ld_h, row_token, hidden);
   __threadfence();
   cooperative_groups::this_grid().sync();
-  stream_tiles<NT, false, DEPTH, WARPS>(groups, tile_dn, tiles_dn, hbuf, ld_h, row_token, hidden, nullptr, ld_h, yexp, red);
+  stream_run<NT, false, DEPTH, WARPS>(st, groups, tile_dn, tiles_dn, hbuf, ld_h, row_token, hidden, nullptr, ld_h, yexp,
+                                      red);
 }
 
 // Resident grid of the fused kernel on the current device (0 if cooperative launch is unavailable).
