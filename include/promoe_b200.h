@@ -224,7 +224,8 @@ typedef struct pm_ffn_group {
 size_t pm_k_swiglu_ffn_scratch_bytes(int n_groups, int n_rows, int max_inter, int hidden);
 /* Grouped SwiGLU FFN: yexp[r, :] = down(silu(gate(x[row_token[r]])) * up(x[row_token[r]])) for
  * every row r of every group. groups is a HOST array; scratch is device memory of at least
- * pm_k_swiglu_ffn_scratch_bytes(). yexp is f32 [n_rows, hidden]. */
+ * pm_k_swiglu_ffn_scratch_bytes(). yexp is f32 [n_rows, hidden]. Returns PM_ERR_UNSUPPORTED when
+ * `stream` is being captured (the launch plan is uploaded from temporary host memory). */
 int pm_k_swiglu_ffn(const pm_ffn_group* groups, int n_groups, int quant4, const void* x, int hidden,
                     const int32_t* row_token, int n_rows, float* yexp, void* scratch,
                     size_t scratch_bytes, void* stream);
@@ -235,9 +236,10 @@ int pm_k_swiglu_ffn(const pm_ffn_group* groups, int n_groups, int quant4, const 
  * by every GPU that loads the library until exit); this call performs no cudaMalloc / cudaFree
  * and no allocating library call. A launch that needs more than the array holds (plan above
  * 64 KiB, or plan + n_rows * max_inter * 2 bytes above the capacity) is rejected with
- * PM_ERR_INVALID. bf16 experts only. The first call on a device looks the array's device
- * address up; make that call before any stream capture. All calls share the array: calls that
- * overlap on the GPU race, serialise them. */
+ * PM_ERR_INVALID. bf16 experts only (groups with scale/zero tensors are rejected). The first call
+ * on a device looks the array's device address up. A call on a stream that is being captured is
+ * refused with PM_ERR_UNSUPPORTED. All calls share the array: calls that overlap on the GPU race,
+ * serialise them. */
 size_t pm_k_swiglu_ffn_static_capacity(void);
 int pm_k_swiglu_ffn_static(const pm_ffn_group* groups, int n_groups, const void* x, int hidden,
                            const int32_t* row_token, int n_rows, float* yexp, void* stream);

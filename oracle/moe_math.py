@@ -190,3 +190,50 @@ def rank_experts(scores: np.ndarray, n: int) -> np.ndarray:
     """Descending sort, first n (src/cpp_worker/predictor.hpp:24-28); ties -> lower id."""
     n = min(n, scores.shape[-1])
     return np.argsort(-scores, kind="stable")[:n].astype(np.int64)
+
+
+# ----------------------------------------------------------------------------- large batches
+def routing_consistent(x, gate_w, gate_bias, ids, top_k, gap=1e-4) -> bool:
+    """True when `ids` (descending order, selected on the float32 canonical logits) is a valid
+    top-k of the float64 logits up to `gap`: no expert left out beats a chosen one by more than
+    `gap`, and the chosen ones are in non-increasing order up to `gap`. (Where two float64 logits
+    lie closer than float32 resolves, either order is a correct selection.)"""
+    lg = gate_logits(x, gate_w, gate_bias)
+    chosen = np.take_along_axis(lg, ids, axis=1)
+    masked = lg.copy()
+    np.put_along_axis(masked, ids, -np.inf, axis=1)
+    if (masked.max(axis=1) - chosen.min(axis=1) > gap).any():
+        return False
+    return not ((chosen[:, 1:] - chosen[:, :-1]) > gap).any()
+
+
+def moe_block_forward_f32(x, ids, w, experts, shared=None, shared_gate_w=None, expert_order=None):
+    """The same block for prefill-size batches with the routing given: float32 torch matmuls on the
+    host cores, grouped per expert, intermediate rows rounded to bf16 as the device stores them.
+    (float64 numpy needs minutes for 8192 tokens x 64 experts; the tolerance of the parity tests,
+    rtol 2e-2, is four orders of magnitude above float32 rounding.) Returns y [T, H] float32."""
+    import torch
+    T, H = x.shape
+    xt = torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32))
+    y = torch.zeros((T, H), dtype=torch.float32)
+    wt = torch.from_numpy(np.ascontiguousarray(w, dtype=np.float32))
+    idt = torch.from_numpy(np.ascontiguousarray(ids, dtype=np.int64))
+
+    def mlp(rows, wg, wu, wd):
+        g = rows @ torch.from_numpy(wg).T
+        h = torch.nn.functional.silu(g) * (rows @ torch.from_numpy(wu).T)
+        return h.to(torch.bfloat16).float() @ torch.from_numpy(wd).T
+
+    order = unique_sorted_experts(ids) if expert_order is None else expert_order
+    for e in order:
+        tok, slot = torch.nonzero(idt == int(e), as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        out = mlp(xt[tok], *experts[int(e)])
+        y.index_add_(0, tok, out * wt[tok, slot][:, None])
+    if shared is not None:
+        s = mlp(xt, *shared)
+        if shared_gate_w is not None:
+            s = s * torch.sigmoid(xt @ torch.from_numpy(np.ascontiguousarray(shared_gate_w, dtype=np.float32)))[:, None]
+        y += s
+    return y.numpy()

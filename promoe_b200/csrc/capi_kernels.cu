@@ -23,7 +23,7 @@ int fail_cuda(cudaError_t e, const char* what) {
 // One planner for both passes: with blob == nullptr it only sizes the launch.
 static int plan_core(const pm_ffn_group* groups, int n_groups, int hidden, unsigned char* blob, size_t cap,
                      FfnPlanInfo* info, int chunk_rows) {
-  if (hidden % 64 != 0) return fail(PM_ERR_INVALID, "hidden must be a multiple of 64");
+  if (hidden <= 0 || hidden % 64 != 0) return fail(PM_ERR_INVALID, "hidden must be a positive multiple of 64");
   // The kernel variant, and with it the tile size, follows from the largest chunk of the launch.
   int largest = 0;
   for (int i = 0; i < n_groups; ++i) largest = std::max(largest, std::min(groups[i].row_count, chunk_rows));
@@ -80,6 +80,18 @@ int plan_groups_into(const pm_ffn_group* groups, int n_groups, int hidden, unsig
 }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// The grouped FFN entry points upload their launch plan from host memory that dies when the call
+// returns. Outside a capture the bytes are staged before cudaMemcpyAsync returns; inside one the
+// graph would keep the host pointer and read it at every graph launch. So they refuse.
+int refuse_if_capturing(cudaStream_t s, const char* who) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  PM_CUDA(cudaStreamIsCapturing(s, &st));
+  if (st != cudaStreamCaptureStatusNone)
+    return fail(PM_ERR_UNSUPPORTED, std::string(who) + ": the stream is capturing; this call uploads a launch plan "
+                                    "from temporary host memory and cannot be part of a CUDA graph");
+  return PM_OK;
+}
 
 }  // namespace pm
 
@@ -141,6 +153,10 @@ int pm_k_swiglu_ffn(const pm_ffn_group* groups, int n_groups, int quant4, const 
   if (n_groups < 0 || n_rows < 0) return fail(PM_ERR_INVALID, "swiglu_ffn: negative size");
   if (n_groups == 0 || n_rows == 0) return PM_OK;
   if (!groups || !x || !row_token || !yexp || !scratch) return fail(PM_ERR_INVALID, "swiglu_ffn: null pointer");
+  {
+    int rc = refuse_if_capturing((cudaStream_t)stream, "swiglu_ffn");
+    if (rc != PM_OK) return rc;
+  }
   for (int i = 0; i < n_groups; ++i)
     if (groups[i].row_count > 0 && (groups[i].row_start < 0 || groups[i].row_start + groups[i].row_count > n_rows))
       return fail(PM_ERR_INVALID, "swiglu_ffn: group rows outside [0, n_rows)");

@@ -9,11 +9,12 @@
 //
 // The array's name is only a host-side handle. Its device address is looked up once per device
 // (with that device current) through cudaGetSymbolAddress, and that address is what the kernels
-// receive. The first call on a device performs this look-up, so make it before any stream
-// capture begins. All calls share the one array and it keeps the previous call's bytes: every
+// receive. The first call on a device performs this look-up. A call on a stream that is being
+// captured is refused (PM_ERR_UNSUPPORTED): the plan is uploaded from the host stack. All calls share the one array and it keeps the previous call's bytes: every
 // byte a launch reads (plan, intermediate rows of its own groups) is written by the same call
 // first, so nothing needs clearing, but two calls that overlap on the GPU (different streams,
 // or different threads) would overwrite each other's plan and rows -- serialise them.
+#include <cstdio>
 #include <mutex>
 
 #include "pm_common.cuh"
@@ -63,25 +64,34 @@ int pm_k_swiglu_ffn_static(const pm_ffn_group* groups, int n_groups, const void*
   if (n_groups < 0 || n_rows < 0) return fail(PM_ERR_INVALID, "swiglu_ffn_static: negative size");
   if (n_groups == 0 || n_rows == 0) return PM_OK;
   if (!groups || !x || !row_token || !yexp) return fail(PM_ERR_INVALID, "swiglu_ffn_static: null pointer");
-  for (int i = 0; i < n_groups; ++i)
-    if (groups[i].row_count > 0 && (groups[i].row_start < 0 || groups[i].row_start + groups[i].row_count > n_rows))
+  if (hidden <= 0) return fail(PM_ERR_INVALID, "swiglu_ffn_static: hidden must be positive");
+  int rc = refuse_if_capturing((cudaStream_t)stream, "swiglu_ffn_static");
+  if (rc != PM_OK) return rc;
+  for (int i = 0; i < n_groups; ++i) {
+    if (groups[i].row_count <= 0) continue;
+    if (groups[i].row_start < 0 || groups[i].row_start + groups[i].row_count > n_rows)
       return fail(PM_ERR_INVALID, "swiglu_ffn_static: group rows outside [0, n_rows)");
+    if (groups[i].q_gate || groups[i].q_up || groups[i].q_down)
+      return fail(PM_ERR_INVALID, "swiglu_ffn_static: bf16 experts only (a group carries scale/zero tensors)");
+  }
   FfnPlanInfo info;
-  int rc = plan_groups_size(groups, n_groups, hidden, &info);
+  rc = plan_groups_size(groups, n_groups, hidden, &info);
   if (rc != PM_OK) return rc;
   if (info.n_desc == 0) return PM_OK;
   const size_t plan_bytes = align_up(info.blob_bytes(), 256);
   const size_t rows_bytes = align_up((size_t)n_rows * info.max_inter * 2, 256);
-  if (info.blob_bytes() > kStaticPlanBytes || plan_bytes + rows_bytes > kStaticScratchBytes)
-    return fail(PM_ERR_INVALID,
-                "swiglu_ffn_static: this launch needs " + std::to_string(plan_bytes + rows_bytes) +
-                    " bytes of scratch (plan " + std::to_string(info.blob_bytes()) + "), the built-in array holds " +
-                    std::to_string(kStaticScratchBytes) + " (plan at most " + std::to_string(kStaticPlanBytes) +
-                    "); use pm_k_swiglu_ffn with caller scratch");
+  if (info.blob_bytes() > kStaticPlanBytes || plan_bytes + rows_bytes > kStaticScratchBytes) {
+    char msg[256];
+    std::snprintf(msg, sizeof(msg),
+                  "swiglu_ffn_static: this launch needs %zu bytes of scratch (plan %zu), the built-in array holds %zu "
+                  "(plan at most %zu); use pm_k_swiglu_ffn with caller scratch",
+                  plan_bytes + rows_bytes, info.blob_bytes(), kStaticScratchBytes, kStaticPlanBytes);
+    return fail(PM_ERR_INVALID, msg);
+  }
   unsigned char* scratch = nullptr;
   rc = scratch_address(&scratch);
   if (rc != PM_OK) return rc;
-  unsigned char plan[kStaticPlanBytes];  // host stack: no heap, no device allocation on this path
+  alignas(16) unsigned char plan[kStaticPlanBytes];  // host stack: no device allocation on this path
   rc = plan_groups_into(groups, n_groups, hidden, plan, sizeof(plan), &info);
   if (rc != PM_OK) return rc;
   cudaStream_t s = (cudaStream_t)stream;

@@ -215,15 +215,20 @@ prefill_ffn_kernel(const __grid_constant__ TcMaps maps, const TcGroup* __restric
 cudaError_t launch_prefill_ffn(const TcMaps& maps, const TcGroup* groups_dev, const TcTile* tiles_gu_dev, int n_gu,
                                const TcTile* tiles_dn_dev, int n_dn, int hidden, __nv_bfloat16* hbuf, int ld_h,
                                float* yexp, int32_t* err_dev, cudaStream_t s, cudaEvent_t mid_event) {
-  static bool configured = false;
-  if (!configured) {
+  // the attribute is per device: a process that drives several GPUs opts in on each of them
+  static bool configured_dev[64] = {};
+  int dev = 0;
+  cudaError_t e0 = cudaGetDevice(&dev);
+  if (e0 != cudaSuccess) return e0;
+  const bool known = dev >= 0 && dev < 64;
+  if (!known || !configured_dev[dev]) {
     cudaError_t e = cudaFuncSetAttribute(prefill_ffn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)tc_smem_bytes<true>());
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(prefill_ffn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)tc_smem_bytes<false>());
     if (e != cudaSuccess) return e;
-    configured = true;
+    if (known) configured_dev[dev] = true;
   }
   if (n_gu > 0)
     prefill_ffn_kernel<true><<<n_gu, kTcThreads, tc_smem_bytes<true>(), s>>>(maps, groups_dev, tiles_gu_dev, hidden,

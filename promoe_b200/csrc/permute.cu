@@ -33,8 +33,9 @@ permute_kernel(const int32_t* __restrict__ topk_ids, int R, int k, int E, int32_
     int e = topk_ids[i];
     if (e >= 0 && e < E) {
       atomicAdd(&cnt[e], 1);
-    } else if (err_flag != nullptr) {
-      atomicExch(err_flag, 1);  // id outside [0, E): the pair is dropped
+    } else {  // id outside [0, E): the pair is dropped and flagged; its position must not keep an old value
+      pos[i] = -1;
+      if (err_flag != nullptr) atomicExch(err_flag, 1);
     }
   }
   __syncthreads();
@@ -77,15 +78,19 @@ constexpr int kChunk = 4096;
 
 __global__ void __launch_bounds__(256)
 permute_count_kernel(const int32_t* __restrict__ topk_ids, int R, int E, int32_t* __restrict__ chunk_cnt,
-                     int32_t* __restrict__ err_flag) {
+                     int32_t* __restrict__ err_flag, int32_t* __restrict__ pos) {
   __shared__ int cnt[kMaxExperts];
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
   __syncthreads();
   const int c0 = blockIdx.x * kChunk, c1 = min(R, c0 + kChunk);
   for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x) {
     const int e = topk_ids[i];
-    if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
-    else if (err_flag != nullptr) atomicExch(err_flag, 1);
+    if (e >= 0 && e < E) {
+      atomicAdd(&cnt[e], 1);
+    } else {
+      pos[i] = -1;
+      if (err_flag != nullptr) atomicExch(err_flag, 1);
+    }
   }
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) chunk_cnt[(size_t)blockIdx.x * E + e] = cnt[e];
@@ -148,14 +153,16 @@ permute_place_kernel(const int32_t* __restrict__ topk_ids, int R, int k, int E,
   }
 }
 
-// dst row r = src row index[r]; rows are row_vec 16-byte vectors long.
+// dst row r = src row index[r]; rows are row_vec 16-byte vectors long. A negative index (a pair the
+// permutation dropped) yields a row of zeros.
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ index, int n_rows, int row_vec,
                    uint4* __restrict__ dst) {
   for (int r = blockIdx.x; r < n_rows; r += gridDim.x) {
-    const uint4* s = src + (size_t)index[r] * row_vec;
+    const int from = index[r];
+    const uint4* s = src + (size_t)(from < 0 ? 0 : from) * row_vec;
     uint4* d = dst + (size_t)r * row_vec;
-    for (int v = threadIdx.x; v < row_vec; v += blockDim.x) d[v] = s[v];
+    for (int v = threadIdx.x; v < row_vec; v += blockDim.x) d[v] = from < 0 ? make_uint4(0, 0, 0, 0) : s[v];
   }
 }
 
@@ -174,7 +181,7 @@ cudaError_t launch_permute(const int32_t* topk_ids, int R, int k, int E, int32_t
                            int tail_rows, int T, cudaStream_t s, int32_t* scratch, size_t scratch_ints) {
   const int n_chunks = (R + kChunk - 1) / kChunk;
   if (R > 2 * kChunk && scratch != nullptr && scratch_ints >= (size_t)n_chunks * E) {
-    permute_count_kernel<<<n_chunks, 256, 0, s>>>(topk_ids, R, E, scratch, err_flag);
+    permute_count_kernel<<<n_chunks, 256, 0, s>>>(topk_ids, R, E, scratch, err_flag, pos);
     permute_scan_kernel<<<1, 256, 0, s>>>(scratch, n_chunks, E, counts, offsets, row_token, R, tail_rows, T > 0 ? T : 1);
     permute_place_kernel<<<n_chunks, 1024, 0, s>>>(topk_ids, R, k, E, scratch, row_token, pos);
     return cudaGetLastError();

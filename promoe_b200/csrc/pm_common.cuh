@@ -18,6 +18,8 @@ namespace pm {
 // Records a message retrievable through pm_last_error(NULL) and returns `code`.
 int fail(int code, const std::string& msg);
 int fail_cuda(cudaError_t e, const char* what);
+// PM_ERR_UNSUPPORTED (with a message naming `who`) while stream `s` is being captured into a graph.
+int refuse_if_capturing(cudaStream_t s, const char* who);
 
 #define PM_CUDA(expr)                                         \
   do {                                                        \

@@ -112,7 +112,8 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
     return o;
   };
   size_t o_ids = take(R * 4), o_slot = take(R * 4), o_w = take(R * 4), o_ss = take((size_t)cap * 4);
-  size_t o_cnt = take((size_t)(2 * E + 1) * 4), o_rt = take(rows * 4), o_pos = take(R * 4), o_err = take(4);
+  // counts [E], offsets [E + 1] and the permutation's error word travel to the host in one copy
+  size_t o_cnt = take((size_t)(2 * E + 2) * 4), o_rt = take(rows * 4), o_pos = take(R * 4);
   size_t o_h = take(rows * I * 2), o_y = take(rows * H * 4), o_desc = take(c->plan_cap);
   size_t o_sc = take((size_t)c->cfg.num_layer * E * 4), o_ph = take((size_t)cap * 4096 * 4);
   size_t o_x = take((size_t)cap * H * 2), o_yo = take((size_t)cap * H * 2);
@@ -140,7 +141,7 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
   c->d_offsets = c->d_counts + E;
   c->d_row_token = (int32_t*)(b + o_rt);
   c->d_pos = (int32_t*)(b + o_pos);
-  c->d_err = (int32_t*)(b + o_err);
+  c->d_err = c->d_counts + 2 * E + 1;
   c->d_hbuf = (__nv_bfloat16*)(b + o_h);
   c->d_yexp = (float*)(b + o_y);
   c->d_plan = b + o_desc;
@@ -160,7 +161,7 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
   c->ws_inter_routed = Ir;
   c->ws_inter_shared = Is;
   // pinned staging: [counts+offsets | scores | routing ids | routing weights | descriptors]
-  c->h_stage_bytes = align_up((size_t)(2 * E + 1) * 4, 256) + align_up((size_t)c->cfg.num_layer * E * 4, 256) +
+  c->h_stage_bytes = align_up((size_t)(2 * E + 2) * 4, 256) + align_up((size_t)c->cfg.num_layer * E * 4, 256) +
                      2 * align_up(R * 4, 256) + align_up(c->plan_cap, 256) +
                      align_up((size_t)E * 4, 256);
   PM_CUDA(cudaHostAlloc((void**)&c->h_stage, c->h_stage_bytes, cudaHostAllocDefault));
@@ -186,7 +187,7 @@ Stage stage_of(pm_ctx* c) {
   Stage s;
   unsigned char* p = c->h_stage;
   s.counts = (int32_t*)p;
-  p += align_up((size_t)(2 * E + 1) * 4, 256);
+  p += align_up((size_t)(2 * E + 2) * 4, 256);
   s.scores = (float*)p;
   p += align_up((size_t)c->cfg.num_layer * E * 4, 256);
   s.ids = (int32_t*)p;
@@ -600,7 +601,7 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
   PM_CUDA(cudaStreamWaitEvent(rb, c->routed_event, 0));
   if (!pred_dsts.empty())
     PM_CUDA(cudaMemcpyAsync(st.scores, c->d_scores, (size_t)c->cfg.num_layer * E * 4, cudaMemcpyDeviceToHost, rb));
-  PM_CUDA(cudaMemcpyAsync(st.counts, c->d_counts, (size_t)(2 * E + 1) * 4, cudaMemcpyDeviceToHost, rb));
+  PM_CUDA(cudaMemcpyAsync(st.counts, c->d_counts, (size_t)(2 * E + 2) * 4, cudaMemcpyDeviceToHost, rb));
   const bool keep = c->keep_routing && !routed;
   if (keep) {
     PM_CUDA(cudaMemcpyAsync(st.ids, c->d_topk_ids, (size_t)R * 4, cudaMemcpyDeviceToHost, rb));
@@ -686,6 +687,12 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
     }
   }
 
+  if (st.counts[2 * E + 1] != 0) {
+    // only the caller's row_expert can be out of range (the router's ids never are); the rows were
+    // dropped by the permutation, so nothing may be returned for this call
+    PM_CUDA(cudaMemsetAsync(c->d_err, 0, 4, s));
+    return fail(PM_ERR_INVALID, "an expert id outside [0, num_expert) was passed for a routed row");
+  }
   if (keep) {
     c->last_ids[layer].assign(st.ids, st.ids + R);
     c->last_w[layer].assign(st.w, st.w + R);

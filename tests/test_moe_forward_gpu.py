@@ -195,3 +195,26 @@ def test_report_hidden_hook_path(lib):
     assert cache.events() == oc.events
     assert cache.stats()["prefetch_miss"] > 0
     cache.close()
+
+
+def test_routed_rows_reject_an_expert_id_out_of_range(lib):
+    """pm_moe_forward_routed takes the caller's expert id per row: an id equal to num_expert is an
+    error, not a silently dropped row, and the context stays usable."""
+    from promoe_b200 import _lib
+    model = TinyModel(seed=8, L=1, E=8, H=128, I=64, k=2)
+    cache = model.make_cache(cache_rate=0.5, num_predict_expert_per_layer=0)
+    x = model.hidden_stream(4, 1)[0]
+    xd = dev_bf16(x)
+    out = torch.full((4, 128), float("nan"), dtype=torch.float32, device="cuda")
+    bad = torch.tensor([0, 3, 8, 1], dtype=torch.int32, device="cuda")
+    with pytest.raises(_lib.PromoeError) as e:
+        _lib.call("pm_moe_forward_routed", cache.handle, 0, xd.data_ptr(), 4, bad.data_ptr(), out.data_ptr(), None)
+    assert "expert id" in str(e.value)
+    good = torch.tensor([0, 3, 7, 1], dtype=torch.int32, device="cuda")
+    _lib.call("pm_moe_forward_routed", cache.handle, 0, xd.data_ptr(), 4, good.data_ptr(), out.data_ptr(), None)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    for r, e_id in enumerate([0, 3, 7, 1]):
+        ref = om.swiglu_mlp(x[r:r + 1], *model.experts[0][e_id], round_h_bf16=True)
+        np.testing.assert_allclose(got[r:r + 1], ref, rtol=RTOL, atol=RTOL * np.abs(ref).max() * 0.25)
+    cache.close()

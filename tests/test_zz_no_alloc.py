@@ -68,3 +68,70 @@ def test_static_scratch_rejects_oversize_and_bad_input(lib):
     with pytest.raises(_lib.PromoeError):
         _lib.call("pm_k_swiglu_ffn_static", arr, 1, 8, 128, 8, 1, 8, None)   # inter % 32 != 0
     _lib.call("pm_k_swiglu_ffn_static", arr, 0, 8, 128, 8, 0, 8, None)       # empty launch: no-op
+
+
+def test_static_scratch_matches_the_oracle_on_a_side_stream(lib):
+    """Stands on its own: the built-in-scratch entry point against the float64 oracle, two calls in a
+    row on a stream that is not the default one."""
+    H, inters, rows, T = 256, [128, 256], [7, 12], 16
+    rng = np.random.default_rng(5)
+    x = om.bf16_round(rng.standard_normal((T, H)).astype(np.float32))
+    xd = dev_bf16(x)
+    ws, keep, row_token, start = [], [], [], 0
+    arr = (_lib.pm_ffn_group * len(inters))()
+    for i, (inter, r) in enumerate(zip(inters, rows)):
+        w = [bf16_weights(rng, s) for s in ((inter, H), (inter, H), (H, inter))]
+        d = [dev_bf16(m) for m in w]
+        ws.append(w)
+        keep += d
+        arr[i] = _lib.pm_ffn_group(ptr(d[0]), ptr(d[1]), ptr(d[2]), None, None, None, start, r, inter, 0)
+        row_token += list(rng.integers(0, T, size=r))
+        start += r
+    rt = dev(np.array(row_token, np.int32))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    for _ in range(2):
+        got = torch.full((start, H), float("nan"), dtype=torch.float32, device="cuda")
+        with torch.cuda.stream(side):
+            _lib.call("pm_k_swiglu_ffn_static", arr, len(inters), ptr(xd), H, ptr(rt), start, ptr(got), side.cuda_stream)
+        side.synchronize()
+        y, s0 = got.cpu().numpy(), 0
+        for w, r in zip(ws, rows):
+            ref = om.swiglu_mlp(x[row_token[s0:s0 + r]], *w, round_h_bf16=True)
+            np.testing.assert_allclose(y[s0:s0 + r], ref, rtol=2e-2, atol=2e-2 * np.abs(ref).max() * 0.1)
+            s0 += r
+
+
+def test_static_scratch_refuses_a_capturing_stream_and_quantised_groups(lib):
+    """Both FFN entry points upload their plan from temporary host memory, which a graph would read
+    after it is gone: on a capturing stream they return an error and enqueue nothing."""
+    case = build_case(3, 128, [64], [4])
+    x, arr, n_groups, rt, n_rows, max_inter, _ = case
+    out = torch.zeros((n_rows, 128), dtype=torch.float32, device="cuda")
+    nbytes = _lib.call("pm_k_swiglu_ffn_scratch_bytes", n_groups, n_rows, max_inter, 128)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        graph.capture_begin(capture_error_mode="thread_local")
+        try:
+            with pytest.raises(_lib.PromoeError) as e1:
+                _lib.call("pm_k_swiglu_ffn_static", arr, n_groups, ptr(x), 128, ptr(rt), n_rows, ptr(out), side.cuda_stream)
+            with pytest.raises(_lib.PromoeError) as e2:
+                _lib.call("pm_k_swiglu_ffn", arr, n_groups, 0, ptr(x), 128, ptr(rt), n_rows, ptr(out), ptr(scratch), nbytes,
+                          side.cuda_stream)
+        finally:
+            graph.capture_end()
+    assert "capturing" in str(e1.value) and "capturing" in str(e2.value)
+    torch.cuda.synchronize()
+    # outside the capture the same call works
+    _lib.call("pm_k_swiglu_ffn_static", arr, n_groups, ptr(x), 128, ptr(rt), n_rows, ptr(out), None)
+    torch.cuda.synchronize()
+    assert np.isfinite(out.cpu().numpy()).all()
+    q = (_lib.pm_ffn_group * 1)()
+    q[0] = _lib.pm_ffn_group(8, 8, 8, 8, 8, 8, 0, 1, 128, 0)
+    with pytest.raises(_lib.PromoeError):
+        _lib.call("pm_k_swiglu_ffn_static", q, 1, 8, 128, 8, 1, 8, None)
+    with pytest.raises(_lib.PromoeError):
+        _lib.call("pm_k_swiglu_ffn_static", arr, n_groups, ptr(x), 0, ptr(rt), n_rows, ptr(out), None)
