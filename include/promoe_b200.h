@@ -96,6 +96,26 @@ int pm_prefetch_layer(pm_ctx* ctx, int layer, const int64_t* ids, int64_t n);
 int pm_report_expert(pm_ctx* ctx, int layer, int expert);
 int pm_expert_done(pm_ctx* ctx, int layer, int expert);
 int pm_layer_done(pm_ctx* ctx, int layer);
+/* The same two calls for a caller that computes the expert itself on `stream` (the reference's
+ * per-expert module loop under ExpertHook, src/sparse_llm_cache/utils/hooks.py:187-198):
+ * pm_expert_acquire = report_one_expert + wait_expert (src/cpp_worker/prefetcher.cpp:225-258): after
+ * the bookkeeping it makes `stream` wait for the copy into the expert's cache line (the host does
+ * not wait) and returns the line's device address; tensor i of the expert sits at
+ * *line + pm_param_offset(i), which is what the reference's logical parameter is re-pointed to on
+ * a fetch (src/cpp_worker/worker.cpp:91-97, src/cpp_worker/model_loader.hpp:290-313).
+ * pm_expert_release = one_expert_done (src/cpp_worker/prefetcher.cpp:259-267): it records on
+ * `stream` the point after which a later copy may overwrite the line. */
+int pm_expert_acquire(pm_ctx* ctx, int layer, int expert, void* stream, void** line);
+int pm_expert_release(pm_ctx* ctx, int layer, int expert, void* stream);
+/* Byte offset of tensor param_id inside every cache line and pinned record (256-byte aligned). */
+int pm_param_offset(pm_ctx* ctx, int param_id, size_t* offset);
+/* PrefetchMngr::temp_move_expert_to_gpu / temp_move_expert_back_to_host
+ * (src/cpp_worker/prefetcher.cpp:664-697): copies the expert's host record into a spare cache line
+ * that no policy owns and returns its address (a quantised layer's post_init can then transform
+ * the tensors on the device), or copies the spare line back into the host record. Both wait for
+ * their copy on `stream`. */
+int pm_temp_move_expert_to_gpu(pm_ctx* ctx, int layer, int expert, void* stream, void** line);
+int pm_temp_move_expert_back_to_host(pm_ctx* ctx, int layer, int expert, void* stream);
 /* CacheMngr::set_cur_seq (src/cpp_worker/cache.hpp:310-314), Belady policy only. */
 int pm_set_cur_seq(pm_ctx* ctx, uint64_t seq_id);
 /* Loads the Belady (MIN) trace: per (seq, layer, expert) ascending use times
@@ -105,6 +125,13 @@ int pm_oracle_add_use_times(pm_ctx* ctx, uint64_t seq_id, int layer, int expert,
 /* CacheMngr::update_priority (src/cpp_worker/cache.cpp:400-430,584-591): prob is
  * [n_layers, num_expert] float32 for layers start_layer.. */
 int pm_update_priority(pm_ctx* ctx, const float* prob, int n_layers, int start_layer);
+/* The input the reference's LegacyPredictor hands its model for the history-based
+ * predict_input_mode values one_token, decode_cumsum, last_use_distance and
+ * weighted_decode_cumsum (src/cpp_worker/predictor.cpp:48-80,143-175,351-365): out receives
+ * [num_layer, num_expert] float32. The history is kept by pm_report_layer (decode-size reports
+ * enter it, a prompt-size report at layer 0 starts a new sequence,
+ * src/cpp_worker/prefetcher.cpp:462-479); other modes read as zeros. */
+int pm_history_input(pm_ctx* ctx, float* out, size_t cap);
 
 /* One cache decision, in the order the schedule performed it. */
 typedef struct pm_event {
@@ -128,6 +155,12 @@ typedef struct pm_stats {
   int64_t kernel_launches;
 } pm_stats;
 int pm_stats_read(pm_ctx* ctx, pm_stats* out);
+/* The counters as they stood at the end of every model iteration (pm_layer_done of the last
+ * layer), oldest first: differences of consecutive entries are the per-forward series the
+ * reference's TimeProfiler keeps (src/cpp_worker/profiler.hpp:262-319, pushed in
+ * PrefetchMngr::one_moe_layer_done, src/cpp_worker/prefetcher.cpp:209-218) and its end-of-run
+ * report averages (src/cpp_worker/prefetcher.cpp:327-402). The copy and launch fields are 0. */
+int pm_iter_marks_read(pm_ctx* ctx, pm_stats* out, size_t cap, size_t* n);
 
 /* Device time and weight bytes of the grouped FFN launches made while the context option
  * profile_ffn=1 was set (CUDA events on the caller's stream around each launch). */
@@ -217,7 +250,8 @@ typedef struct pm_ffn_group {
   int32_t row_start;  /* first permuted row */
   int32_t row_count;
   int32_t inter;
-  int32_t pad;
+  int32_t ld_down;    /* row pitch of w_down in elements; 0 = inter. A larger pitch (the group is a slice of
+                         a wider matrix's columns) is accepted for bf16 launches of at most 16 rows per group */
 } pm_ffn_group;
 /* Bytes of device scratch pm_k_swiglu_ffn needs for n_rows rows in n_groups groups (launch plan:
  * group descriptors and per-tile tables, plus the bf16 intermediate rows). */

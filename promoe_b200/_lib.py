@@ -49,7 +49,7 @@ class pm_ffn_group(C.Structure):
     _fields_ = [("w_gate", C.c_void_p), ("w_up", C.c_void_p), ("w_down", C.c_void_p),
                 ("q_gate", C.c_void_p), ("q_up", C.c_void_p), ("q_down", C.c_void_p),
                 ("row_start", C.c_int32), ("row_count", C.c_int32), ("inter", C.c_int32),
-                ("pad", C.c_int32)]
+                ("ld_down", C.c_int32)]
 
 
 _vp, _i, _i64, _u64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_uint64, C.c_float, C.c_size_t
@@ -77,13 +77,20 @@ SIGNATURES = {
     "pm_report_expert": (_i, [_vp, _i, _i]),
     "pm_expert_done": (_i, [_vp, _i, _i]),
     "pm_layer_done": (_i, [_vp, _i]),
+    "pm_expert_acquire": (_i, [_vp, _i, _i, _vp, C.POINTER(_vp)]),
+    "pm_expert_release": (_i, [_vp, _i, _i, _vp]),
+    "pm_param_offset": (_i, [_vp, _i, C.POINTER(_sz)]),
+    "pm_temp_move_expert_to_gpu": (_i, [_vp, _i, _i, _vp, C.POINTER(_vp)]),
+    "pm_temp_move_expert_back_to_host": (_i, [_vp, _i, _i, _vp]),
     "pm_set_cur_seq": (_i, [_vp, _u64]),
     "pm_oracle_add_use_times": (_i, [_vp, _u64, _i, _i, C.POINTER(_i64), _i64]),
     "pm_update_priority": (_i, [_vp, C.POINTER(_f), _i, _i]),
+    "pm_history_input": (_i, [_vp, C.POINTER(_f), _sz]),
     "pm_event_log_enable": (_i, [_vp, _i]),
     "pm_event_log_read": (_i, [_vp, C.POINTER(pm_event), _sz, C.POINTER(_sz)]),
     "pm_event_log_clear": (_i, [_vp]),
     "pm_stats_read": (_i, [_vp, C.POINTER(pm_stats)]),
+    "pm_iter_marks_read": (_i, [_vp, C.POINTER(pm_stats), _sz, C.POINTER(_sz)]),
     "pm_profile_read": (_i, [_vp, C.POINTER(pm_profile), _i]),
     "pm_layer_set_weights": (_i, [_vp, _i, C.POINTER(pm_layer_weights)]),
     "pm_moe_forward": (_i, [_vp, _i, _vp, _i, _vp, _vp]),

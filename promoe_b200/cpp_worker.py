@@ -9,8 +9,9 @@ Differences that a caller can observe, all documented where they occur:
   * no worker threads exist: `launch_thread()` only marks the manager as launched, and every
     cache decision is taken synchronously inside the call that requests it;
   * errors raise `promoe_b200._lib.PromoeError` instead of aborting the process;
-  * `ref_one_expert_param` returns a placeholder: the fused MoE block reads expert weights by
-    cache slot, module parameters are not re-pointed on every fetch.
+  * `ref_one_expert_param` returns a tensor that aliases the expert's current cache line; it is
+    re-pointed inside `report_one_expert` (the reference does it on the fetch thread). The fused
+    MoE block does not need it: it reads expert weights by cache slot.
 """
 from __future__ import annotations
 
@@ -152,9 +153,25 @@ class PredictorBase:
     TorchScript module or a state dict of one MLP hidden -> d -> num_expert
     (first and last 2-D tensors = the two matrices, 1-D tensors = biases)."""
 
+    HISTORY_MODES = ("one_token", "decode_cumsum", "last_use_distance", "weighted_decode_cumsum")
+
     def __init__(self, meta: ModuleMeta):
         self.metas = meta
         self.loaded = {}
+        self.history_model = None   # optional module for the history-based input modes
+
+    def history_scores(self, hist: torch.Tensor):
+        """Scores from the history-based predictor input `hist` [num_layer, num_expert]
+        (LegacyPredictor::predict, src/cpp_worker/predictor.cpp:143-175,240-250): the model is applied
+        to the rows, its output reshaped to [rows, -1, num_expert] and summed over the rows. Without
+        a model file the history itself is the score of every layer (frequency / recency ranking).
+        Returns (scores [n_layers, num_expert] float32, first predicted layer)."""
+        E = hist.shape[1]
+        if self.history_model is None:
+            return hist.float().contiguous(), 0
+        with torch.no_grad():
+            out = self.history_model(hist.float().flatten(1, -1))
+        return out.reshape(hist.shape[0], -1, E).sum(0).float().contiguous(), 0
 
     @staticmethod
     def create(meta: ModuleMeta) -> "PredictorBase":
@@ -164,8 +181,14 @@ class PredictorBase:
         import os
         cache = self.metas.cache
         path = path if path is not None else cache.get("predictor_model_path")
-        if not path:
+        if not path or path == "None":
             return  # no predictor configured: prediction stays off
+        if cache.get("predict_input_mode") in self.HISTORY_MODES:
+            # one model file for the whole stack (LegacyPredictor::load_model, predictor.cpp:262-281)
+            self.history_model = torch.jit.load(path, map_location="cpu") if _is_torchscript(path) \
+                else torch.load(path, map_location="cpu", weights_only=False)
+            self.history_model.eval()
+            return
         if not os.path.isdir(path):
             raise FileNotFoundError(f"Model file is not a directory: {path}")
         from .synth import predict_layer_mapping
@@ -222,6 +245,10 @@ class ModelLoader:
         self.metas = meta
         self._names = {n: i for i, n in enumerate(meta._param_names)}
         self._dtype = {}
+        self._shape = {}     # (layer, expert, pid) -> tensor shape
+        self._logical = {}   # (layer, expert, pid) -> the tensor handed to the model
+        self._line = {}      # (layer, expert) -> line address the logical tensors point at
+        self._slab = None
 
     def add_one_expert_param(self, param: torch.Tensor, layer_id: int, expert_id: int, param_name: str):
         pid = self._names[param_name]
@@ -231,14 +258,46 @@ class ModelLoader:
         if t.is_floating_point() and t.dtype != torch.bfloat16 and t.dim() == 2:
             t = t.to(torch.bfloat16)  # the device kernels compute on bf16 weight matrices
         self._dtype[pid] = t.dtype
+        self._shape[(layer_id, expert_id, pid)] = tuple(t.shape)
         _register_one(self.metas.cache, layer_id, expert_id, pid, t)
 
     def build_logical_expert_param(self):
-        """Nothing to build: weights are addressed by cache slot, not through re-pointed tensors."""
+        """Logical tensors are created on demand by ref_one_expert_param."""
 
     def ref_one_expert_param(self, layer_id: int, expert_id: int, param) -> torch.Tensor:
+        """The tensor a module uses for one expert tensor (ModelLoader::ref_one_expert_param,
+        src/cpp_worker/model_loader.hpp:290-313): it has the registered shape and dtype once the
+        expert has been fetched and aliases the cache line that holds the expert; before the
+        first fetch it is empty. `PrefetchMngr.report_one_expert` re-points it."""
         pid = self._names[param] if isinstance(param, str) else int(param)
-        return torch.empty(0, dtype=self._dtype.get(pid, torch.bfloat16), device="cuda")
+        key = (layer_id, expert_id, pid)
+        if key not in self._logical:
+            self._logical[key] = torch.empty(0, dtype=self._dtype.get(pid, torch.bfloat16), device="cuda")
+        return self._logical[key]
+
+    def repoint(self, layer_id: int, expert_id: int, line_addr: int):
+        """Points the logical tensors of one expert at the cache line at `line_addr`."""
+        if self._line.get((layer_id, expert_id)) == line_addr:
+            return
+        cache = self.metas.cache
+        if self._slab is None:
+            self._slab = cache.slab_tensor()
+            self._slab_base = int(cache.get("slab_base"))
+            self._offsets = [cache.param_offset(p) for p in range(len(self._names))]
+        for pid in range(len(self._names)):
+            key = (layer_id, expert_id, pid)
+            t = self._logical.get(key)
+            if t is None:
+                continue
+            shape, dtype = self._shape[key], self._dtype[pid]
+            n = 1
+            for d in shape:
+                n *= d
+            off = line_addr - self._slab_base + self._offsets[pid]
+            view = self._slab[off:off + n * torch.empty(0, dtype=dtype).element_size()].view(dtype).view(shape)
+            with torch.no_grad():
+                t.set_(view)
+        self._line[(layer_id, expert_id)] = line_addr
 
     def pin_memory(self):
         if not self.metas.cache.pinned:  # init_gpu_mem_buffer may have pinned already
@@ -270,6 +329,10 @@ class CacheOracle:
                     use.setdefault((l, int(prefill_expert_selection[seq][l][off])), []).append(time_)
                 time_ += 1
             for r in range(int(reply_len[seq])):
+                row = entry_metas[begin + r]
+                if int(row[0]) != seq or int(row[1]) != r:  # the reference CHECKs the same (cache.cpp:624-625)
+                    raise ValueError(f"trace entry {begin + r} is (seq {int(row[0])}, token {int(row[1])}), "
+                                     f"expected (seq {seq}, token {r})")
                 for l in range(self._L):
                     for e in decode_expert_selection[begin + r][l].tolist():
                         use.setdefault((l, int(e)), []).append(time_)
@@ -311,15 +374,32 @@ class CacheMngr:
 
 
 class CacheStatistics:
-    """Per layer-call ready / unready counts (src/cpp_worker/profiler.hpp:201-251)."""
+    """Per layer-call ready / unready counts (src/cpp_worker/profiler.hpp:201-251): one row per
+    `report_one_layer`, filled from the library's counters. "Ready" is an activated expert that was
+    completely resident when it was demanded, "unready" one whose copy the demand had to issue or
+    finish (the reference counts whether the main thread had to spin in wait_expert,
+    src/cpp_worker/prefetcher.cpp:243-258; here the host never waits, the device does)."""
 
-    def __init__(self):
+    def __init__(self, cache: ExpertCache | None = None):
+        self._cache = cache
         self.rows = []
+        self._last = (0, 0)
+
+    def _settle(self):
+        if self._cache is None or not self.rows:
+            return
+        st = self._cache.stats()
+        now = (st["ready"], st["unready"])
+        self.rows[-1][0] += now[0] - self._last[0]
+        self.rows[-1][1] += now[1] - self._last[1]
+        self._last = now
 
     def forward(self):
+        self._settle()
         self.rows.append([0, 0])
 
     def to_tensor(self) -> torch.Tensor:
+        self._settle()
         return torch.tensor(self.rows, dtype=torch.float32).reshape(-1, 2)
 
     def dump_average(self, prefill_cnt_threshold: int) -> torch.Tensor:
@@ -333,11 +413,75 @@ class CacheStatistics:
 
 
 class TimeProfiler:
-    def __init__(self):
-        self.series = {TimeType.kModelForward: []}
+    """The per-forward series of the reference's TimeProfiler (src/cpp_worker/profiler.hpp:262-319).
+    The counter series come from the library (differences of its end-of-iteration snapshots); the
+    forward times and sequence lengths are pushed on the Python side, where the reference's hooks
+    produce them (TimingHook, MoeLayerHook at layer 0)."""
 
-    def push(self, kind, dur_us):
-        self.series.setdefault(kind, []).append(int(dur_us))
+    COUNTER_KINDS = {"activated": "activated_experts", "hit": "precise_hit", "miss": "precise_miss",
+                     "ready": "ready", "unready": "unready", "prefetch_hit": "prefetch_hit",
+                     "prefetch_miss": "prefetch_miss"}
+
+    def __init__(self, cache: ExpertCache | None = None):
+        self._cache = cache
+        self.series = {TimeType.kModelForward: [], "seq_len": [], "predict_time": []}
+
+    def push(self, kind, value):
+        self.series.setdefault(kind, []).append(int(value))
+
+    def to_tensor(self, kind) -> torch.Tensor:
+        """One value per completed model iteration for the counter kinds ("hit", "miss", "ready",
+        "unready", "prefetch_hit", "prefetch_miss", "activated", "wait_time"), one per push for
+        TimeType.kModelForward, "seq_len" and "predict_time"."""
+        if kind in self.COUNTER_KINDS:
+            field, prev, out = self.COUNTER_KINDS[kind], 0, []
+            for m in (self._cache.iter_marks() if self._cache is not None else []):
+                out.append(m[field] - prev)
+                prev = m[field]
+            return torch.tensor(out, dtype=torch.int64)
+        if kind == "wait_time":  # the host never waits for a copy: the device stream does
+            n = len(self._cache.iter_marks()) if self._cache is not None else 0
+            return torch.zeros(n, dtype=torch.int64)
+        return torch.tensor(self.series.get(kind, []), dtype=torch.int64)
+
+    def report_lines(self) -> list[str]:
+        """The `key:value` lines the reference prints when its profiler is destroyed
+        (src/cpp_worker/prefetcher.cpp:327-402), which its sweep scripts parse: means over the decode
+        and the prefill iterations after the warm-up prompts (the first four prefill iterations and
+        everything before them are skipped, five when the run starts llama.cpp style with prefill
+        iterations at positions 0, 1, 2)."""
+        seq = self.to_tensor("seq_len")
+        n = min(len(seq), len(self.to_tensor("hit")))
+        seq = seq[:n]
+        is_prefill, is_decode = seq > 1, seq <= 1
+        prefill_idx = torch.nonzero(is_prefill).flatten().tolist()
+        skip = 5 if len(prefill_idx) > 2 and prefill_idx[1] == 1 and prefill_idx[2] == 2 else 4
+        start = n if len(prefill_idx) <= skip else prefill_idx[skip]
+        is_prefill[:start] = False
+        is_decode[:start] = False
+
+        def mean(kind, idx, scale=1.0):
+            t = self.to_tensor(kind)[:n][idx].float()
+            return float("nan") if t.numel() == 0 else t.mean().item() / scale
+
+        lines = []
+        for on, off, name in (("ready", "unready", "ready"), ("hit", "miss", "hit"),
+                              ("prefetch_hit", "prefetch_miss", "prefetch_hit")):
+            for stage, idx in (("decode", is_decode), ("prefill", is_prefill)):
+                a, b = mean(on, idx), mean(off, idx)
+                off_name = name.replace("hit", "miss") if "hit" in name else "unready"
+                lines += [f"{stage}_stage_{name}_cnt:{a:g}", f"{stage}_stage_{off_name}_cnt:{b:g}",
+                          f"{stage}_stage_{name}_rate:{(a / (a + b) if a + b else float('nan')):g}"]
+        fwd = self.to_tensor(TimeType.kModelForward)[:n]
+        for stage, idx in (("decode", is_decode), ("prefill", is_prefill)):
+            lines.append(f"{stage}_stage_wait_time:{mean('wait_time', idx, 1000.0):g}")
+        for stage, idx in (("decode", is_decode), ("prefill", is_prefill)):
+            t = fwd[idx[:len(fwd)]].float() if len(fwd) else fwd.float()
+            lines.append(f"{stage}_stage_forward_time:{(t.mean().item() / 1000.0 if t.numel() else float('nan')):g}")
+        lines += [f"num_prefill_iter:{int(is_prefill.sum())}", f"num_decode_iter:{int(is_decode.sum())}"]
+        pt = self.to_tensor("predict_time")[10:].float()
+        lines.append(f"predict_time:{(pt.mean().item() / 1000.0 if pt.numel() else float('nan')):g}")
+        return lines
 
 
 class TimerGuard:
@@ -389,20 +533,35 @@ class PrefetchMngr:
         self.metas, self.model_loader, self.predictor = meta, model_loader, predictor
         self._cache = meta.cache
         self.cache = CacheMngr(self._cache, meta.num_layer, meta.num_expert)
-        self.cache_stats = CacheStatistics()
-        self.profiler = TimeProfiler()
+        self.cache_stats = CacheStatistics(self._cache)
+        self.profiler = TimeProfiler(self._cache)
         # The reference creates a private non-blocking compute stream and makes torch use it
         # (prefetcher.cpp:406-418); this keeps that contract for the caller's set_stream().
-        self._stream = torch.cuda.Stream()
-        self.compute_stream = self._stream.cuda_stream
+        self._stream = torch.cuda.Stream() if torch.cuda.is_available() else None  # policy-only use needs no GPU
+        self.compute_stream = self._stream.cuda_stream if self._stream is not None else 0
         self.copy_stream = 0  # owned by the library, created with the slab
         self.launched = False
 
     def launch_thread(self):
-        self.launched = True  # no worker threads: decisions are taken inside the requesting call
+        """No worker threads exist: decisions are taken inside the requesting call. What remains of
+        the reference's launch is the end-of-run report, printed at interpreter exit like the
+        reference's profiler destructor does."""
+        if not self.launched:
+            import atexit
+            atexit.register(self._report_at_exit)
+        self.launched = True
+
+    def _report_at_exit(self):
+        try:
+            if len(self.profiler.to_tensor("seq_len")) and len(self.profiler.to_tensor("hit")):
+                print("\n".join(self.profiler.report_lines()), flush=True)
+        except Exception:
+            pass  # the context may already be closed
 
     def reload_env(self):
-        pass
+        """Re-reads the environment switches of the reference's logging and tracing
+        (src/cpp_worker/prefetcher.cpp:659-662). Tracing is read from the environment on every span
+        here, so there is nothing to cache."""
 
     def init_gpu_mem_buffer(self):
         # The reference pins after building the lines (utils/__init__.py:331-334); here the pinned
@@ -419,18 +578,53 @@ class PrefetchMngr:
                   C.cast(experts.data_ptr(), C.POINTER(C.c_int64)), experts.numel())
 
     def report_one_expert(self, layer_id: int, expert_id: int):
-        self._cache.report_expert(layer_id, expert_id)
+        """report_one_expert + wait_expert (src/cpp_worker/prefetcher.cpp:225-258). With a slab, torch's
+        current stream is made to wait for the expert's copy (the host does not wait) and the expert's
+        logical parameters are pointed at its cache line."""
+        if self._cache.get("slab_impl") == "none":
+            self._cache.report_expert(layer_id, expert_id)
+            return
+        line = self._cache.expert_acquire(layer_id, expert_id, torch.cuda.current_stream().cuda_stream)
+        self.model_loader.repoint(layer_id, expert_id, line)
 
     def one_expert_done(self, layer_id: int, expert_id: int):
-        self._cache.expert_done(layer_id, expert_id)
+        if self._cache.get("slab_impl") == "none":
+            self._cache.expert_done(layer_id, expert_id)
+            return
+        self._cache.expert_release(layer_id, expert_id, torch.cuda.current_stream().cuda_stream)
 
     def one_moe_layer_done(self, layer_id: int):
         self._cache.layer_done(layer_id)
+        if layer_id == self.metas.num_layer - 1:
+            self._predict_from_history()
+
+    def _predict_from_history(self):
+        """End of a model iteration in a history-based input mode (PredictWorker::on_one_iter_done ->
+        do_one_task_impl, src/cpp_worker/worker.cpp:6-77): score every layer from the access history,
+        hand the scores to the NN policy and prefetch the top experts of every layer in layer order."""
+        mode = self._cache.get("predict_input_mode")
+        if mode not in PredictorBase.HISTORY_MODES:
+            return
+        n = int(self._cache.get("num_predict_expert_per_layer"))
+        nn = self._cache.get("cache_policy") == "nn"
+        if n <= 0 and not nn:
+            return
+        t0 = time.perf_counter()
+        scores, start = self.predictor.history_scores(torch.from_numpy(self._cache.history_input()))
+        self.profiler.push("predict_time", (time.perf_counter() - t0) * 1e6)
+        if nn:
+            self._cache.update_priority(scores.numpy(), start)
+        if n > 0:
+            order = torch.argsort(scores, dim=1, descending=True, stable=True)[:, :n]
+            for i in range(scores.shape[0]):
+                self._cache.prefetch_layer(start + i, order[i].tolist())
 
     def report_moe_attn_logits(self, layer_id: int, attn_logits: torch.Tensor):
         pass  # only the moe_layer_logits input mode has a device predictor
 
     def report_moe_layer_logits(self, layer_id: int, layer_logits: torch.Tensor):
+        if layer_id == 0 and layer_logits.dim() == 3:
+            self.profiler.push("seq_len", layer_logits.shape[1])  # prefetcher.cpp:453-456
         if self._cache.get("predict_input_mode") != "moe_layer_logits":
             return  # the other input modes ignore hidden states (predictor.cpp:641-648)
         if layer_logits.dim() != 3:
@@ -444,10 +638,15 @@ class PrefetchMngr:
         return TimerGuard(self.profiler)
 
     def temp_move_expert_to_gpu(self, layer_id: int, expert_id: int):
-        raise _lib.PromoeError(4, "temp_move_expert_to_gpu serves exllama post_init, which this library does not run")
+        """Copies the expert into the spare cache line and points its logical parameters there, so
+        that a quantised layer's post_init can work on device tensors
+        (src/cpp_worker/prefetcher.cpp:664-680; used by AutoGPTQFirstPostInitHook)."""
+        line = self._cache.temp_move_expert_to_gpu(layer_id, expert_id, torch.cuda.current_stream().cuda_stream)
+        self.model_loader.repoint(layer_id, expert_id, line)
 
     def temp_move_expert_back_to_host(self, layer_id: int, expert_id: int):
-        raise _lib.PromoeError(4, "temp_move_expert_back_to_host serves exllama post_init, which this library does not run")
+        """Copies the spare line back into the expert's pinned host record (prefetcher.cpp:681-697)."""
+        self._cache.temp_move_expert_back_to_host(layer_id, expert_id, torch.cuda.current_stream().cuda_stream)
 
     def __reduce__(self):
         raise TypeError("PrefetchMngr cannot be pickled across processes")

@@ -552,7 +552,66 @@ std::string CacheEngine::report_layer(int layer, int64_t* ids, int64_t n, std::v
   layer_q_[layer].clear();
   std::string err = drain(out);
   counters.activated_experts += n;
+  record_history(layer, ids, n);
   return err;
+}
+
+// LegacyPredictor::add_one_layer / start_of_new_sequence (src/cpp_worker/predictor.cpp:48-80,351-365),
+// called as PrefetchMngr::record_then_predict_and_prefetch does (src/cpp_worker/prefetcher.cpp:462-479):
+// a report of at most num_expert_per_token ids is a decode step and enters the history; a larger one
+// is a prompt pass, and at layer 0 it starts a new sequence.
+void CacheEngine::record_history(int layer, const int64_t* ids, int64_t n) {
+  const std::string& mode = cfg_.predict_input_mode;
+  const bool counts = mode == "one_token" || mode == "decode_cumsum";
+  const bool distance = mode == "last_use_distance", weighted = mode == "weighted_decode_cumsum";
+  if (!counts && !distance && !weighted) return;
+  const size_t LE = (size_t)cfg_.num_layer * cfg_.num_expert;
+  if (access_count_.empty()) {
+    access_count_.assign(LE, 0.f);
+    last_use_distance_.assign(LE, 0.f);
+    weighted_access_.assign(LE, 0.f);
+  }
+  if (n > cfg_.num_expert_per_token) {
+    if (layer == 0) {
+      if (mode == "decode_cumsum") std::fill(access_count_.begin(), access_count_.end(), 0.f);
+      if (distance) std::fill(last_use_distance_.begin(), last_use_distance_.end(), 0.f);
+      if (weighted) std::fill(weighted_access_.begin(), weighted_access_.end(), 0.f);
+    }
+    return;
+  }
+  const size_t row = (size_t)layer * cfg_.num_expert;
+  if (distance)
+    for (int e = 0; e < cfg_.num_expert; ++e) last_use_distance_[row + e] += 1.f;
+  if (weighted)
+    for (int e = 0; e < cfg_.num_expert; ++e) weighted_access_[row + e] /= (float)cfg_.predict_input_decay;
+  for (int64_t i = 0; i < n; ++i) {
+    if (counts) access_count_[row + ids[i]] += 1.f;
+    if (distance) last_use_distance_[row + ids[i]] = 0.f;
+    if (weighted) weighted_access_[row + ids[i]] += 1.f;
+  }
+}
+
+std::vector<float> CacheEngine::history_input() const {
+  const size_t LE = (size_t)cfg_.num_layer * cfg_.num_expert;
+  std::vector<float> out(LE, 0.f);
+  if (access_count_.empty()) return out;
+  const std::string& mode = cfg_.predict_input_mode;
+  if (mode == "one_token") {
+    out = access_count_;
+  } else if (mode == "decode_cumsum") {  // each layer's counts divided by their sum, 0 where the sum is 0
+    for (int l = 0; l < cfg_.num_layer; ++l) {
+      float sum = 0.f;
+      for (int e = 0; e < cfg_.num_expert; ++e) sum += access_count_[(size_t)l * cfg_.num_expert + e];
+      for (int e = 0; e < cfg_.num_expert; ++e)
+        out[(size_t)l * cfg_.num_expert + e] = sum > 0.f ? access_count_[(size_t)l * cfg_.num_expert + e] / sum : 0.f;
+    }
+  } else if (mode == "last_use_distance") {  // max(dmax - d, 0) / dmax
+    const float dmax = (float)cfg_.predict_input_reuse_distance_max;
+    for (size_t i = 0; i < LE; ++i) out[i] = std::max(dmax - last_use_distance_[i], 0.f) / dmax;
+  } else if (mode == "weighted_decode_cumsum") {
+    out = weighted_access_;
+  }
+  return out;
 }
 
 // PrefetchLayerTask, src/cpp_worker/prefetcher.cpp:585-611
@@ -605,6 +664,7 @@ std::string CacheEngine::expert_done(int layer, int e) {
 
 std::string CacheEngine::layer_done(int layer) {
   if (layer < 0 || layer >= cfg_.num_layer) return "layer out of range";
+  if (layer == cfg_.num_layer - 1) iter_marks.push_back(counters);  // one model iteration ends
   return "";
 }
 

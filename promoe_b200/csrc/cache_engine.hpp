@@ -91,8 +91,21 @@ class CacheEngine {
   Config& config() { return cfg_; }
   const Config& config() const { return cfg_; }
   Counters counters;
+  // Snapshot of `counters` at the end of every model iteration (layer_done of the last layer): the
+  // per-forward series of the reference's TimeProfiler (src/cpp_worker/profiler.hpp:262-275,
+  // pushed in PrefetchMngr::one_moe_layer_done, src/cpp_worker/prefetcher.cpp:209-218) are the
+  // differences of consecutive snapshots.
+  std::vector<Counters> iter_marks;
   bool log_enabled = false;
   std::vector<CacheEvent> log;
+
+  // The history-based predictor inputs of the reference's LegacyPredictor
+  // (src/cpp_worker/predictor.cpp:48-80,351-365), fed by every decode-size report_layer
+  // (PrefetchMngr::record_then_predict_and_prefetch, src/cpp_worker/prefetcher.cpp:462-479):
+  // access counts, layer steps since the last use, and access counts decayed by predict_input_decay.
+  // history_input() gives the tensor the predictor model receives for the configured
+  // predict_input_mode (src/cpp_worker/predictor.cpp:143-175), [num_layer * num_expert].
+  std::vector<float> history_input() const;
 
   // use-time lookup for the Belady policy
   const std::vector<int64_t>* use_times(uint64_t seq, int flat) const;
@@ -120,6 +133,8 @@ class CacheEngine {
   Config& cfg_;
   std::vector<Pool> pools_;
   std::vector<ExpertState> experts_;
+  void record_history(int layer, const int64_t* ids, int64_t n);
+  std::vector<float> access_count_, last_use_distance_, weighted_access_;  // [L * E] each
   std::vector<float> priority_;  // "nn" policy only: [L * E]
   float max_priority_ = std::numeric_limits<float>::min();
   std::string deferred_error_;  // first policy error raised inside hit()

@@ -43,6 +43,8 @@ static int plan_core(const pm_ffn_group* groups, int n_groups, int hidden, unsig
     const pm_ffn_group& g = groups[i];
     if (g.row_count <= 0) continue;
     if (g.inter % 32 != 0 || g.inter <= 0) return fail(PM_ERR_INVALID, "inter must be a positive multiple of 32");
+    if (g.ld_down != 0 && g.ld_down != g.inter && (g.ld_down < g.inter || !split))
+      return fail(PM_ERR_INVALID, "ld_down must be 0 or at least inter, and a wider pitch needs chunks of at most 16 rows");
     for (int r0 = 0; r0 < g.row_count; r0 += chunk_rows) {
       const int n_gu = (g.inter + tile_gu - 1) / tile_gu, n_dn = hidden / tile_dn;
       if (blob != nullptr) {
@@ -52,6 +54,7 @@ static int plan_core(const pm_ffn_group* groups, int n_groups, int hidden, unsig
         d.row_start = g.row_start + r0;
         d.row_count = std::min(chunk_rows, g.row_count - r0);
         d.inter = g.inter;
+        d.ld_down = g.ld_down;
         d.tile_start_gu = tg;
         d.tile_start_dn = td;
         desc[n] = d;
@@ -66,7 +69,7 @@ static int plan_core(const pm_ffn_group* groups, int n_groups, int hidden, unsig
     }
   }
   info->n_desc = n; info->tiles_gu = tg; info->tiles_dn = td; info->max_rows = mr; info->max_inter = mi;
-  if (blob != nullptr) std::memset(blob + info->off_counters(), 0, 16);
+  if (blob != nullptr) std::memset(blob + info->off_counters(), 0, info->counter_bytes());
   return PM_OK;
 }
 
@@ -184,10 +187,12 @@ int pm_k_swiglu_ffn(const pm_ffn_group* groups, int n_groups, int quant4, const 
   // The plan upload is from pageable memory, so it is staged before this call returns.
   PM_CUDA(cudaMemcpyAsync(scratch, blob.data(), blob.size(), cudaMemcpyHostToDevice, s));
   __nv_bfloat16* hbuf = (__nv_bfloat16*)((unsigned char*)scratch + plan_bytes);
-  // PM_FFN_TWO_LAUNCH=1 selects the two-launch path (for comparisons); the default is the fused kernel.
-  static const bool two_launch = std::getenv("PM_FFN_TWO_LAUNCH") != nullptr;
+  if (quant4)
+    for (int i = 0; i < n_groups; ++i)
+      if (groups[i].row_count > 0 && groups[i].ld_down != 0 && groups[i].ld_down != groups[i].inter)
+        return fail(PM_ERR_INVALID, "swiglu_ffn: uint4 experts take no ld_down");
   PM_CUDA(launch_swiglu_ffn((const unsigned char*)scratch, info, quant4, (const __nv_bfloat16*)x, hidden,
-                            row_token, hbuf, info.max_inter, yexp, s, nullptr, !two_launch));
+                            row_token, hbuf, info.max_inter, yexp, s, nullptr));
   return PM_OK;
 }
 

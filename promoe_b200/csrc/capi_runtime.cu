@@ -77,11 +77,15 @@ int pm_ctx_get(pm_ctx* ctx, const char* key, char* buf, size_t cap) {
   else if (k == "seq_len") v = std::to_string(ctx->seq_len);
   else if (k == "tc_launches") v = std::to_string(ctx->tc_launches);
   else if (k == "tc_error") {
+    int32_t code = 0;
     if (ctx->have_last_stream) cudaStreamSynchronize(ctx->last_stream);
-    v = std::to_string(ctx->h_tc_err ? *ctx->h_tc_err : 0);
+    if (ctx->d_tc_err) cudaMemcpy(&code, ctx->d_tc_err, 4, cudaMemcpyDeviceToHost);
+    v = std::to_string(code);
   }
   else if (k == "slab_impl") v = !ctx->slab_built ? "none" : (ctx->slab_vmm ? "vmm" : "cudamalloc");
   else if (k == "line_stride") v = std::to_string(ctx->line_stride);
+  else if (k == "slab_base") v = std::to_string((unsigned long long)(uintptr_t)ctx->slab);
+  else if (k == "slab_bytes") v = std::to_string((unsigned long long)ctx->line_stride * (ctx->n_lines + 1));
   else if (k == "num_lines") v = std::to_string(ctx->n_lines);
   else if (k == "record_bytes") v = std::to_string(ctx->param_offset.empty() ? 0 : ctx->param_offset.back());
   else if (!ctx->cfg.get(k, &v)) return fail(PM_ERR_INVALID, "unknown config key " + k);
@@ -108,10 +112,6 @@ int pm_ctx_set(pm_ctx* ctx, const char* key, const char* value) {
   }
   if (k == "device_plan") {
     ctx->device_plan = (v == "1" || v == "true" || v == "True" || v == "on");
-    return PM_OK;
-  }
-  if (k == "fused_ffn") {
-    ctx->fused_ffn = (v == "1" || v == "true" || v == "True" || v == "on");
     return PM_OK;
   }
   if (k == "profile_ffn") {
@@ -247,6 +247,35 @@ int pm_expert_done(pm_ctx* ctx, int layer, int expert) {
   return from(ctx->eng->expert_done(layer, expert), PM_ERR_INVALID);
 }
 
+int pm_expert_acquire(pm_ctx* ctx, int layer, int expert, void* stream, void** line) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  return rt_expert_acquire(ctx, layer, expert, (cudaStream_t)stream, line);
+}
+
+int pm_expert_release(pm_ctx* ctx, int layer, int expert, void* stream) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  return rt_expert_release(ctx, layer, expert, (cudaStream_t)stream);
+}
+
+int pm_param_offset(pm_ctx* ctx, int param_id, size_t* offset) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  if (!ctx->pinned) return fail(PM_ERR_STATE, "param_offset before pin_all");
+  if (!offset || param_id < 0 || param_id >= ctx->cfg.num_per_expert_param())
+    return fail(PM_ERR_INVALID, "tensor index out of range");
+  *offset = ctx->param_offset[param_id];
+  return PM_OK;
+}
+
+int pm_temp_move_expert_to_gpu(pm_ctx* ctx, int layer, int expert, void* stream, void** line) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  return rt_temp_move(ctx, layer, expert, true, (cudaStream_t)stream, line);
+}
+
+int pm_temp_move_expert_back_to_host(pm_ctx* ctx, int layer, int expert, void* stream) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  return rt_temp_move(ctx, layer, expert, false, (cudaStream_t)stream, nullptr);
+}
+
 int pm_layer_done(pm_ctx* ctx, int layer) {
   if (need(ctx)) return PM_ERR_INVALID;
   return from(ctx->eng->layer_done(layer), PM_ERR_INVALID);
@@ -268,6 +297,15 @@ int pm_update_priority(pm_ctx* ctx, const float* prob, int n_layers, int start_l
   if (need(ctx)) return PM_ERR_INVALID;
   if (!prob) return fail(PM_ERR_INVALID, "null scores");
   return from(ctx->eng->update_priority(prob, n_layers, start_layer));
+}
+
+int pm_history_input(pm_ctx* ctx, float* out, size_t cap) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  const size_t LE = (size_t)ctx->cfg.num_layer * ctx->cfg.num_expert;
+  if (!out || cap < LE) return fail(PM_ERR_INVALID, "history_input: buffer of num_layer * num_expert floats needed");
+  std::vector<float> h = ctx->eng->history_input();
+  std::memcpy(out, h.data(), LE * sizeof(float));
+  return PM_OK;
 }
 
 int pm_event_log_enable(pm_ctx* ctx, int on) {
@@ -307,6 +345,27 @@ int pm_stats_read(pm_ctx* ctx, pm_stats* out) {
   out->h2d_bytes = ctx->h2d_bytes;
   out->h2d_copies = ctx->h2d_copies;
   out->kernel_launches = ctx->kernel_launches;
+  return PM_OK;
+}
+
+int pm_iter_marks_read(pm_ctx* ctx, pm_stats* out, size_t cap, size_t* n) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  const std::vector<Counters>& marks = ctx->eng->iter_marks;
+  if (n) *n = marks.size();
+  if (out == nullptr) return PM_OK;
+  for (size_t i = 0; i < std::min(cap, marks.size()); ++i) {
+    const Counters& k = marks[i];
+    pm_stats s{};
+    s.precise_hit = k.precise_hit;
+    s.precise_miss = k.precise_miss;
+    s.prefetch_hit = k.prefetch_hit;
+    s.prefetch_miss = k.prefetch_miss;
+    s.ready = k.ready;
+    s.unready = k.unready;
+    s.activated_experts = k.activated_experts;
+    s.layer_calls = k.layer_calls;
+    out[i] = s;
+  }
   return PM_OK;
 }
 

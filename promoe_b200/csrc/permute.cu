@@ -19,13 +19,15 @@ constexpr int kMaxExperts = 256;
 __global__ void __launch_bounds__(kPermThreads)
 permute_kernel(const int32_t* __restrict__ topk_ids, int R, int k, int E, int32_t* __restrict__ counts,
                int32_t* __restrict__ offsets, int32_t* __restrict__ row_token,
-               int32_t* __restrict__ pos, int32_t* __restrict__ err_flag, int tail_rows, int T) {
+               int32_t* __restrict__ pos, int32_t* __restrict__ err_flag, int tail_rows, int T,
+               int32_t* __restrict__ zero_words, int zero_n) {
   __shared__ int cnt[kMaxExperts];
   __shared__ int off[kMaxExperts + 1];
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
   for (int e = tid; e < E; e += kPermThreads) cnt[e] = 0;
+  for (int i = tid; i < zero_n; i += kPermThreads) zero_words[i] = 0;
   // Rows after the R routed ones belong to the shared experts: every token once per shared expert.
   for (int i = tid; i < tail_rows; i += kPermThreads) row_token[R + i] = i % T;
   __syncthreads();
@@ -178,16 +180,22 @@ cudaError_t launch_gather_rows(const void* src, const int32_t* index, int n_rows
 
 cudaError_t launch_permute(const int32_t* topk_ids, int R, int k, int E, int32_t* counts,
                            int32_t* offsets, int32_t* row_token, int32_t* pos, int32_t* err_flag,
-                           int tail_rows, int T, cudaStream_t s, int32_t* scratch, size_t scratch_ints) {
+                           int tail_rows, int T, cudaStream_t s, int32_t* scratch, size_t scratch_ints,
+                           int32_t* zero_words, int zero_n) {
   const int n_chunks = (R + kChunk - 1) / kChunk;
+  if (zero_words == nullptr) zero_n = 0;
   if (R > 2 * kChunk && scratch != nullptr && scratch_ints >= (size_t)n_chunks * E) {
     permute_count_kernel<<<n_chunks, 256, 0, s>>>(topk_ids, R, E, scratch, err_flag, pos);
     permute_scan_kernel<<<1, 256, 0, s>>>(scratch, n_chunks, E, counts, offsets, row_token, R, tail_rows, T > 0 ? T : 1);
     permute_place_kernel<<<n_chunks, 1024, 0, s>>>(topk_ids, R, k, E, scratch, row_token, pos);
+    if (zero_n > 0) {
+      cudaError_t e = cudaMemsetAsync(zero_words, 0, (size_t)zero_n * 4, s);
+      if (e != cudaSuccess) return e;
+    }
     return cudaGetLastError();
   }
   permute_kernel<<<1, kPermThreads, 0, s>>>(topk_ids, R, k, E, counts, offsets, row_token, pos, err_flag,
-                                            tail_rows, T > 0 ? T : 1);
+                                            tail_rows, T > 0 ? T : 1, zero_words, zero_n);
   return cudaGetLastError();
 }
 

@@ -42,7 +42,8 @@ struct GroupDesc {
   int32_t inter;
   int32_t tile_start_gu;  // first CTA tile of this chunk in the gate/up launch
   int32_t tile_start_dn;  // first CTA tile of this chunk in the down launch
-  int32_t pad;
+  int32_t ld_down;        // row pitch of w_down in elements (0 = inter); larger when the chunk is one
+                          // slice of a wider matrix's reduction dimension (fused decode kernel only)
 };
 
 constexpr int kTileRows = 64;       // weight rows per CTA tile of the staged kernel (4 warps x 16)
@@ -58,20 +59,25 @@ cudaError_t launch_gate_topk(const __nv_bfloat16* x, const __nv_bfloat16* w_gate
                              int32_t* topk_ids, float* topk_w, int32_t* topk_slot,
                              float* shared_scale, float* logits_out, cudaStream_t s);
 
+// zero_words / zero_n: an int32 array the permutation also clears (the dependency counters of the
+// fused FFN launch that follows on the same stream), or nullptr.
 cudaError_t launch_permute(const int32_t* topk_ids, int R, int k, int E, int32_t* counts,
                            int32_t* offsets, int32_t* row_token, int32_t* pos, int32_t* err_flag,
                            int tail_rows, int T, cudaStream_t s, int32_t* scratch = nullptr,
-                           size_t scratch_ints = 0);
+                           size_t scratch_ints = 0, int32_t* zero_words = nullptr, int zero_n = 0);
 
 // Geometry of one grouped FFN launch pair. The device blob it describes holds, 16-byte aligned
 // and in this order: n_desc GroupDesc, tiles_gu int32 (chunk index of every gate/up CTA tile),
-// tiles_dn int32 (same for the down launch), then two int32 tile counters that start at zero.
+// tiles_dn int32 (same for the down launch), then n_desc + 1 int32 dependency counters that start
+// at zero (the fused kernel counts the finished gate/up tiles per chunk and in total there) and one
+// int32 error word.
 struct FfnPlanInfo {
   int n_desc = 0, tiles_gu = 0, tiles_dn = 0, max_rows = 0, max_inter = 0;
   size_t off_tile_gu() const { return ((size_t)n_desc * sizeof(GroupDesc) + 15) / 16 * 16; }
   size_t off_tile_dn() const { return off_tile_gu() + ((size_t)tiles_gu * 4 + 15) / 16 * 16; }
   size_t off_counters() const { return off_tile_dn() + ((size_t)tiles_dn * 4 + 15) / 16 * 16; }
-  size_t blob_bytes() const { return off_counters() + 16; }  // two zeroed tile counters (fused kernel)
+  size_t counter_bytes() const { return ((size_t)(n_desc + 2) * 4 + 15) / 16 * 16; }
+  size_t blob_bytes() const { return off_counters() + counter_bytes(); }
 };
 
 // Splits caller groups into chunks of at most kMaxChunkRows rows, assigns CTA tile ranges and
@@ -82,44 +88,59 @@ int plan_groups_into(const pm_ffn_group* groups, int n_groups, int hidden, unsig
 int plan_groups_size(const pm_ffn_group* groups, int n_groups, int hidden, FfnPlanInfo* info,
                      int chunk_rows = kMaxChunkRows);
 
-// Everything the device-side planner needs to describe the resident experts of one layer.
-struct ResidentPlanArgs {
+constexpr int kMaxSharedSlices = 8;
+constexpr int kMaxFusedGroups = 256 + kMaxSharedSlices;  // groups of one fused launch
+
+// What the fused kernel needs to describe, on the device, the shared expert and the routed experts
+// a layer's slot table shows resident (no host round trip between the router and this launch).
+// The shared expert is cut along its intermediate dimension into slices of `shared_slice` columns,
+// each a group of its own with its own output rows (the combine adds them), so that every tile
+// of the launch has about the same weight bytes.
+struct ResidentArgs {
+  const int32_t* counts;      // [num_expert] routed rows per expert (permutation output)
+  const int32_t* offsets;     // [num_expert + 1]
+  const int32_t* slot_table;  // [num_expert] cache slot of each expert, -1 = absent
   const unsigned char* pool_base;  // first cache line of the layer's pool
   size_t line_stride;
   size_t off_gate, off_up, off_down;  // tensor offsets inside a line
   const void *shared_w_gate, *shared_w_up, *shared_w_down;
-  int32_t num_expert, inter, shared_inter, hidden;
+  int32_t num_expert, inter, shared_inter, shared_slice;
   int32_t tokens, n_routed_rows;
-  // byte offsets of the sections inside the device blob (header of five int32 at offset 0)
-  size_t off_desc, off_tile_gu, off_tile_dn;
-  // Section sizes for num_expert experts plus the shared expert.
-  static size_t blob_bytes(int num_expert, int inter, int shared_inter, int hidden, size_t* off_desc,
-                           size_t* off_gu, size_t* off_dn) {
-    const size_t n = (size_t)num_expert + 1;
-    const size_t gu = (size_t)num_expert * (inter / kSplitTileGu) + shared_inter / kSplitTileGu;
-    const size_t dn = n * (hidden / kSplitTileDn);
-    *off_desc = 64;
-    *off_gu = *off_desc + n * sizeof(GroupDesc);
-    *off_dn = *off_gu + (gu * 4 + 15) / 16 * 16;
-    return *off_dn + (dn * 4 + 15) / 16 * 16;
-  }
 };
-// Plans (on the device) and launches the fused FFN for the shared expert and every activated
-// expert that the slot table shows resident. start_event (optional) is recorded between the
-// planner and the FFN kernel. Needs cooperative launch and at most kSplitMaxRows rows per expert.
-cudaError_t launch_resident_ffn(const int32_t* counts, const int32_t* offsets, const int32_t* slot_table,
-                                const ResidentPlanArgs& a, unsigned char* blob_dev, int max_rows,
-                                const __nv_bfloat16* x, const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h,
-                                float* yexp, cudaStream_t s, cudaEvent_t start_event);
+// Width of one slice of a shared expert of width shared_inter beside routed experts of width inter.
+inline int shared_slice_width(int inter, int shared_inter) {
+  int w = inter > 0 ? inter : shared_inter;
+  const int least = (shared_inter + kMaxSharedSlices - 1) / kMaxSharedSlices;
+  if (w < least) w = least;
+  w = (w + 31) / 32 * 32;
+  return w < shared_inter ? w : shared_inter;
+}
+inline int shared_slice_count(int inter, int shared_inter) {
+  if (shared_inter <= 0) return 0;
+  const int w = shared_slice_width(inter, shared_inter);
+  return (shared_inter + w - 1) / w;
+}
+// Launches the fused FFN for the shared expert (sliced) and every activated resident expert.
+// counters: kMaxFusedGroups + 1 int32 (per chunk, then the launch total), zero at launch. err: a device word that receives a non-zero
+// code if a bounded dependency wait gives up. Needs cooperative launch and at most kSplitMaxRows
+// rows per expert.
+cudaError_t launch_resident_ffn(const ResidentArgs& a, int32_t* counters, int32_t* err, int max_rows,
+                                const __nv_bfloat16* x, int hidden, const int32_t* row_token,
+                                __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s);
 bool resident_ffn_available(int max_rows);
 
-// Launches of at most kSplitMaxRows rows per chunk run as ONE cooperative kernel (gate/up tiles,
-// grid barrier, down tiles) unless `fused` is false or a mid_event is wanted; mid_event
-// (optional) is recorded between the gate/up and the down launch of the two-launch path.
+// bf16 launches of at most kSplitMaxRows rows per chunk run as ONE cooperative kernel (gate/up
+// tiles, then down tiles, a chunk's down tiles waiting on its gate/up tiles through the blob's
+// counters); uint4 launches and larger chunks run as a gate/up and a down launch, and mid_event
+// (optional) is recorded between the two. err (optional): device word that receives a code when a
+// bounded wait of the fused kernel gives up (default: the blob's own error word).
 cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& info, int quant4,
                               const __nv_bfloat16* x, int H, const int32_t* row_token,
                               __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s,
-                              cudaEvent_t mid_event = nullptr, bool fused = true);
+                              cudaEvent_t mid_event = nullptr, int32_t* err = nullptr);
+inline bool ffn_launch_is_fused(const FfnPlanInfo& info, int quant4) {
+  return !quant4 && info.max_rows <= kSplitMaxRows;
+}
 
 cudaError_t launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst,
                                cudaStream_t s);

@@ -95,12 +95,14 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
   const int cap = std::max(T, std::max(16, c->ws_tokens * 2));
   const int H = std::max(w.hidden, c->ws_hidden), I = std::max(max_inter, c->ws_inter);
   const int k = std::max(w.top_k, c->ws_topk);
-  const size_t R = (size_t)cap * k, rows = R + cap;  // routed rows + one shared-expert row per token
+  // routed rows + one shared-expert row per token; decode batches (at most kSplitMaxRows tokens) cut the
+  // shared expert into up to kMaxSharedSlices slices with a row per token each
+  const size_t R = (size_t)cap * k, rows = R + cap + (size_t)kSplitMaxRows * kMaxSharedSlices;
   {
     // worst case of one layer call: every expert plus the shared expert, chunks of 64 rows, smallest
     // tiles, and a few extra segments each aligned to 256 bytes
     FfnPlanInfo worst;
-    worst.n_desc = E + (int)(rows / kSplitMaxRows) + 8;
+    worst.n_desc = E + (int)(rows / kSplitMaxRows) + 8 + kMaxSharedSlices;
     worst.tiles_gu = worst.n_desc * ((I + kSplitTileGu - 1) / kSplitTileGu);
     worst.tiles_dn = worst.n_desc * ((H + kSplitTileDn - 1) / kSplitTileDn);
     c->plan_cap = align_up(worst.blob_bytes(), 256) + 64 * 256;
@@ -112,21 +114,22 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
     return o;
   };
   size_t o_ids = take(R * 4), o_slot = take(R * 4), o_w = take(R * 4), o_ss = take((size_t)cap * 4);
-  // counts [E], offsets [E + 1] and the permutation's error word travel to the host in one copy
-  size_t o_cnt = take((size_t)(2 * E + 2) * 4), o_rt = take(rows * 4), o_pos = take(R * 4);
+  // counts [E], offsets [E + 1], the permutation's error word and the FFN kernels' error word travel
+  // to the host in one copy
+  size_t o_cnt = take((size_t)(2 * E + 3) * 4), o_rt = take(rows * 4), o_pos = take(R * 4);
   size_t o_h = take(rows * I * 2), o_y = take(rows * H * 4), o_desc = take(c->plan_cap);
   size_t o_sc = take((size_t)c->cfg.num_layer * E * 4), o_ph = take((size_t)cap * 4096 * 4);
   size_t o_x = take((size_t)cap * H * 2), o_yo = take((size_t)cap * H * 2);
   const int Ir = std::max(w.inter, c->ws_inter_routed);
   const int Is = std::max(w.shared_inter, c->ws_inter_shared);
-  size_t o_res = take(ResidentPlanArgs::blob_bytes(E, Ir, Is, H, &c->res_off_desc, &c->res_off_gu, &c->res_off_dn));
+  size_t o_res = take((size_t)(kMaxFusedGroups + 1) * 4);
   size_t o_xp = take(rows * H * 2);
   {
     const size_t m_tiles = rows / 128 + (size_t)E + 2;
     c->tc_plan_cap = 16 * ((size_t)E + 2) + 16 * m_tiles * ((size_t)(std::max(I, Is) + 127) / 128 + (size_t)(H + 127) / 128) + 1024 +
                      768 * ((size_t)E + 2);  // three 256-byte roundings per segment, at most one segment per expert
   }
-  size_t o_tcp = take(c->tc_plan_cap), o_tce = take(16);
+  size_t o_tcp = take(c->tc_plan_cap);
   c->perm_scratch_ints = (R / 4096 + 2) * (size_t)E;
   size_t o_ps = take(c->perm_scratch_ints * 4);
   PM_CUDA(cudaMalloc(&c->ws_dev, off));
@@ -142,6 +145,7 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
   c->d_row_token = (int32_t*)(b + o_rt);
   c->d_pos = (int32_t*)(b + o_pos);
   c->d_err = c->d_counts + 2 * E + 1;
+  c->d_tc_err = c->d_counts + 2 * E + 2;
   c->d_hbuf = (__nv_bfloat16*)(b + o_h);
   c->d_yexp = (float*)(b + o_y);
   c->d_plan = b + o_desc;
@@ -149,19 +153,16 @@ int ensure_workspace(pm_ctx* c, int T, const pm_layer_weights& w) {
   c->d_pred_hidden = (float*)(b + o_ph);
   c->d_xin = (__nv_bfloat16*)(b + o_x);
   c->d_yout = (__nv_bfloat16*)(b + o_yo);
-  c->d_res_plan = b + o_res;
+  c->d_res_counters = (int32_t*)(b + o_res);
   c->d_xperm = (__nv_bfloat16*)(b + o_xp);
   c->d_tc_plan = b + o_tcp;
-  c->d_tc_err = (int32_t*)(b + o_tce);
   c->d_perm_scratch = (int32_t*)(b + o_ps);
   if (c->h_tc_plan) PM_CUDA(cudaFreeHost(c->h_tc_plan));
   PM_CUDA(cudaHostAlloc((void**)&c->h_tc_plan, c->tc_plan_cap + 64, cudaHostAllocDefault));
-  c->h_tc_err = (int32_t*)(c->h_tc_plan + c->tc_plan_cap);
-  *c->h_tc_err = 0;
   c->ws_inter_routed = Ir;
   c->ws_inter_shared = Is;
   // pinned staging: [counts+offsets | scores | routing ids | routing weights | descriptors]
-  c->h_stage_bytes = align_up((size_t)(2 * E + 2) * 4, 256) + align_up((size_t)c->cfg.num_layer * E * 4, 256) +
+  c->h_stage_bytes = align_up((size_t)(2 * E + 3) * 4, 256) + align_up((size_t)c->cfg.num_layer * E * 4, 256) +
                      2 * align_up(R * 4, 256) + align_up(c->plan_cap, 256) +
                      align_up((size_t)E * 4, 256);
   PM_CUDA(cudaHostAlloc((void**)&c->h_stage, c->h_stage_bytes, cudaHostAllocDefault));
@@ -187,7 +188,7 @@ Stage stage_of(pm_ctx* c) {
   Stage s;
   unsigned char* p = c->h_stage;
   s.counts = (int32_t*)p;
-  p += align_up((size_t)(2 * E + 2) * 4, 256);
+  p += align_up((size_t)(2 * E + 3) * 4, 256);
   s.scores = (float*)p;
   p += align_up((size_t)c->cfg.num_layer * E * 4, 256);
   s.ids = (int32_t*)p;
@@ -338,6 +339,8 @@ int rt_build_slab(pm_ctx* c) {
   int n_lines = 0;
   for (const Pool& p : c->eng->pools()) n_lines += p.full_len;
   if (n_lines <= 0) return fail(PM_ERR_INVALID, "cache_rate gives zero cache lines");
+  const int n_policy_lines = n_lines;
+  n_lines += 1;  // the spare line of temp_move_expert_to_gpu: no pool owns it
   const size_t rec = c->param_offset.back();
   const char* impl = std::getenv("PM_SLAB_IMPL");
   const bool want_vmm = impl == nullptr || std::string(impl) != "cudamalloc";
@@ -377,7 +380,7 @@ int rt_build_slab(pm_ctx* c) {
     c->line_stride = align_up(rec, 256);
     PM_CUDA(cudaMalloc((void**)&c->slab, c->line_stride * n_lines));
   }
-  c->n_lines = n_lines;
+  c->n_lines = n_policy_lines;
   // cache_only: copies run on the caller's compute stream (src/cpp_worker/prefetcher.cpp:420-424)
   if (!c->cfg.cache_only) PM_CUDA(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
   c->line_ready.resize(n_lines);
@@ -513,7 +516,7 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
       }
       return cudaEventCreate(e);
     };
-    sample.fused = c->fused_ffn && !w.quant4 && info.max_rows <= kSplitMaxRows;
+    sample.fused = ffn_launch_is_fused(info, w.quant4);
     PM_CUDA(take_event(&sample.e0));
     if (!sample.fused) PM_CUDA(take_event(&sample.e1));
     PM_CUDA(take_event(&sample.e2));
@@ -527,12 +530,13 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
     PM_CUDA(cudaEventRecord(sample.e0, s));
   }
   PM_CUDA(launch_swiglu_ffn(c->d_plan + *desc_used, info, w.quant4, x, w.hidden, c->d_row_token, c->d_hbuf,
-                            c->ws_inter, c->d_yexp, s, c->profile_ffn ? sample.e1 : nullptr, c->fused_ffn));
+                            c->ws_inter, c->d_yexp, s, (c->profile_ffn && !sample.fused) ? sample.e1 : nullptr,
+                            c->d_tc_err));
   if (c->profile_ffn) {
     PM_CUDA(cudaEventRecord(sample.e2, s));
     c->ffn_samples.push_back(sample);
   }
-  c->kernel_launches += (c->fused_ffn && !w.quant4 && info.max_rows <= kSplitMaxRows) ? 1 : 2;
+  c->kernel_launches += ffn_launch_is_fused(info, w.quant4) ? 1 : 2;
   *desc_used += align_up(info.blob_bytes(), 256);
   if (!seg->lines.empty()) {
     cudaEvent_t ev = next_seg_event(c);
@@ -562,7 +566,11 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
   if (!routed && w.gate_w == nullptr) return fail(PM_ERR_STATE, "this layer has no router weights (routed rows only)");
   const int E = c->cfg.num_expert, k = routed ? 1 : w.top_k, H = w.hidden, N = c->cfg.num_per_expert_param();
   const int R = T * k;
-  const int n_shared = (!routed && w.shared_inter > 0) ? 1 : 0;
+  // Decode batches give every slice of the shared expert its own output rows (the combine adds them);
+  // larger batches keep the shared expert whole.
+  const bool has_shared = !routed && w.shared_inter > 0;
+  const bool sliced = has_shared && T <= kSplitMaxRows && !w.quant4;
+  const int n_shared = !has_shared ? 0 : (sliced ? shared_slice_count(w.inter, w.shared_inter) : 1);
   int rc = ensure_workspace(c, T, w);
   if (rc != PM_OK) return rc;
   if (c->have_last_stream && c->last_stream != s) PM_CUDA(cudaStreamSynchronize(c->last_stream));
@@ -586,8 +594,10 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
                              c->d_topk_w, c->d_topk_slot, c->d_shared_scale, nullptr, s));
     c->kernel_launches += 1;
   }
+  const bool spec = c->device_plan && !w.quant4 && resident_ffn_available(T);  // rows per expert <= T
   PM_CUDA(launch_permute(ids_dev, R, k, E, c->d_counts, c->d_offsets, c->d_row_token, c->d_pos, c->d_err,
-                         n_shared * T, T, s, c->d_perm_scratch, c->perm_scratch_ints));
+                         n_shared * T, T, s, c->d_perm_scratch, c->perm_scratch_ints,
+                         spec ? c->d_res_counters : nullptr, kMaxFusedGroups + 1));
   c->kernel_launches += 1;
   std::vector<int> pred_dsts;
   if (!routed && c->cfg.predict_from_moe_input && c->seq_len == 1) {
@@ -601,7 +611,7 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
   PM_CUDA(cudaStreamWaitEvent(rb, c->routed_event, 0));
   if (!pred_dsts.empty())
     PM_CUDA(cudaMemcpyAsync(st.scores, c->d_scores, (size_t)c->cfg.num_layer * E * 4, cudaMemcpyDeviceToHost, rb));
-  PM_CUDA(cudaMemcpyAsync(st.counts, c->d_counts, (size_t)(2 * E + 2) * 4, cudaMemcpyDeviceToHost, rb));
+  PM_CUDA(cudaMemcpyAsync(st.counts, c->d_counts, (size_t)(2 * E + 3) * 4, cudaMemcpyDeviceToHost, rb));
   const bool keep = c->keep_routing && !routed;
   if (keep) {
     PM_CUDA(cudaMemcpyAsync(st.ids, c->d_topk_ids, (size_t)R * 4, cudaMemcpyDeviceToHost, rb));
@@ -611,7 +621,6 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
 
   // Experts resident right now (the device slot table shows the same state).
   std::vector<int> resident_line(E, -1);
-  const bool spec = c->device_plan && c->fused_ffn && !w.quant4 && resident_ffn_available(T);  // rows per expert <= T
   pm_ctx::FfnSample spec_sample{};
   if (spec) {
     for (int e = 0; e < E; ++e) {
@@ -624,8 +633,11 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
         c->line_waiter[line] = s;
       }
     }
-    ResidentPlanArgs a{};
+    ResidentArgs a{};
     const Pool& pool = c->eng->pools()[c->eng->pool_index(layer)];
+    a.counts = c->d_counts;
+    a.offsets = c->d_offsets;
+    a.slot_table = ly.slot_table_dev;
     a.pool_base = line_ptr(c, pool.base);
     a.line_stride = c->line_stride;
     a.off_gate = c->param_offset[c->role_gate];
@@ -636,13 +648,10 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
     a.shared_w_down = w.shared_w_down;
     a.num_expert = E;
     a.inter = w.inter;
-    a.shared_inter = w.shared_inter;
-    a.hidden = H;
+    a.shared_inter = has_shared ? w.shared_inter : 0;
+    a.shared_slice = has_shared ? shared_slice_width(w.inter, w.shared_inter) : 0;
     a.tokens = T;
     a.n_routed_rows = R;
-    a.off_desc = c->res_off_desc;
-    a.off_tile_gu = c->res_off_gu;
-    a.off_tile_dn = c->res_off_dn;
     if (c->profile_ffn) {
       auto take_event = [&](cudaEvent_t* e) -> cudaError_t {
         if (!c->ffn_event_pool.empty()) {
@@ -656,11 +665,12 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
       spec_sample.resident = true;
       PM_CUDA(take_event(&spec_sample.e0));
       PM_CUDA(take_event(&spec_sample.e2));
+      PM_CUDA(cudaEventRecord(spec_sample.e0, s));
     }
-    PM_CUDA(launch_resident_ffn(c->d_counts, c->d_offsets, ly.slot_table_dev, a, c->d_res_plan, T, x, c->d_row_token,
-                                c->d_hbuf, c->ws_inter, c->d_yexp, s, c->profile_ffn ? spec_sample.e0 : nullptr));
+    PM_CUDA(launch_resident_ffn(a, c->d_res_counters, c->d_tc_err, T, x, H, c->d_row_token, c->d_hbuf, c->ws_inter,
+                                c->d_yexp, s));
     if (c->profile_ffn) PM_CUDA(cudaEventRecord(spec_sample.e2, s));
-    c->kernel_launches += 2;
+    c->kernel_launches += 1;
     cudaEvent_t ev = next_seg_event(c);
     PM_CUDA(cudaEventRecord(ev, s));
     for (int e = 0; e < E; ++e)
@@ -677,16 +687,14 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
     rc = rt_profile_collect(c);
     if (rc != PM_OK) return rc;
   }
-  if (c->tc_err_pending) {
-    c->tc_err_pending = false;
-    if (*c->h_tc_err != 0) {
-      const int code = *c->h_tc_err;
-      *c->h_tc_err = 0;
-      return fail(PM_ERR_TIMEOUT, "the prefill kernel of the previous layer call gave up a bounded wait (code " +
-                                      std::to_string(code) + ")");
-    }
+  if (st.counts[2 * E + 2] != 0) {
+    // written by an FFN kernel of an earlier layer call (everything enqueued before this call's router
+    // has finished by now): a bounded wait gave up
+    const int code = st.counts[2 * E + 2];
+    PM_CUDA(cudaMemsetAsync(c->d_tc_err, 0, 4, s));
+    return fail(PM_ERR_TIMEOUT, "an expert FFN kernel of the previous layer call gave up a bounded wait (code " +
+                                    std::to_string(code) + ")");
   }
-
   if (st.counts[2 * E + 1] != 0) {
     // only the caller's row_expert can be out of range (the router's ids never are); the rows were
     // dropped by the permutation, so nothing may be returned for this call
@@ -751,15 +759,19 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
   Segment seg;
   size_t desc_used = 0;
   if (n_shared && !spec) {
-    pm_ffn_group g{};
-    g.w_gate = w.shared_w_gate;
-    g.w_up = w.shared_w_up;
-    g.w_down = w.shared_w_down;
-    g.row_start = R;
-    g.row_count = T;
-    g.inter = w.shared_inter;
-    seg.groups.push_back(g);
-    seg.group_line.push_back(-1);
+    const int slice = sliced ? shared_slice_width(w.inter, w.shared_inter) : w.shared_inter;
+    for (int j = 0; j < n_shared; ++j) {
+      pm_ffn_group g{};
+      g.w_gate = (const unsigned char*)w.shared_w_gate + (size_t)j * slice * H * 2;
+      g.w_up = (const unsigned char*)w.shared_w_up + (size_t)j * slice * H * 2;
+      g.w_down = (const unsigned char*)w.shared_w_down + (size_t)j * slice * 2;
+      g.row_start = R + j * T;
+      g.row_count = T;
+      g.inter = std::min(slice, w.shared_inter - j * slice);
+      g.ld_down = w.shared_inter;
+      seg.groups.push_back(g);
+      seg.group_line.push_back(-1);
+    }
   }
   for (const Action& a : acts) {
     if (a.type == Action::kCopy) {
@@ -794,10 +806,6 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
                            w.shared_gate_w ? c->d_shared_scale : nullptr, (__nv_bfloat16*)yv, s));
   }
   c->kernel_launches += 1;
-  if (c->xperm_ready) {  // the prefill path ran in this call
-    PM_CUDA(cudaMemcpyAsync(c->h_tc_err, c->d_tc_err, 4, cudaMemcpyDeviceToHost, s));
-    c->tc_err_pending = true;
-  }
   for (int64_t id : ids) c->eng->expert_done(layer, (int)id);
   c->eng->layer_done(layer);
   (void)N;
@@ -818,6 +826,61 @@ int rt_forward_host(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStr
   if (rc != PM_OK) return rc;
   PM_CUDA(cudaMemcpyAsync(y, c->d_yout, bytes, cudaMemcpyDeviceToHost, s));
   PM_CUDA(cudaStreamSynchronize(s));
+  return PM_OK;
+}
+
+// The per-expert path: the caller computes the expert itself on `s` from the line's address.
+int rt_expert_acquire(pm_ctx* c, int layer, int expert, cudaStream_t s, void** line_out) {
+  if (!c->slab_built) return fail(PM_ERR_STATE, "expert_acquire before build_slab");
+  if (layer < 0 || layer >= c->cfg.num_layer || expert < 0 || expert >= c->cfg.num_expert || !line_out)
+    return fail(PM_ERR_INVALID, "layer or expert out of range");
+  *line_out = nullptr;
+  std::vector<Action> acts;
+  std::string err = c->eng->report_expert(layer, expert, &acts);
+  if (!err.empty()) return fail(PM_ERR_STATE, err);
+  rt_mark_dirty(c, acts);
+  int rc = rt_execute_copies(c, acts);
+  if (rc != PM_OK) return rc;
+  const int line = c->eng->expert(layer, expert).line;
+  if (line < 0) return fail(PM_ERR_STATE, "the expert has no cache line after report_one_expert (report_one_layer missing?)");
+  if (c->line_pending[line] || (c->line_waiter[line] != nullptr && c->line_waiter[line] != s)) {
+    PM_CUDA(cudaStreamWaitEvent(s, c->line_ready[line], 0));
+    c->line_pending[line] = 0;
+    c->line_waiter[line] = s;
+  }
+  *line_out = line_ptr(c, line);
+  return PM_OK;
+}
+
+int rt_expert_release(pm_ctx* c, int layer, int expert, cudaStream_t s) {
+  if (!c->slab_built) return fail(PM_ERR_STATE, "expert_release before build_slab");
+  if (layer < 0 || layer >= c->cfg.num_layer || expert < 0 || expert >= c->cfg.num_expert)
+    return fail(PM_ERR_INVALID, "layer or expert out of range");
+  const int line = c->eng->expert(layer, expert).line;
+  if (line >= 0) {  // a later copy into this line waits for the caller's kernels
+    cudaEvent_t ev = next_seg_event(c);
+    PM_CUDA(cudaEventRecord(ev, s));
+    c->line_read[line] = ev;
+  }
+  std::string err = c->eng->expert_done(layer, expert);
+  if (!err.empty()) return fail(PM_ERR_INVALID, err);
+  return PM_OK;
+}
+
+int rt_temp_move(pm_ctx* c, int layer, int expert, bool to_gpu, cudaStream_t s, void** line_out) {
+  if (!c->slab_built) return fail(PM_ERR_STATE, "temp_move_expert before build_slab");
+  if (layer < 0 || layer >= c->cfg.num_layer || expert < 0 || expert >= c->cfg.num_expert)
+    return fail(PM_ERR_INVALID, "layer or expert out of range");
+  unsigned char* spare = line_ptr(c, c->n_lines);
+  unsigned char* rec = c->host_rec[(size_t)layer * c->cfg.num_expert + expert];
+  const size_t bytes = c->param_offset.back();
+  if (to_gpu) {
+    PM_CUDA(cudaMemcpyAsync(spare, rec, bytes, cudaMemcpyHostToDevice, s));
+  } else {
+    PM_CUDA(cudaMemcpyAsync(rec, spare, bytes, cudaMemcpyDeviceToHost, s));
+  }
+  PM_CUDA(cudaStreamSynchronize(s));
+  if (line_out) *line_out = spare;
   return PM_OK;
 }
 

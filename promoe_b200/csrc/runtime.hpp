@@ -39,7 +39,7 @@ struct pm_ctx {
   bool slab_vmm = false;
   unsigned char* slab = nullptr;
   size_t line_stride = 0;
-  int n_lines = 0;
+  int n_lines = 0;  // lines the policy owns; one more (index n_lines) is the spare line of temp_move_expert_*
   std::vector<CUmemGenericAllocationHandle> line_handles;
   size_t slab_va_bytes = 0;
 
@@ -57,8 +57,7 @@ struct pm_ctx {
   cudaStream_t readback_stream = nullptr;  // carries the router's counts to the host beside the FFN
   cudaEvent_t routed_event = nullptr;      // router + permute done on the compute stream
   bool device_plan = true;                 // plan and launch the resident experts without a host round trip
-  unsigned char* d_res_plan = nullptr;     // device blob of that plan
-  size_t res_off_desc = 0, res_off_gu = 0, res_off_dn = 0;
+  int32_t* d_res_counters = nullptr;       // dependency counters of that launch (cleared by the permutation)
 
   // ---- per-layer model weights ----------------------------------------------------------
   struct Layer {
@@ -100,9 +99,8 @@ struct pm_ctx {
   size_t tc_plan_cap = 0, tc_plan_used = 0;
   int32_t* d_perm_scratch = nullptr;  // per-chunk expert counts of the multi-CTA permutation
   size_t perm_scratch_ints = 0;
-  int32_t* d_tc_err = nullptr;        // set by the kernel when a bounded wait gave up
-  int32_t* h_tc_err = nullptr;        // pinned copy, checked at the next layer call
-  bool tc_err_pending = false;
+  int32_t* d_tc_err = nullptr;        // set by an FFN kernel when a bounded wait gave up; sits behind the
+                                      // permutation's counts and reaches the host with them at the next layer call
   bool xperm_ready = false, tc_maps_ready = false;  // per layer call
   pm::TcMaps tc_maps;
   int64_t tc_launches = 0;
@@ -122,7 +120,6 @@ struct pm_ctx {
     bool resident;  // the device-planned launch (shared expert + experts already resident)
   };
   bool profile_ffn = false;
-  bool fused_ffn = true;  // one cooperative launch per segment when the chunks are small enough
   std::vector<FfnSample> ffn_samples;      // recorded, not yet read
   std::vector<cudaEvent_t> ffn_event_pool; // free events
   double ffn_ms_gu = 0, ffn_ms_dn = 0, ffn_ms_fused = 0;
@@ -148,6 +145,9 @@ struct RoutedRows {
 int rt_forward(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStream_t s, const RoutedRows* routed = nullptr);
 int rt_forward_host(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStream_t s);
 int rt_report_hidden(pm_ctx* c, int index, const void* hidden, int B, int seq, cudaStream_t s);
+int rt_expert_acquire(pm_ctx* c, int layer, int expert, cudaStream_t s, void** line);
+int rt_expert_release(pm_ctx* c, int layer, int expert, cudaStream_t s);
+int rt_temp_move(pm_ctx* c, int layer, int expert, bool to_gpu, cudaStream_t s, void** line);
 void rt_mark_dirty(pm_ctx* c, const std::vector<Action>& actions);
 int rt_profile_collect(pm_ctx* c);
 bool tc_prefill_usable(const pm_ctx* c, const pm_layer_weights& w);

@@ -1,11 +1,13 @@
 // K3a: grouped SwiGLU expert FFN for decode-size batches, weights read by cache-slot
-// indirection. Two launches per layer:
+// indirection:
 //   gate/up : h[r, i] = silu(x_r . Wg[i, :]) * (x_r . Wu[i, :])
 //   down    : y[r, n] = h_r . Wd[n, :]
-// Every CTA tile streams 64 weight rows (4 warps x 16 rows) exactly once from HBM
-// and applies them to all token rows of its chunk (up to 64) with warp-level
-// bf16 MMAs, fp32 accumulation. The kernel is HBM-bound: the weight bytes of each
-// activated expert are the algorithmic traffic.
+// Three kernels share the arithmetic: the fused decode kernel (chunks of at most 16 token rows,
+// one cooperative launch for both passes), the uint4 decode kernel (two launches) and the staged
+// kernel for chunks of up to 64 rows (two launches; every CTA tile streams 64 weight rows, 4 warps
+// x 16 rows, and applies them to all token rows of its chunk). Every weight byte of an activated
+// expert is read exactly once with warp-level bf16 MMAs and fp32 accumulation: the kernels are
+// HBM-bound and the weight bytes are the algorithmic traffic.
 //
 // It replaces the per-expert Python loop over torch linears that the reference
 // drives through ExpertHook (src/sparse_llm_cache/utils/hooks.py:187-198) after
@@ -17,8 +19,6 @@
 // lane loads 16 contiguous bytes (8 bf16) of a weight row and of a token row at
 // the same k offset and feeds pairs {0,1} and {2,3} to one m16n8k16 MMA and pairs
 // {4,5}, {6,7} to a second one. Both operands therefore use full 128-bit loads.
-#include <cooperative_groups.h>
-
 #include <cstdlib>
 
 #include "pm_common.cuh"
@@ -173,19 +173,14 @@ grouped_ffn_kernel(const GroupDesc* __restrict__ groups, const int32_t* __restri
 
 
 // ---------------------------------------------------------------------------------------------
-// Decode variant for chunks of at most 16 token rows (the common case: a handful of tokens per
-// expert). A CTA owns one m-tile (16 gate rows + the same 16 up rows, or 32 down rows) and its
-// 8 warps split the reduction dimension, so every warp issues its whole share of weight loads
-// in one or two batches and a tile lives for a couple of DRAM round trips. Token rows are
-// read straight from global memory (they are tiny and stay in L1/L2) into MMA B fragments,
-// so there is no shared-memory staging and no barrier before the final cross-warp reduction.
+// Decode tiles (chunks of at most 16 token rows): a CTA owns one m-tile and its 8 warps split the
+// reduction dimension. Shared by the uint4 kernel and the fused bf16 kernel below.
 // ---------------------------------------------------------------------------------------------
 constexpr int kSplitWarps = 8;
 constexpr int kSplitThreads = kSplitWarps * 32;
 
-// Token-row fragment load. Rows written earlier in the same kernel (the fused variant reads the
-// intermediate rows other CTAs produced before the grid barrier) must not go through the
-// non-coherent path.
+// Token-row fragment load. Rows written earlier in the same kernel (the fused kernel's down tiles
+// read the intermediate rows other CTAs produced) must not go through the non-coherent path.
 template <bool COHERENT>
 __device__ __forceinline__ uint4 load_b(const unsigned char* p) {
   uint4 r;
@@ -195,122 +190,6 @@ __device__ __forceinline__ uint4 load_b(const unsigned char* p) {
     r = __ldg(reinterpret_cast<const uint4*>(p));
   }
   return r;
-}
-
-// One split-K tile: 16 gate + 16 up rows (GATEUP) or 32 down rows of one chunk, all 8 warps of
-// the CTA. `red` is the CTA's reduction buffer; the caller separates consecutive tiles by a barrier.
-template <int NT, bool GATEUP, int DEPTH, bool COHERENT_B>
-__device__ __forceinline__ void splitk_tile(const GroupDesc& grp, int tile_local,
-                                            const __nv_bfloat16* __restrict__ bsrc, int ldb,
-                                            const int32_t* __restrict__ row_token, int hidden,
-                                            __nv_bfloat16* __restrict__ hbuf, int ld_h,
-                                            float* __restrict__ yexp, float (*red)[2 * NT * 4][32]) {
-  const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
-  const int g = lane >> 2;
-  const int q = lane & 3;
-  const int K = GATEUP ? hidden : grp.inter;
-  const int rows = grp.row_count;
-  const int m0 = tile_local * (GATEUP ? 16 : 32);
-  const size_t row_bytes = (size_t)K * 2;
-
-  // Four weight-row streams per lane: gate rows g / g+8 and up rows g / g+8, or down rows
-  // g, g+8, g+16, g+24 of the tile.
-  const unsigned char* a_ptr[4];
-  if (GATEUP) {
-    const unsigned char* w0 = reinterpret_cast<const unsigned char*>(grp.w_gate);
-    const unsigned char* w1 = reinterpret_cast<const unsigned char*>(grp.w_up);
-    a_ptr[0] = w0 + (size_t)(m0 + g) * row_bytes + q * 16;
-    a_ptr[1] = w0 + (size_t)(m0 + g + 8) * row_bytes + q * 16;
-    a_ptr[2] = w1 + (size_t)(m0 + g) * row_bytes + q * 16;
-    a_ptr[3] = w1 + (size_t)(m0 + g + 8) * row_bytes + q * 16;
-  } else {
-    const unsigned char* w0 = reinterpret_cast<const unsigned char*>(grp.w_down);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) a_ptr[j] = w0 + (size_t)(m0 + g + 8 * j) * row_bytes + q * 16;
-  }
-  const unsigned char* b_ptr[NT];
-  bool b_ok[NT];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    const int n = nt * 8 + g;
-    b_ok[nt] = n < rows;
-    const int src_row = b_ok[nt] ? (GATEUP ? row_token[grp.row_start + n] : grp.row_start + n) : 0;
-    b_ptr[nt] = reinterpret_cast<const unsigned char*>(bsrc + (size_t)src_row * ldb) + q * 16;
-  }
-
-  float acc[2][NT][4];
-#pragma unroll
-  for (int m = 0; m < 2; ++m)
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[m][nt][i] = 0.f;
-
-  const int steps = K / 32;
-  const int s_begin = (warp * steps) / kSplitWarps;
-  const int s_end = ((warp + 1) * steps) / kSplitWarps;
-  for (int s0 = s_begin; s0 < s_end; s0 += DEPTH) {
-    uint4 a[DEPTH][4];
-    uint4 b[DEPTH][NT];
-#pragma unroll
-    for (int d = 0; d < DEPTH; ++d) {
-      if (s0 + d < s_end) {
-        const size_t off = (size_t)(s0 + d) * 64;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) a[d][j] = ldg_stream(a_ptr[j] + off);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-          b[d][nt] = b_ok[nt] ? load_b<COHERENT_B>(b_ptr[nt] + off) : make_uint4(0, 0, 0, 0);
-      }
-    }
-#pragma unroll
-    for (int d = 0; d < DEPTH; ++d) {
-      if (s0 + d < s_end) {
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-          for (int m = 0; m < 2; ++m) {
-            const uint4& lo = a[d][2 * m];
-            const uint4& hi = a[d][2 * m + 1];
-            mma_bf16(acc[m][nt], lo.x, hi.x, lo.y, hi.y, b[d][nt].x, b[d][nt].y);
-            mma_bf16(acc[m][nt], lo.z, hi.z, lo.w, hi.w, b[d][nt].z, b[d][nt].w);
-          }
-        }
-      }
-    }
-  }
-
-  // Cross-warp reduction of the split-K partial sums, then the epilogue.
-#pragma unroll
-  for (int m = 0; m < 2; ++m)
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) red[warp][(m * NT + nt) * 4 + i][lane] = acc[m][nt][i];
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < NT * 4 * 32; idx += kSplitThreads) {
-    const int l = idx & 31;
-    const int v = idx >> 5;  // nt * 4 + i
-    const int nt = v >> 2, i = v & 3;
-    float s0v = 0.f, s1v = 0.f;
-#pragma unroll
-    for (int w = 0; w < kSplitWarps; ++w) {
-      s0v += red[w][v][l];
-      s1v += red[w][NT * 4 + v][l];
-    }
-    const int lg = l >> 2, lq = l & 3;
-    const int n = nt * 8 + 2 * lq + (i & 1);
-    if (n >= rows) continue;
-    const int m = m0 + lg + ((i & 2) ? 8 : 0);
-    const size_t r = (size_t)(grp.row_start + n);
-    if (GATEUP) {
-      hbuf[r * ld_h + m] = __float2bfloat16_rn(silu(s0v) * s1v);
-    } else {
-      yexp[r * hidden + m] = s0v;
-      yexp[r * hidden + m + 16] = s1v;
-    }
-  }
 }
 
 
@@ -484,123 +363,117 @@ cudaError_t launch_q4(const GroupDesc* groups, const int32_t* tile_group, int ti
   return cudaGetLastError();
 }
 
-template <int NT, int NMAT, int DEPTH>
-__global__ void __launch_bounds__(kSplitThreads, 2)
-grouped_ffn_splitk_kernel(const GroupDesc* __restrict__ groups, const int32_t* __restrict__ tile_group,
-                          const __nv_bfloat16* __restrict__ bsrc, int ldb,
-                          const int32_t* __restrict__ row_token, int hidden,
-                          __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp) {
-  constexpr bool GATEUP = (NMAT == 2);
-  __shared__ float red[kSplitWarps][2 * NT * 4][32];
-  const GroupDesc grp = groups[tile_group[blockIdx.x]];
-  const int tile_local = blockIdx.x - (GATEUP ? grp.tile_start_gu : grp.tile_start_dn);
-  splitk_tile<NT, GATEUP, DEPTH, false>(grp, tile_local, bsrc, ldb, row_token, hidden, hbuf, ld_h, yexp, red);
-}
+// ---------------------------------------------------------------------------------------------
+// Fused decode kernel: ONE cooperative launch per segment, chunks of at most 16 token rows (the
+// common case: a handful of tokens per expert). A tile is 16 gate rows + the same 16 up rows, or
+// 32 down rows, of one chunk; the 8 warps of a CTA split the reduction dimension, so every warp
+// issues its share of weight loads in one or two batches. Token rows come straight from global
+// memory (they are tiny and stay in L1/L2) into MMA B fragments.
+//
+// All tiles of the launch form one sequence, gate/up tiles first, then down tiles, dealt round
+// robin to a fixed grid of resident CTAs. There is no grid barrier: a gate/up tile bumps its
+// chunk's counter when its intermediate rows are stored, and a down tile waits (bounded) until
+// its chunk's counter shows every gate/up tile of the chunk. Because every CTA runs all its
+// gate/up tiles before its first down tile and the grid is co-resident (cooperative launch), the
+// wait cannot deadlock; it is bounded anyway and reports a give-up through `err`.
+//
+// Every CTA first builds the launch's chunk table in shared memory, either from descriptors the
+// host uploaded or, for the device-planned launch, from the router's per-expert row counts and
+// the layer's expert -> slot table. The shared expert enters as slices of its intermediate
+// dimension (a chunk per slice: rows of W_gate / W_up, columns of W_down), so its tiles weigh the
+// same as a routed expert's and the round-robin deal stays balanced.
+// ---------------------------------------------------------------------------------------------
+struct FusedGroup {  // shared-memory record of one chunk
+  const unsigned char* w_gate;
+  const unsigned char* w_up;
+  const unsigned char* w_down;
+  int32_t row_start, rows, inter, ld_down;
+  int32_t tile_gu, tile_dn;  // first gate/up tile, first down tile
+};
 
-// ---------------------------------------------------------------------------------------------
-// Fused decode variant: ONE cooperative launch per segment. A fixed grid of resident CTAs strides
-// over the gate/up tiles, meets at a grid barrier (the intermediate rows must be complete before
-// any down tile reads them), then strides over the down tiles. Compared with two launches this
-// removes one launch gap and one tail per segment.
-// ---------------------------------------------------------------------------------------------
-// The same split-K tile cut into stages, so that a resident CTA can have the first loads of its
-// NEXT tile in flight while it reduces and stores the current one.
+struct FusedLaunch {
+  const GroupDesc* groups;  // host-planned launch: n_groups descriptors; nullptr = device-planned
+  int32_t n_groups, tiles_gu, tiles_dn;
+  ResidentArgs res;         // device-planned launch
+  int32_t* counters;        // one per chunk, zero at launch
+  int32_t* total;           // arrivals of the whole launch, zero at launch
+  int32_t* err;             // may be nullptr
+  const __nv_bfloat16* x;
+  const int32_t* row_token;
+  __nv_bfloat16* hbuf;
+  float* yexp;
+  int32_t hidden, ld_h;
+};
+
+// The split-K tile cut into stages, so that a resident CTA can have the first loads of its NEXT
+// tile in flight while it reduces and stores the current one. Only what the load stream needs
+// lives in registers; everything else is re-read from the shared-memory chunk table.
 template <int NT>
 struct TileCtx {
   const unsigned char* a_ptr[4];
   const unsigned char* b_ptr[NT];
-  bool b_ok[NT];
-  int rows, m0, row_start, s_begin, s_end;  // s_* count this warp's k-steps: 0 .. s_end
-  int step_bytes;                            // distance between two of them
+  int s_end;  // this warp's k-steps; a row without a token has b_ptr == nullptr
+  int gi;     // chunk index
+  int m0;     // first weight row of the tile
 };
 
-// What a tile needs from its chunk descriptor and the row table. It is fetched one tile ahead, so
-// that the two dependent loads (descriptor, then token row numbers) never stall the load stream.
-template <int NT>
-struct TileMeta {
-  const unsigned char* w0;
-  const unsigned char* w1;
-  int row_start, rows, inter, tile_start;
-  int src_row[NT];
-};
-
-template <int NT, bool GATEUP>
-__device__ __forceinline__ void meta_load_desc(TileMeta<NT>& m, const GroupDesc* __restrict__ groups, int gi) {
-  const GroupDesc* d = groups + gi;
-  m.w0 = reinterpret_cast<const unsigned char*>(GATEUP ? d->w_gate : d->w_down);
-  m.w1 = reinterpret_cast<const unsigned char*>(GATEUP ? d->w_up : d->w_down);
-  m.row_start = d->row_start;
-  m.rows = d->row_count;
-  m.inter = d->inter;
-  m.tile_start = GATEUP ? d->tile_start_gu : d->tile_start_dn;
+// First chunk at or after `from` whose tile range holds `tile` (tiles only move forward).
+template <bool GATEUP>
+__device__ __forceinline__ int find_group(const FusedGroup* sg, int n, int from, int tile) {
+  int gi = from;
+  while (gi + 1 < n && (GATEUP ? sg[gi + 1].tile_gu : sg[gi + 1].tile_dn) <= tile) ++gi;
+  return gi;
 }
 
+// Source rows of the tile's token fragments (this lane's n-tile rows): the one global round trip
+// a tile needs before its token loads, fetched one tile ahead.
 template <int NT, bool GATEUP>
-__device__ __forceinline__ void meta_load_rows(TileMeta<NT>& m, const int32_t* __restrict__ row_token) {
+__device__ __forceinline__ void load_src_rows(int (&src_row)[NT], const FusedGroup& d,
+                                              const int32_t* __restrict__ row_token) {
   const int g = (threadIdx.x & 31) >> 2;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int n = nt * 8 + g;
-    m.src_row[nt] = (n < m.rows) ? (GATEUP ? row_token[m.row_start + n] : m.row_start + n) : -1;
+    src_row[nt] = (n < d.rows) ? (GATEUP ? row_token[d.row_start + n] : d.row_start + n) : -1;
   }
 }
 
 template <int NT, bool GATEUP, int WARPS>
-__device__ __forceinline__ void tile_setup(TileCtx<NT>& t, const TileMeta<NT>& m, int tile,
-                                           const __nv_bfloat16* bsrc, int ldb, int hidden) {
+__device__ __forceinline__ void tile_setup(TileCtx<NT>& t, const FusedGroup& d, int gi, int tile,
+                                           const int (&src_row)[NT], const __nv_bfloat16* bsrc, int ldb, int hidden) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, q = lane & 3;
-  const int tile_local = tile - m.tile_start;
-  const int K = GATEUP ? hidden : m.inter;
-  const size_t row_bytes = (size_t)K * 2;
-  t.rows = m.rows;
-  t.row_start = m.row_start;
+  const int tile_local = tile - (GATEUP ? d.tile_gu : d.tile_dn);
+  const int K = GATEUP ? hidden : d.inter;
+  const size_t row_bytes = (size_t)(GATEUP ? hidden : d.ld_down) * 2;
+  t.gi = gi;
   t.m0 = tile_local * (GATEUP ? 16 : 32);
   // Every warp takes a contiguous range of k-steps (interleaving them across warps, w, w+8, ...,
   // measured 6 % slower: longer contiguous runs per warp suit DRAM better).
   const int steps = K / 32;
   const int first = (warp * steps) / WARPS;
   t.s_end = ((warp + 1) * steps) / WARPS - first;
-  t.s_begin = 0;
-  t.step_bytes = 64;
   const size_t col = (size_t)first * 64 + q * 16;
   if (GATEUP) {
-    t.a_ptr[0] = m.w0 + (size_t)(t.m0 + g) * row_bytes + col;
-    t.a_ptr[1] = m.w0 + (size_t)(t.m0 + g + 8) * row_bytes + col;
-    t.a_ptr[2] = m.w1 + (size_t)(t.m0 + g) * row_bytes + col;
-    t.a_ptr[3] = m.w1 + (size_t)(t.m0 + g + 8) * row_bytes + col;
+    t.a_ptr[0] = d.w_gate + (size_t)(t.m0 + g) * row_bytes + col;
+    t.a_ptr[1] = d.w_gate + (size_t)(t.m0 + g + 8) * row_bytes + col;
+    t.a_ptr[2] = d.w_up + (size_t)(t.m0 + g) * row_bytes + col;
+    t.a_ptr[3] = d.w_up + (size_t)(t.m0 + g + 8) * row_bytes + col;
   } else {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) t.a_ptr[j] = m.w0 + (size_t)(t.m0 + g + 8 * j) * row_bytes + col;
+    for (int j = 0; j < 4; ++j) t.a_ptr[j] = d.w_down + (size_t)(t.m0 + g + 8 * j) * row_bytes + col;
   }
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    t.b_ok[nt] = m.src_row[nt] >= 0;
-    t.b_ptr[nt] = reinterpret_cast<const unsigned char*>(bsrc + (size_t)max(m.src_row[nt], 0) * ldb) + col;
-  }
+  for (int nt = 0; nt < NT; ++nt)
+    t.b_ptr[nt] = src_row[nt] >= 0 ? reinterpret_cast<const unsigned char*>(bsrc + (size_t)src_row[nt] * ldb) + col
+                                   : nullptr;
 }
 
-template <int NT, int DEPTH, bool COHERENT_B>
-__device__ __forceinline__ void tile_issue(const TileCtx<NT>& t, int s0, uint4 (&a)[DEPTH][4], uint4 (&b)[DEPTH][NT]) {
-#pragma unroll
-  for (int d = 0; d < DEPTH; ++d) {
-    if (s0 + d < t.s_end) {
-      const size_t off = (size_t)(s0 + d) * t.step_bytes;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) a[d][j] = ldg_stream(t.a_ptr[j] + off);
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-        b[d][nt] = t.b_ok[nt] ? load_b<COHERENT_B>(t.b_ptr[nt] + off) : make_uint4(0, 0, 0, 0);
-    }
-  }
-}
-
-// First batch of a tile in two halves: the weight loads can go out before the token rows exist.
 template <int NT, int DEPTH>
 __device__ __forceinline__ void tile_issue_a(const TileCtx<NT>& t, int s0, uint4 (&a)[DEPTH][4]) {
 #pragma unroll
   for (int d = 0; d < DEPTH; ++d) {
     if (s0 + d < t.s_end) {
-      const size_t off = (size_t)(s0 + d) * t.step_bytes;
+      const size_t off = (size_t)(s0 + d) * 64;
 #pragma unroll
       for (int j = 0; j < 4; ++j) a[d][j] = ldg_stream(t.a_ptr[j] + off);
     }
@@ -612,10 +485,10 @@ __device__ __forceinline__ void tile_issue_b(const TileCtx<NT>& t, int s0, uint4
 #pragma unroll
   for (int d = 0; d < DEPTH; ++d) {
     if (s0 + d < t.s_end) {
-      const size_t off = (size_t)(s0 + d) * t.step_bytes;
+      const size_t off = (size_t)(s0 + d) * 64;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
-        b[d][nt] = t.b_ok[nt] ? load_b<COHERENT_B>(t.b_ptr[nt] + off) : make_uint4(0, 0, 0, 0);
+        b[d][nt] = t.b_ptr[nt] != nullptr ? load_b<COHERENT_B>(t.b_ptr[nt] + off) : make_uint4(0, 0, 0, 0);
     }
   }
 }
@@ -640,10 +513,56 @@ __device__ __forceinline__ void tile_compute(const TileCtx<NT>& t, int s0, const
   }
 }
 
+__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+
+__device__ __forceinline__ int load_relaxed(const int32_t* p) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Dependency of a down tile on its chunk's gate/up tiles. counters[gi] counts the arrivals of
+// chunk gi, *total all arrivals of the launch. Once the launch total shows every
+// gate/up tile, `all_done` latches and later tiles skip the check. The poll is a relaxed load; the
+// fence that follows a successful poll orders this thread's token-row loads behind it (it runs
+// when the thread has no load in flight, so it is cheap). Bounded: after about a quarter of a
+// second without progress the wait gives up, records code 4 in *err and lets the tile run on.
+__device__ __forceinline__ void wait_rows_ready(const int32_t* counters, const int32_t* total, int gi, int target,
+                                                int total_target, bool& all_done, int32_t* err) {
+  if (all_done) return;
+  if (load_relaxed(total) >= total_target) {
+    all_done = true;
+  } else {
+    bool ok = false;
+    for (int i = 0; i < (1 << 21); ++i) {
+      if (load_relaxed(counters + gi) >= target) {
+        ok = true;
+        break;
+      }
+      __nanosleep(100);
+    }
+    if (!ok && err != nullptr) atomicExch(err, 4);
+  }
+  fence_acq_rel_gpu();
+}
+
+// Arrival of one gate/up tile of chunk `gi`: called by ONE thread after a CTA barrier that follows
+// the tile's stores (the barrier orders them before this thread's fence, the fence publishes them).
+__device__ __forceinline__ void arrive_rows(int32_t* counters, int32_t* total, int gi) {
+  fence_acq_rel_gpu();
+  atomicAdd(counters + gi, 1);
+  atomicAdd(total, 1);
+}
+
+// Cross-warp reduction of the split-K partial sums and the epilogue. The barrier in here also lies
+// behind the stores of the PREVIOUS tile, so one thread signals that tile's arrival (chunk
+// `pending`, -1 = none) right after it: it is the last thread of the CTA, whose warp has nothing
+// else to do until its next loads land.
 template <int NT, bool GATEUP, int WARPS>
-__device__ __forceinline__ void tile_finish(int rows, int m0, int row_start, float (&acc)[2][NT][4],
+__device__ __forceinline__ void tile_finish(const FusedGroup& d, int m0, float (&acc)[2][NT][4],
                                             float (*red)[2 * NT * 4][32], __nv_bfloat16* __restrict__ hbuf, int ld_h,
-                                            float* __restrict__ yexp, int hidden) {
+                                            float* __restrict__ yexp, int hidden, int32_t* counters, int32_t* total,
+                                            int pending) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
   for (int m = 0; m < 2; ++m)
@@ -655,73 +574,73 @@ __device__ __forceinline__ void tile_finish(int rows, int m0, int row_start, flo
         acc[m][nt][i] = 0.f;
       }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < NT * 4 * 32; idx += WARPS * 32) {
-    const int l = idx & 31, v = idx >> 5;
+  static_assert(NT * 4 <= WARPS, "one pass of the epilogue, NT * 4 storing warps");
+  if (GATEUP && pending >= 0 && threadIdx.x == WARPS * 32 - 1) arrive_rows(counters, total, pending);
+  if (warp < NT * 4) {
+    const int v = warp;  // nt * 4 + i
     const int nt = v >> 2, i = v & 3;
     float s0v = 0.f, s1v = 0.f;
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) {
-      s0v += red[w][v][l];
-      s1v += red[w][NT * 4 + v][l];
+      s0v += red[w][v][lane];
+      s1v += red[w][NT * 4 + v][lane];
     }
-    const int lg = l >> 2, lq = l & 3;
+    const int lg = lane >> 2, lq = lane & 3;
     const int n = nt * 8 + 2 * lq + (i & 1);
-    if (n >= rows) continue;
-    const int m = m0 + lg + ((i & 2) ? 8 : 0);
-    const size_t r = (size_t)(row_start + n);
-    if (GATEUP) {
-      hbuf[r * ld_h + m] = __float2bfloat16_rn(silu(s0v) * s1v);
-    } else {
-      yexp[r * hidden + m] = s0v;
-      yexp[r * hidden + m + 16] = s1v;
+    if (n < d.rows) {
+      const int m = m0 + lg + ((i & 2) ? 8 : 0);
+      const size_t r = (size_t)(d.row_start + n);
+      if (GATEUP) {
+        hbuf[r * ld_h + m] = __float2bfloat16_rn(silu(s0v) * s1v);
+      } else {
+        yexp[r * hidden + m] = s0v;
+        yexp[r * hidden + m + 16] = s1v;
+      }
     }
   }
   // no trailing barrier: the caller alternates between two reduction buffers, and the barrier above of
   // the NEXT tile orders this tile's reads before the writes of the tile after it
 }
 
-// Tiles blockIdx.x, blockIdx.x + gridDim.x, ... of one phase. The assignment is static, so the
-// next tile is known early: its descriptor is fetched one tile ahead and its first batch of loads
-// is issued before the current tile is reduced, which keeps DRAM requests in flight across tile
-// boundaries. The phase is cut in two calls so that the fused kernel can start the down phase's
-// first weight loads (which do not depend on the intermediate rows) BEFORE the grid barrier.
 template <int NT, int DEPTH>
 struct StreamState {
   TileCtx<NT> t;
-  TileMeta<NT> m;
   uint4 a[DEPTH][4];
   uint4 b[DEPTH][NT];
-  int tile;
-  bool active;
+  int tile, buf;
+  bool active, all_done;
 };
 
-// Sets the CTA's first tile up and issues its weight loads. Reads only the plan and the weights.
+// Sets the CTA's first tile of a phase up and issues its weight loads. Reads only the chunk table,
+// the row table and the weights: for the down phase nothing here depends on the gate/up tiles.
 template <int NT, bool GATEUP, int DEPTH, int WARPS>
-__device__ __forceinline__ void stream_begin(StreamState<NT, DEPTH>& st, const GroupDesc* __restrict__ groups,
-                                             const int32_t* __restrict__ tile_group, int n_tiles,
-                                             const __nv_bfloat16* bsrc, int ldb,
+__device__ __forceinline__ void stream_begin(StreamState<NT, DEPTH>& st, const FusedGroup* sg, int n_groups,
+                                             int first_tile, int n_tiles, const __nv_bfloat16* bsrc, int ldb,
                                              const int32_t* __restrict__ row_token, int hidden) {
-  st.tile = blockIdx.x;
-  st.active = st.tile < n_tiles;
+  st.tile = first_tile;
+  st.active = first_tile < n_tiles;
   if (!st.active) return;
-  meta_load_desc<NT, GATEUP>(st.m, groups, tile_group[st.tile]);  // only the first tile pays for these round trips
-  meta_load_rows<NT, GATEUP>(st.m, row_token);
-  tile_setup<NT, GATEUP, WARPS>(st.t, st.m, st.tile, bsrc, ldb, hidden);
-  tile_issue_a<NT, DEPTH>(st.t, st.t.s_begin, st.a);
+  const int gi = find_group<GATEUP>(sg, n_groups, 0, first_tile);
+  int src_row[NT];
+  load_src_rows<NT, GATEUP>(src_row, sg[gi], row_token);
+  tile_setup<NT, GATEUP, WARPS>(st.t, sg[gi], gi, first_tile, src_row, bsrc, ldb, hidden);
+  tile_issue_a<NT, DEPTH>(st.t, 0, st.a);
 }
 
+// Tiles st.tile, st.tile + gridDim.x, ... of one phase. The next tile is known early: its token row
+// numbers are fetched one tile ahead and its first batch of loads is issued before the current
+// tile is reduced, which keeps DRAM requests in flight across tile boundaries. A gate/up tile's
+// arrival is signalled one tile late, behind the next tile's reduction barrier (see tile_finish).
 template <int NT, bool GATEUP, int DEPTH, int WARPS>
-__device__ __forceinline__ void stream_run(StreamState<NT, DEPTH>& st, const GroupDesc* __restrict__ groups,
-                                           const int32_t* __restrict__ tile_group, int n_tiles,
+__device__ __forceinline__ void stream_run(StreamState<NT, DEPTH>& st, const FusedGroup* sg, int n_groups, int n_tiles,
                                            const __nv_bfloat16* bsrc, int ldb,
                                            const int32_t* __restrict__ row_token, int hidden,
                                            __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp,
-                                           float (*red2)[WARPS][2 * NT * 4][32]) {
+                                           float (*red2)[WARPS][2 * NT * 4][32], int32_t* counters, int32_t* total,
+                                           int total_target, int32_t* err) {
   constexpr bool COH = !GATEUP;  // the down phase reads rows other CTAs wrote in this kernel
   if (!st.active) return;
   TileCtx<NT>& t = st.t;
-  TileMeta<NT>& m = st.m;
-  int buf = 0;
   float acc[2][NT][4];
 #pragma unroll
   for (int mm = 0; mm < 2; ++mm)
@@ -729,68 +648,165 @@ __device__ __forceinline__ void stream_run(StreamState<NT, DEPTH>& st, const Gro
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[mm][nt][i] = 0.f;
-  tile_issue_b<NT, DEPTH, COH>(t, t.s_begin, st.b);
+  // arrivals a chunk's counter shows when its intermediate rows are complete
+  auto target_of = [&](int gi) { return sg[gi].inter / kSplitTileGu; };
+  if (!GATEUP) wait_rows_ready(counters, total, t.gi, target_of(t.gi), total_target, st.all_done, err);
+  tile_issue_b<NT, DEPTH, COH>(t, 0, st.b);
   const int stride = gridDim.x;
-  int tile = st.tile;
-  int next = tile + stride;
-  int gi_next = (next < n_tiles) ? tile_group[next] : 0;
+  int next = st.tile + stride;
+  int pending = -1;  // chunk of the gate/up tile whose arrival is still to be signalled
   while (true) {
     const bool has_next = next < n_tiles;
-    if (has_next) meta_load_desc<NT, GATEUP>(m, groups, gi_next);  // arrives while this tile streams
-    const int next2 = next + stride;
-    const int gi_next2 = (next2 < n_tiles) ? tile_group[next2] : 0;
+    const int gi_next = has_next ? find_group<GATEUP>(sg, n_groups, t.gi, next) : 0;
+    int src_row[NT];
     bool rows_loaded = false;
-    for (int s0 = t.s_begin; s0 < t.s_end;) {
+    for (int s0 = 0; s0 < t.s_end;) {
       tile_compute<NT, DEPTH>(t, s0, st.a, st.b, acc);
-      if (has_next && !rows_loaded) {  // the descriptor is here by now: fetch the token row numbers
-        meta_load_rows<NT, GATEUP>(m, row_token);
+      if (has_next && !rows_loaded) {  // fetch the next tile's token row numbers under this tile's loads
+        load_src_rows<NT, GATEUP>(src_row, sg[gi_next], row_token);
         rows_loaded = true;
       }
       s0 += DEPTH;
-      if (s0 < t.s_end) tile_issue<NT, DEPTH, COH>(t, s0, st.a, st.b);
+      if (s0 < t.s_end) {
+        tile_issue_a<NT, DEPTH>(t, s0, st.a);
+        tile_issue_b<NT, DEPTH, COH>(t, s0, st.b);
+      }
     }
-    if (has_next && !rows_loaded) meta_load_rows<NT, GATEUP>(m, row_token);
-    const int rows = t.rows, m0 = t.m0, row_start = t.row_start;
+    if (has_next && !rows_loaded) load_src_rows<NT, GATEUP>(src_row, sg[gi_next], row_token);
+    const int gi = t.gi, m0 = t.m0;
     if (has_next) {
-      tile_setup<NT, GATEUP, WARPS>(t, m, next, bsrc, ldb, hidden);
-      tile_issue<NT, DEPTH, COH>(t, t.s_begin, st.a, st.b);
+      if (!GATEUP) wait_rows_ready(counters, total, gi_next, target_of(gi_next), total_target, st.all_done, err);
+      tile_setup<NT, GATEUP, WARPS>(t, sg[gi_next], gi_next, next, src_row, bsrc, ldb, hidden);
+      tile_issue_a<NT, DEPTH>(t, 0, st.a);
+      tile_issue_b<NT, DEPTH, COH>(t, 0, st.b);
     }
-    tile_finish<NT, GATEUP, WARPS>(rows, m0, row_start, acc, red2[buf], hbuf, ld_h, yexp, hidden);
-    buf ^= 1;
+    tile_finish<NT, GATEUP, WARPS>(sg[gi], m0, acc, red2[st.buf], hbuf, ld_h, yexp, hidden, counters, total, pending);
+    pending = gi;
+    st.buf ^= 1;
     if (!has_next) break;
-    tile = next;
-    next = next2;
-    gi_next = gi_next2;
+    next += stride;
+  }
+  if (GATEUP) {  // the last tile's arrival: once per CTA
+    __syncthreads();
+    if (threadIdx.x == WARPS * 32 - 1) arrive_rows(counters, total, pending);
+  }
+}
+
+// Chunk table of the launch in shared memory; meta = {chunks, gate/up tiles, down tiles}.
+__device__ __forceinline__ void build_chunk_table(const FusedLaunch& a, FusedGroup* sg, int* meta) {
+  if (a.groups != nullptr) {
+    for (int i = threadIdx.x; i < a.n_groups; i += blockDim.x) {
+      const GroupDesc& d = a.groups[i];
+      FusedGroup g;
+      g.w_gate = reinterpret_cast<const unsigned char*>(d.w_gate);
+      g.w_up = reinterpret_cast<const unsigned char*>(d.w_up);
+      g.w_down = reinterpret_cast<const unsigned char*>(d.w_down);
+      g.row_start = d.row_start;
+      g.rows = d.row_count;
+      g.inter = d.inter;
+      g.ld_down = d.ld_down > 0 ? d.ld_down : d.inter;
+      g.tile_gu = d.tile_start_gu;
+      g.tile_dn = d.tile_start_dn;
+      sg[i] = g;
+    }
+    if (threadIdx.x == 0) {
+      meta[0] = a.n_groups;
+      meta[1] = a.tiles_gu;
+      meta[2] = a.tiles_dn;
+    }
+    return;
+  }
+  const ResidentArgs& r = a.res;
+  const int dn_tiles = a.hidden / kSplitTileDn;
+  const int slice = r.shared_slice;
+  const int n_sh = r.shared_inter > 0 ? (r.shared_inter + slice - 1) / slice : 0;
+  const int sh_tiles = r.shared_inter / kSplitTileGu;
+  if ((int)threadIdx.x < n_sh) {  // heaviest rows first: the slices of the shared expert
+    const int j = threadIdx.x;
+    FusedGroup g;
+    g.w_gate = reinterpret_cast<const unsigned char*>(r.shared_w_gate) + (size_t)j * slice * a.hidden * 2;
+    g.w_up = reinterpret_cast<const unsigned char*>(r.shared_w_up) + (size_t)j * slice * a.hidden * 2;
+    g.w_down = reinterpret_cast<const unsigned char*>(r.shared_w_down) + (size_t)j * slice * 2;
+    g.row_start = r.n_routed_rows + j * r.tokens;
+    g.rows = r.tokens;
+    g.inter = min(slice, r.shared_inter - j * slice);
+    g.ld_down = r.shared_inter;
+    g.tile_gu = j * (slice / kSplitTileGu);
+    g.tile_dn = j * dn_tiles;
+    sg[j] = g;
+  }
+  if (threadIdx.x < 32) {  // one warp compacts the activated resident experts in ascending id order
+    const int lane = threadIdx.x;
+    const unsigned lt = (1u << lane) - 1u;
+    const int gu_tiles = r.inter / kSplitTileGu;
+    int base = n_sh;
+    for (int c = 0; c < r.num_expert; c += 32) {
+      const int e = c + lane;
+      int cnt = 0, slot = -1, off = 0;
+      if (e < r.num_expert) {
+        cnt = r.counts[e];
+        slot = r.slot_table[e];
+        off = r.offsets[e];
+      }
+      const bool act = cnt > 0 && slot >= 0;
+      const unsigned mask = __ballot_sync(0xffffffffu, act);
+      if (act) {
+        const int idx = base + __popc(mask & lt);
+        const unsigned char* line = r.pool_base + (size_t)slot * r.line_stride;
+        FusedGroup g;
+        g.w_gate = line + r.off_gate;
+        g.w_up = line + r.off_up;
+        g.w_down = line + r.off_down;
+        g.row_start = off;
+        g.rows = cnt;
+        g.inter = r.inter;
+        g.ld_down = r.inter;
+        g.tile_gu = sh_tiles + (idx - n_sh) * gu_tiles;
+        g.tile_dn = idx * dn_tiles;
+        sg[idx] = g;
+      }
+      base += __popc(mask);
+    }
+    if (lane == 0) {
+      meta[0] = base;
+      meta[1] = sh_tiles + (base - n_sh) * gu_tiles;
+      meta[2] = base * dn_tiles;
+    }
   }
 }
 
 template <int NT, int DEPTH, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS)
-grouped_ffn_fused_kernel(const GroupDesc* __restrict__ groups, const int32_t* __restrict__ tile_gu,
-                         const int32_t* __restrict__ tile_dn, int tiles_gu, int tiles_dn, int* counters,
-                         const __nv_bfloat16* __restrict__ x, int hidden,
-                         const int32_t* __restrict__ row_token, __nv_bfloat16* hbuf, int ld_h,
-                         float* __restrict__ yexp, const int32_t* __restrict__ dev_tiles) {
+grouped_ffn_fused_kernel(const __grid_constant__ FusedLaunch a) {
   __shared__ float red[2][WARPS][2 * NT * 4][32];  // two reduction buffers, used alternately
-  (void)counters;
-  if (dev_tiles != nullptr) {  // plan built on the device: the tile counts live there too
-    tiles_gu = dev_tiles[0];
-    tiles_dn = dev_tiles[1];
-  }
+  __shared__ FusedGroup sg[kMaxFusedGroups];
+  __shared__ int meta[3];
+  build_chunk_table(a, sg, meta);
+  __syncthreads();
+  const int n = meta[0], tiles_gu = meta[1], tiles_dn = meta[2];
+  const int total_target = tiles_gu;  // arrivals of the whole launch: one per gate/up tile
+  const int b = blockIdx.x, grid = gridDim.x;
   StreamState<NT, DEPTH> st;
-  stream_begin<NT, true, DEPTH, WARPS>(st, groups, tile_gu, tiles_gu, x, hidden, row_token, hidden);
-  stream_run<NT, true, DEPTH, WARPS>(st, groups, tile_gu, tiles_gu, x, hidden, row_token, hidden, hbuf, ld_h, yexp, red);
-  // The first down tile's descriptor and weight loads do not depend on the intermediate rows: they go
-  // out before the barrier, so their DRAM latency is hidden behind it.
-  stream_begin<NT, false, DEPTH, WARPS>(st, groups, tile_dn, tiles_dn, hbuf, ld_h, row_token, hidden);
-  __threadfence();
-  cooperative_groups::this_grid().sync();
-  stream_run<NT, false, DEPTH, WARPS>(st, groups, tile_dn, tiles_dn, hbuf, ld_h, row_token, hidden, nullptr, ld_h, yexp,
-                                      red);
+  st.buf = 0;
+  st.all_done = false;
+  stream_begin<NT, true, DEPTH, WARPS>(st, sg, n, b, tiles_gu, a.x, a.hidden, a.row_token, a.hidden);
+  stream_run<NT, true, DEPTH, WARPS>(st, sg, n, tiles_gu, a.x, a.hidden, a.row_token, a.hidden, a.hbuf, a.ld_h, a.yexp,
+                                     red, a.counters, a.total, total_target, a.err);
+  // This CTA's place in the one round-robin sequence continues into the down tiles, so the CTAs
+  // that had one gate/up tile fewer take the first down tiles.
+  const int n1 = b < tiles_gu ? (tiles_gu - b + grid - 1) / grid : 0;
+  const int first_dn = b + n1 * grid - tiles_gu;
+  stream_begin<NT, false, DEPTH, WARPS>(st, sg, n, first_dn, tiles_dn, a.hbuf, a.ld_h, a.row_token, a.hidden);
+  stream_run<NT, false, DEPTH, WARPS>(st, sg, n, tiles_dn, a.hbuf, a.ld_h, a.row_token, a.hidden, nullptr, a.ld_h,
+                                      a.yexp, red, a.counters, a.total, total_target, a.err);
 }
 
+// 8 warps x 2 CTAs per SM. (16 warps x 1 CTA, one batch of loads per tile, measured 28 % slower at
+// 60 experts: with a single CTA per SM nothing overlaps the reduction.)
+constexpr int kFusedWarps = 8;
+
 // Resident grid of the fused kernel on the current device (0 if cooperative launch is unavailable).
-template <int NT, int DEPTH, int WARPS>
+template <int NT, int DEPTH>
 int fused_grid_size() {
   static int cached[64] = {};
   int dev = 0;
@@ -800,8 +816,8 @@ int fused_grid_size() {
   cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (!coop || sms <= 0 ||
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, grouped_ffn_fused_kernel<NT, DEPTH, WARPS>, WARPS * 32, 0) !=
-          cudaSuccess ||
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, grouped_ffn_fused_kernel<NT, DEPTH, kFusedWarps>,
+                                                    kFusedWarps * 32, 0) != cudaSuccess ||
       per_sm <= 0) {
     cached[dev] = -1;
     return 0;
@@ -810,47 +826,18 @@ int fused_grid_size() {
   return cached[dev];
 }
 
-template <int NT, int DEPTH, int WARPS>
-cudaError_t launch_fused_w(const GroupDesc* groups, const int32_t* t_gu, const int32_t* t_dn, int tiles_gu,
-                         int tiles_dn, int* counters, const __nv_bfloat16* x, int hidden,
-                         const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s,
-                         const int32_t* dev_tiles = nullptr) {
-  int grid = fused_grid_size<NT, DEPTH, WARPS>();
+template <int NT, int DEPTH>
+cudaError_t launch_fused(const FusedLaunch& a, int total_tiles, cudaStream_t s) {
+  int grid = fused_grid_size<NT, DEPTH>();
   if (grid <= 0) return cudaErrorNotSupported;
-  if (dev_tiles == nullptr) grid = min(grid, max(tiles_gu, tiles_dn));
-  void* args[] = {(void*)&groups, (void*)&t_gu, (void*)&t_dn, (void*)&tiles_gu, (void*)&tiles_dn, (void*)&counters,
-                  (void*)&x, (void*)&hidden, (void*)&row_token, (void*)&hbuf, (void*)&ld_h, (void*)&yexp,
-                  (void*)&dev_tiles};
-  return cudaLaunchCooperativeKernel((const void*)grouped_ffn_fused_kernel<NT, DEPTH, WARPS>, dim3(grid),
-                                     dim3(WARPS * 32), args, 0, s);
+  if (total_tiles > 0) grid = min(grid, total_tiles);
+  void* args[] = {(void*)&a};
+  return cudaLaunchCooperativeKernel((const void*)grouped_ffn_fused_kernel<NT, DEPTH, kFusedWarps>, dim3(grid),
+                                     dim3(kFusedWarps * 32), args, 0, s);
 }
 
-// 8 warps x 2 CTAs per SM. (16 warps x 1 CTA, one batch of loads per tile, measured 28 % slower at
-// 60 experts: with a single CTA per SM nothing overlaps the reduction and the barrier.)
-constexpr int kFusedWarps = 8;
-
-template <int NT, int DEPTH>
-cudaError_t launch_fused(const GroupDesc* groups, const int32_t* t_gu, const int32_t* t_dn, int tiles_gu,
-                         int tiles_dn, int* counters, const __nv_bfloat16* x, int hidden,
-                         const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s,
-                         const int32_t* dev_tiles = nullptr) {
-  return launch_fused_w<NT, DEPTH, kFusedWarps>(groups, t_gu, t_dn, tiles_gu, tiles_dn, counters, x, hidden, row_token,
-                                                hbuf, ld_h, yexp, s, dev_tiles);
-}
-
-template <int NT, int DEPTH>
-int fused_grid_size_any() {
-  return fused_grid_size<NT, DEPTH, kFusedWarps>();
-}
-
-template <int NT, int NMAT>
-cudaError_t launch_splitk(const GroupDesc* groups, const int32_t* tile_group, int tiles, const __nv_bfloat16* bsrc, int ldb,
-                          const int32_t* row_token, int hidden, __nv_bfloat16* hbuf, int ld_h, float* yexp,
-                          cudaStream_t s) {
-  constexpr int kDepthSplit = (NT == 1) ? 4 : 2;
-  grouped_ffn_splitk_kernel<NT, NMAT, kDepthSplit><<<tiles, kSplitThreads, 0, s>>>(
-      groups, tile_group, bsrc, ldb, row_token, hidden, hbuf, ld_h, yexp);
-  return cudaGetLastError();
+cudaError_t launch_fused_rows(const FusedLaunch& a, int max_rows, int total_tiles, cudaStream_t s) {
+  return max_rows <= 8 ? launch_fused<1, 4>(a, total_tiles, s) : launch_fused<2, 2>(a, total_tiles, s);
 }
 
 int kc_cap_for(int nt, int maxK) {
@@ -890,94 +877,34 @@ cudaError_t dispatch_nt(int max_rows, const GroupDesc* groups, const int32_t* ti
 
 }  // namespace
 
-// ---------------------------------------------------------------------------------------------
-// Device-side planner for the experts that are already resident. It turns the router's per-expert
-// row counts and the layer's expert -> slot table into a launch plan (descriptors, tile tables,
-// zeroed counters) without a host round trip, so the fused kernel for the resident experts and
-// the shared expert can be enqueued right behind the router while the host is still reading the
-// counts back to decide about the misses.
-// ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
-plan_resident_kernel(const int32_t* __restrict__ counts, const int32_t* __restrict__ offsets,
-                     const int32_t* __restrict__ slot_table, ResidentPlanArgs a, unsigned char* blob) {
-  __shared__ int s_n, s_tg, s_td;
-  __shared__ int s_cnt[256], s_off[256], s_slot[256];  // staged so that the serial pass reads no global memory
-  for (int e = threadIdx.x; e < a.num_expert; e += blockDim.x) {
-    s_cnt[e] = counts[e];
-    s_off[e] = offsets[e];
-    s_slot[e] = slot_table[e];
-  }
-  __syncthreads();
-  GroupDesc* desc = reinterpret_cast<GroupDesc*>(blob + a.off_desc);
-  int32_t* t_gu = reinterpret_cast<int32_t*>(blob + a.off_tile_gu);
-  int32_t* t_dn = reinterpret_cast<int32_t*>(blob + a.off_tile_dn);
-  int32_t* header = reinterpret_cast<int32_t*>(blob);  // [tiles_gu, tiles_dn, counter_gu, counter_dn, n_desc]
-  if (threadIdx.x == 0) {
-    int n = 0, tg = 0, td = 0;
-    const int dn_tiles = a.hidden / kSplitTileDn;
-    if (a.shared_inter > 0) {  // heaviest tiles first
-      GroupDesc d{};
-      d.w_gate = a.shared_w_gate; d.w_up = a.shared_w_up; d.w_down = a.shared_w_down;
-      d.row_start = a.n_routed_rows; d.row_count = a.tokens; d.inter = a.shared_inter;
-      d.tile_start_gu = tg; d.tile_start_dn = td;
-      desc[n++] = d;
-      tg += a.shared_inter / kSplitTileGu;
-      td += dn_tiles;
-    }
-    for (int e = 0; e < a.num_expert; ++e) {
-      const int slot = s_slot[e];
-      if (s_cnt[e] <= 0 || slot < 0) continue;
-      const unsigned char* line = a.pool_base + (size_t)slot * a.line_stride;
-      GroupDesc d{};
-      d.w_gate = line + a.off_gate; d.w_up = line + a.off_up; d.w_down = line + a.off_down;
-      d.row_start = s_off[e]; d.row_count = s_cnt[e]; d.inter = a.inter;
-      d.tile_start_gu = tg; d.tile_start_dn = td;
-      desc[n++] = d;
-      tg += a.inter / kSplitTileGu;
-      td += dn_tiles;
-    }
-    s_n = n; s_tg = tg; s_td = td;
-    header[0] = tg; header[1] = td; header[2] = 0; header[3] = 0; header[4] = n;
-  }
-  __syncthreads();
-  for (int d = 0; d < s_n; ++d) {
-    const int g0 = desc[d].tile_start_gu, g1 = (d + 1 < s_n) ? desc[d + 1].tile_start_gu : s_tg;
-    const int d0 = desc[d].tile_start_dn, d1 = (d + 1 < s_n) ? desc[d + 1].tile_start_dn : s_td;
-    for (int t = g0 + threadIdx.x; t < g1; t += blockDim.x) t_gu[t] = d;
-    for (int t = d0 + threadIdx.x; t < d1; t += blockDim.x) t_dn[t] = d;
-  }
-}
-
-cudaError_t launch_resident_ffn(const int32_t* counts, const int32_t* offsets, const int32_t* slot_table,
-                                const ResidentPlanArgs& a, unsigned char* blob_dev, int max_rows,
-                                const __nv_bfloat16* x, const int32_t* row_token, __nv_bfloat16* hbuf, int ld_h,
-                                float* yexp, cudaStream_t s, cudaEvent_t start_event) {
+cudaError_t launch_resident_ffn(const ResidentArgs& r, int32_t* counters, int32_t* err, int max_rows,
+                                const __nv_bfloat16* x, int hidden, const int32_t* row_token,
+                                __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s) {
   if (max_rows > kSplitMaxRows) return cudaErrorNotSupported;
-  plan_resident_kernel<<<1, 256, 0, s>>>(counts, offsets, slot_table, a, blob_dev);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
-  if (start_event != nullptr) {
-    e = cudaEventRecord(start_event, s);
-    if (e != cudaSuccess) return e;
-  }
-  const GroupDesc* groups = reinterpret_cast<const GroupDesc*>(blob_dev + a.off_desc);
-  const int32_t* t_gu = reinterpret_cast<const int32_t*>(blob_dev + a.off_tile_gu);
-  const int32_t* t_dn = reinterpret_cast<const int32_t*>(blob_dev + a.off_tile_dn);
-  int32_t* header = reinterpret_cast<int32_t*>(blob_dev);
-  if (max_rows <= 8)
-    return launch_fused<1, 4>(groups, t_gu, t_dn, 0, 0, header + 2, x, a.hidden, row_token, hbuf, ld_h, yexp, s, header);
-  return launch_fused<2, 2>(groups, t_gu, t_dn, 0, 0, header + 2, x, a.hidden, row_token, hbuf, ld_h, yexp, s, header);
+  FusedLaunch a{};
+  a.groups = nullptr;
+  a.res = r;
+  a.counters = counters;
+  a.total = counters + kMaxFusedGroups;
+  a.err = err;
+  a.x = x;
+  a.row_token = row_token;
+  a.hbuf = hbuf;
+  a.yexp = yexp;
+  a.hidden = hidden;
+  a.ld_h = ld_h;
+  return launch_fused_rows(a, max_rows, 0, s);  // the tile count is only known on the device: full grid
 }
 
 bool resident_ffn_available(int max_rows) {
   if (max_rows > kSplitMaxRows) return false;
-  return (max_rows <= 8 ? fused_grid_size_any<1, 4>() : fused_grid_size_any<2, 2>()) > 0;
+  return (max_rows <= 8 ? fused_grid_size<1, 4>() : fused_grid_size<2, 2>()) > 0;
 }
 
 cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& info, int quant4,
                               const __nv_bfloat16* x, int H, const int32_t* row_token,
                               __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s,
-                              cudaEvent_t mid_event, bool fused) {
+                              cudaEvent_t mid_event, int32_t* err) {
   if (info.n_desc <= 0) return cudaSuccess;
   const GroupDesc* groups = reinterpret_cast<const GroupDesc*>(blob_dev);
   const int32_t* t_gu = reinterpret_cast<const int32_t*>(blob_dev + info.off_tile_gu());
@@ -998,30 +925,31 @@ cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& 
                ? launch_q4<1, 1>(groups, t_dn, info.tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s)
                : launch_q4<2, 1>(groups, t_dn, info.tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s);
   }
-  if (fused && max_rows <= kSplitMaxRows && mid_event == nullptr) {
-    int* counters = reinterpret_cast<int*>(const_cast<unsigned char*>(blob_dev) + info.off_counters());
-    e = (max_rows <= 8)
-            ? launch_fused<1, 4>(groups, t_gu, t_dn, info.tiles_gu, info.tiles_dn, counters, x, H, row_token, hbuf, ld_h, yexp, s)
-            : launch_fused<2, 2>(groups, t_gu, t_dn, info.tiles_gu, info.tiles_dn, counters, x, H, row_token, hbuf, ld_h, yexp, s);
-    if (e != cudaErrorNotSupported) return e;
-    (void)cudaGetLastError();  // cooperative launch unavailable: fall through to the two-launch path
+  if (ffn_launch_is_fused(info, quant4)) {
+    if (info.n_desc > kMaxFusedGroups) return cudaErrorInvalidValue;
+    FusedLaunch a{};
+    a.groups = groups;
+    a.n_groups = info.n_desc;
+    a.tiles_gu = info.tiles_gu;
+    a.tiles_dn = info.tiles_dn;
+    int32_t* counters = reinterpret_cast<int32_t*>(const_cast<unsigned char*>(blob_dev) + info.off_counters());
+    a.counters = counters;
+    a.total = counters + info.n_desc;
+    a.err = err != nullptr ? err : counters + info.n_desc + 1;  // default: the blob's error word
+    a.x = x;
+    a.row_token = row_token;
+    a.hbuf = hbuf;
+    a.yexp = yexp;
+    a.hidden = H;
+    a.ld_h = ld_h;
+    return launch_fused_rows(a, max_rows, info.tiles_gu + info.tiles_dn, s);
   }
-  if (max_rows <= 8) {
-    e = launch_splitk<1, 2>(groups, t_gu, info.tiles_gu, x, H, row_token, H, hbuf, ld_h, yexp, s);
-  } else if (max_rows <= kSplitMaxRows) {
-    e = launch_splitk<2, 2>(groups, t_gu, info.tiles_gu, x, H, row_token, H, hbuf, ld_h, yexp, s);
-  } else {
-    e = dispatch_nt<2>(max_rows, groups, t_gu, info.tiles_gu, x, H, row_token, H, H, hbuf, ld_h, yexp, s);
-  }
+  e = dispatch_nt<2>(max_rows, groups, t_gu, info.tiles_gu, x, H, row_token, H, H, hbuf, ld_h, yexp, s);
   if (e != cudaSuccess) return e;
   if (mid_event != nullptr) {
     e = cudaEventRecord(mid_event, s);
     if (e != cudaSuccess) return e;
   }
-  if (max_rows <= 8)
-    return launch_splitk<1, 1>(groups, t_dn, info.tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s);
-  if (max_rows <= kSplitMaxRows)
-    return launch_splitk<2, 1>(groups, t_dn, info.tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s);
   return dispatch_nt<1>(max_rows, groups, t_dn, info.tiles_dn, hbuf, ld_h, row_token, H, ld_h, nullptr, ld_h,
                         yexp, s);
 }

@@ -116,6 +116,37 @@ class ExpertCache:
         _lib.call("pm_expert_slot", self._ctx, layer, expert, C.byref(s))
         return s.value
 
+    def expert_acquire(self, layer: int, expert: int, stream: int) -> int:
+        """report_one_expert + wait_expert for a caller that runs the expert itself on `stream`:
+        returns the device address of the expert's cache line (tensor i at + param_offset(i))."""
+        p = C.c_void_p()
+        _lib.call("pm_expert_acquire", self._ctx, layer, expert, stream, C.byref(p))
+        return p.value
+
+    def expert_release(self, layer: int, expert: int, stream: int) -> None:
+        _lib.call("pm_expert_release", self._ctx, layer, expert, stream)
+
+    def param_offset(self, param: int) -> int:
+        n = C.c_size_t()
+        _lib.call("pm_param_offset", self._ctx, param, C.byref(n))
+        return n.value
+
+    def temp_move_expert_to_gpu(self, layer: int, expert: int, stream: int) -> int:
+        p = C.c_void_p()
+        _lib.call("pm_temp_move_expert_to_gpu", self._ctx, layer, expert, stream, C.byref(p))
+        return p.value
+
+    def temp_move_expert_back_to_host(self, layer: int, expert: int, stream: int) -> None:
+        _lib.call("pm_temp_move_expert_back_to_host", self._ctx, layer, expert, stream)
+
+    def slab_tensor(self) -> torch.Tensor:
+        """The whole slab (policy lines + the spare line) as one uint8 CUDA tensor that aliases it."""
+        base, nbytes = int(self.get("slab_base")), int(self.get("slab_bytes"))
+
+        class _Raw:
+            __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (base, False), "version": 3}
+        return torch.as_tensor(_Raw(), device=torch.device("cuda", torch.cuda.current_device()))
+
     def param_device_ptr(self, layer: int, expert: int, param: int) -> int | None:
         p = C.c_void_p()
         _lib.call("pm_param_device_ptr", self._ctx, layer, expert, param, C.byref(p))
@@ -151,6 +182,12 @@ class ExpertCache:
         p = np.ascontiguousarray(prob, np.float32).reshape(-1, self.num_expert)
         _lib.call("pm_update_priority", self._ctx, p.ctypes.data_as(C.POINTER(C.c_float)), p.shape[0], start_layer)
 
+    def history_input(self) -> np.ndarray:
+        """[num_layer, num_expert] float32: the history-based predictor input (see pm_history_input)."""
+        out = np.zeros((self.num_layer, self.num_expert), np.float32)
+        _lib.call("pm_history_input", self._ctx, out.ctypes.data_as(C.POINTER(C.c_float)), out.size)
+        return out
+
     def enable_event_log(self, on: bool = True) -> None:
         _lib.call("pm_event_log_enable", self._ctx, int(on))
 
@@ -168,6 +205,14 @@ class ExpertCache:
         s = _lib.pm_stats()
         _lib.call("pm_stats_read", self._ctx, C.byref(s))
         return {name: getattr(s, name) for name, _ in s._fields_}
+
+    def iter_marks(self) -> list[dict]:
+        """Counters at the end of every model iteration (see pm_iter_marks_read)."""
+        n = C.c_size_t()
+        _lib.call("pm_iter_marks_read", self._ctx, None, 0, C.byref(n))
+        arr = (_lib.pm_stats * max(1, n.value))()
+        _lib.call("pm_iter_marks_read", self._ctx, arr, n.value, C.byref(n))
+        return [{name: getattr(s, name) for name, _ in s._fields_} for s in arr[: n.value]]
 
     def profile(self, reset: bool = False) -> dict:
         """Accumulated device time / weight bytes of the grouped FFN launches (profile_ffn=1)."""

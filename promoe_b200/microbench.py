@@ -17,30 +17,47 @@ import torch
 from . import _lib
 
 
-def run_rotating(groups: int, rows: int, hidden: int, inter: int, iters: int, sets: int) -> dict:
+def run_rotating(groups: int, rows: int, hidden: int, inter: int, iters: int, sets: int, shared_inter: int = 0,
+                 slices: int = 1, tokens: int = 8) -> dict:
     """Like run(), but cycles through `sets` disjoint weight sets (as a layer stack does), so that no
-    launch finds its weights, or their page translations, warm from the previous launch."""
+    launch finds its weights, or their page translations, warm from the previous launch. With
+    shared_inter > 0 every launch also carries a shared expert over all `tokens` rows, whole
+    (slices = 1) or cut into `slices` groups along its intermediate dimension, the way a decode
+    layer call launches it."""
     _lib.load()
     dev = torch.device("cuda")
     mat = inter * hidden
     x = torch.randn((64, hidden), device=dev).to(torch.bfloat16)
-    n_rows = groups * rows
+    n_routed = groups * rows
+    n_rows = n_routed + (slices * tokens if shared_inter else 0)
     row_token = torch.randint(0, 64, (n_rows,), dtype=torch.int32, device=dev)
-    nbytes = _lib.call("pm_k_swiglu_ffn_scratch_bytes", groups, n_rows, inter, hidden)
+    n_groups = groups + (slices if shared_inter else 0)
+    nbytes = _lib.call("pm_k_swiglu_ffn_scratch_bytes", n_groups, n_rows, max(inter, shared_inter), hidden)
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     yexp = torch.empty((n_rows, hidden), dtype=torch.float32, device=dev)
     plans, keep = [], []
     for _ in range(sets):
-        arr = (_lib.pm_ffn_group * groups)()
+        arr = (_lib.pm_ffn_group * n_groups)()
+        g0 = 0
+        if shared_inter:
+            sw = torch.empty(3 * shared_inter * hidden, dtype=torch.bfloat16, device=dev).normal_(0, 0.02)
+            keep.append(sw)
+            p, smat, width = sw.data_ptr(), shared_inter * hidden, shared_inter // slices
+            for j in range(slices):
+                arr[j] = _lib.pm_ffn_group(p + j * width * hidden * 2, p + smat * 2 + j * width * hidden * 2,
+                                           p + 2 * smat * 2 + j * width * 2, None, None, None,
+                                           n_routed + j * tokens, tokens, width, shared_inter)
+            g0 = slices
         for i in range(groups):
             w = torch.empty(3 * mat, dtype=torch.bfloat16, device=dev).normal_(0, 0.02)
             keep.append(w)
             p = w.data_ptr()
-            arr[i] = _lib.pm_ffn_group(p, p + mat * 2, p + 2 * mat * 2, None, None, None, i * rows, rows, inter, 0)
+            arr[g0 + i] = _lib.pm_ffn_group(p, p + mat * 2, p + 2 * mat * 2, None, None, None, i * rows, rows, inter, 0)
         plans.append(arr)
+    groups_total = n_groups
 
     def once(arr):
-        _lib.call("pm_k_swiglu_ffn", arr, groups, 0, x.data_ptr(), hidden, row_token.data_ptr(), n_rows,
+        _lib.call("pm_k_swiglu_ffn", arr, groups_total, 0, x.data_ptr(), hidden, row_token.data_ptr(), n_rows,
                   yexp.data_ptr(), scratch.data_ptr(), nbytes, None)
 
     for arr in plans:
@@ -53,8 +70,9 @@ def run_rotating(groups: int, rows: int, hidden: int, inter: int, iters: int, se
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / iters
-    weight_bytes = groups * 3 * mat * 2
-    return {"groups": groups, "rows": rows, "sets": sets, "total_gb": sets * weight_bytes / 1e9,
+    weight_bytes = (groups * 3 * mat + 3 * shared_inter * hidden) * 2
+    return {"groups": groups, "rows": rows, "shared_inter": shared_inter, "slices": slices, "sets": sets,
+            "total_gb": sets * weight_bytes / 1e9, "mb_per_launch": weight_bytes / 1e6,
             "us_per_launch": ms * 1e3, "gb_per_s": weight_bytes / ms / 1e6}
 
 
@@ -151,12 +169,16 @@ def main():
     ap.add_argument("--config", default="c5")
     ap.add_argument("--no-tc", action="store_true", help="prefill through the staged mma.sync kernel")
     ap.add_argument("--rotate", type=int, default=0, help="cycle through this many disjoint weight sets")
+    ap.add_argument("--shared-inter", type=int, default=0, help="with --rotate: add a shared expert of this width")
+    ap.add_argument("--slices", type=int, default=1, help="cut the shared expert into this many groups")
+    ap.add_argument("--tokens", type=int, default=8, help="rows of the shared expert")
     a = ap.parse_args()
     if a.prefill_tokens:
         print(json.dumps(run_prefill(a.config, a.prefill_tokens, a.iters, not a.no_tc)))
         return
     if a.rotate > 1:
-        print(json.dumps(run_rotating(a.groups, a.rows, a.hidden, a.inter, a.iters, a.rotate)))
+        print(json.dumps(run_rotating(a.groups, a.rows, a.hidden, a.inter, a.iters, a.rotate, a.shared_inter, a.slices,
+                                      a.tokens)))
         return
     print(json.dumps(run(a.groups, a.rows, a.hidden, a.inter, a.iters, a.warmup, a.quant4)))
 

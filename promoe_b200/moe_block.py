@@ -34,7 +34,13 @@ def describe_block(block: torch.nn.Module, config=None) -> dict:
     gate_w = gate.weight
     first = block.experts[0]
     mixtral = hasattr(first, "w1")
-    inter = (first.w1 if mixtral else first.gate_proj).weight.shape[0]
+    proj = first.w1 if mixtral else first.gate_proj
+    # uint4 experts in this library's layout (promoe_b200.quant4.adapt_quantised_linear): packed rows
+    quant4 = getattr(proj, "qweight", None) is not None and getattr(proj, "scale_zero", None) is not None
+    inter = proj.qweight.shape[0] if quant4 else proj.weight.shape[0]
+    method = getattr(gate, "topk_method", getattr(block, "topk_method", "greedy"))
+    if method not in (None, "greedy"):
+        raise ValueError(f"the fused router selects the k largest probabilities (greedy); this block uses {method!r}")
     shared = _first(block, ("shared_expert", "shared_experts"))
     shared_gate = getattr(block, "shared_expert_gate", None)
     cfg = config if config is not None else getattr(block, "config", None)
@@ -48,7 +54,7 @@ def describe_block(block: torch.nn.Module, config=None) -> dict:
         norm = bool(getattr(block, "norm_topk_prob", getattr(gate, "norm_topk_prob", getattr(cfg, "norm_topk_prob", False))))
     scale = float(getattr(block, "routed_scaling_factor", getattr(gate, "routed_scaling_factor", 1.0)) or 1.0)
     return dict(gate_w=gate_w, inter=inter, top_k=int(top_k), norm_topk=norm, routed_scale=scale,
-                shared=shared, shared_gate=shared_gate)
+                shared=shared, shared_gate=shared_gate, quant4=quant4)
 
 
 def install_fused_forward(block: torch.nn.Module, cache, layer_id: int, device="cuda", config=None,
@@ -65,7 +71,7 @@ def install_fused_forward(block: torch.nn.Module, cache, layer_id: int, device="
     if d["shared_gate"] is not None:
         sgw = _bf16_dev(d["shared_gate"].weight.reshape(-1), dev)
     cache.set_layer_weights(layer_id, _bf16_dev(d["gate_w"], dev), d["inter"], d["top_k"], d["norm_topk"],
-                            d["routed_scale"], shared=shared, shared_gate_w=sgw)
+                            d["routed_scale"], shared=shared, shared_gate_w=sgw, quant4=d["quant4"])
     block._promoe_layer_id = layer_id
     block._promoe_cache = cache
     if not hasattr(block, "_unfused_forward"):

@@ -82,14 +82,16 @@ def register_expert_params(model, model_loader, filter=_EXPERT):
 
 def replace_expert_param_reference(model, model_loader, filter=_EXPERT):
     """Points every expert parameter at the loader's logical tensor, which releases the original
-    host copy once it has been pinned into the cache's records."""
+    host copy once it has been pinned into the cache's records. The logical tensor object itself
+    goes into the module (as in the reference, utils/__init__.py:58-69): the loader re-points it in
+    place whenever the expert moves to another cache line."""
     model_loader.build_logical_expert_param()
 
     def per_expert(module, name):
         def per_leaf(leaf, leaf_name):
             for n, _ in list(leaf.named_parameters(recurse=False)):
-                ref = model_loader.ref_one_expert_param(module._layer_id, module._expert_id, f"{leaf_name}.{n}")
-                leaf._parameters[n] = torch.nn.Parameter(ref, requires_grad=False)
+                leaf._parameters[n] = model_loader.ref_one_expert_param(module._layer_id, module._expert_id,
+                                                                        f"{leaf_name}.{n}")
             for n, _ in list(leaf.named_buffers(recurse=False)):
                 if param_buffer_name_to_prefetch(n):
                     leaf._buffers[n] = model_loader.ref_one_expert_param(module._layer_id, module._expert_id, f"{leaf_name}.{n}")
@@ -141,8 +143,10 @@ def install_fused_moe_forward(model, prefetch_mngr, filter, device="cuda"):
     config = getattr(model, "config", None)
 
     def install(module, name):
-        if hasattr(module, "experts") and hasattr(module, "gate"):
-            install_fused_forward(module, cache, module._layer_id, device, config)
+        if not (hasattr(module, "experts") and hasattr(module, "gate")):
+            raise ValueError(f"{name} matches the MoE block filter but has no `experts` and `gate`: it cannot be "
+                             "given the fused forward (pass fused=False to keep the model's own expert loop)")
+        install_fused_forward(module, cache, module._layer_id, device, config)
     recursive_traverse_childrens(model, install, filter)
 
 

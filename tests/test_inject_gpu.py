@@ -174,3 +174,112 @@ def test_hook_path_replays_a_trace_like_the_simulate_demo(lib):
             step = []
     assert cache.events() == oc.events
     assert cache.plan_slots() == oc.lens
+
+
+def test_inject_model_unfused_python_expert_loop(lib):
+    """fused=False: the model's own Python expert loop runs under ExpertHook. Every expert module's
+    parameters are the loader's logical tensors, re-pointed to the expert's cache line inside
+    report_one_expert, so the loop computes from the cache lines. With 6 lines for up to 12 activated
+    experts, lines change hands inside one layer call."""
+    from promoe_b200.utils import inject_model
+    torch.manual_seed(1)
+    L, H, E, I, k = 2, 128, 12, 64, 4
+    model = TinyQwen(L, H, E, I).eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            p.copy_((p * (3.0 if p.shape[0] == E and p.dim() == 2 and p.shape[1] == H else 1.0)).to(torch.bfloat16).float())
+    xs = [torch.randn(5, 1, H).to(torch.bfloat16) for _ in range(4)]
+    import copy
+    plain = copy.deepcopy(model).to("cuda", torch.bfloat16)
+    routed = []
+    for l, layer in enumerate(plain.model.layers):
+        layer.mlp.report_experts = (lambda ll: lambda ids: routed.append((ll, ids.tolist())) or ids)(l)
+    with torch.no_grad():
+        ref = [plain(x.cuda()) for x in xs]     # the same modules with their own weights on the GPU
+    fused_model = copy.deepcopy(model)
+    mngr = inject_model(model, num_moe_layer=L, num_expert_per_layer=E, num_expert_per_token=k, cache_rate=0.5,
+                        num_predict_expert_per_layer=0, fused=False)
+    cache = mngr.metas.cache
+    cache.enable_event_log(True)
+    model.to("cuda", torch.bfloat16)
+    first = model.model.layers[0].mlp.experts[0].gate_proj
+    assert first.weight.numel() == 0, "nothing is resident before the first report"
+    with torch.no_grad():
+        for x, r in zip(xs, ref):
+            y = model(x.cuda())
+            torch.cuda.synchronize()
+            # same modules, same kernels, weights read from the cache lines: equal to the last bit
+            assert torch.equal(y, r)
+    assert any(m.gate_proj.weight.shape == (I, H) for m in model.model.layers[0].mlp.experts)
+    oc = sp.SequentialCache(L, E, k, cache_rate=0.5, num_predict=0)
+    for l, ids in routed:
+        oc.report_layer(l, ids)                # includes the per-expert hook calls
+    assert cache.events() == oc.events
+    st = cache.stats()
+    assert st["precise_miss"] > 0 and st["h2d_copies"] == st["precise_miss"]
+    # and the fused path on a copy of the same model agrees within the bf16 tolerance
+    mngr2 = inject_model(fused_model, num_moe_layer=L, num_expert_per_layer=E, num_expert_per_token=k, cache_rate=0.5,
+                         num_predict_expert_per_layer=0)
+    fused_model.to("cuda", torch.bfloat16)
+    with torch.no_grad():
+        for x, r in zip(xs, ref):
+            y = fused_model(x.cuda()).float().cpu().numpy()
+            np.testing.assert_allclose(y, r.float().cpu().numpy(), rtol=3e-2, atol=3e-2 * np.abs(r.float().cpu().numpy()).max())
+
+
+def test_param_device_ptr_follows_the_expert_across_an_eviction(lib):
+    """pm_param_device_ptr / pm_expert_slot through the C ABI: NULL while the expert is absent, the
+    line's address while it is resident, NULL again after the eviction, and the tensor's bytes
+    in the line equal the registered ones."""
+    from tests.helpers import TinyModel
+    model = TinyModel(seed=2, L=1, E=4, H=128, I=64, k=1)
+    cache = model.make_cache(cache_rate=0.5, num_predict_expert_per_layer=0)   # 2 lines
+    assert cache.param_device_ptr(0, 0, 0) is None and cache.expert_slot(0, 0) == -1
+    cache.report_layer(0, [0])
+    cache.report_expert(0, 0)
+    p0 = cache.param_device_ptr(0, 0, 1)
+    assert p0 is not None and cache.expert_slot(0, 0) == 1       # the first miss takes the last-created line
+    torch.cuda.synchronize()
+    base, off = int(cache.get("slab_base")), cache.param_offset(1)
+    slab = cache.slab_tensor()
+    got = slab[p0 - base: p0 - base + 64 * 128 * 2].view(torch.bfloat16).view(64, 128).float().cpu().numpy()
+    np.testing.assert_array_equal(got, model.experts[0][0][1])
+    assert (p0 - base - off) % int(cache.get("line_stride")) == 0
+    cache.expert_done(0, 0)
+    cache.report_layer(0, [1])
+    cache.report_expert(0, 1)
+    cache.expert_done(0, 1)
+    cache.report_layer(0, [2])
+    cache.report_expert(0, 2)                                    # LRU: expert 0 loses its line
+    assert cache.param_device_ptr(0, 0, 1) is None and cache.expert_slot(0, 0) == -1
+    assert cache.param_device_ptr(0, 2, 1) == p0                 # the line changed hands
+    cache.close()
+
+
+def test_temp_move_expert_round_trip(lib):
+    """temp_move_expert_to_gpu puts the expert into the spare line and points its logical parameters
+    there; a device-side change of the tensors reaches the pinned host record with
+    temp_move_expert_back_to_host (what a quantised layer's post_init relies on)."""
+    from promoe_b200 import cpp_worker as cw
+    meta = cw.ModuleMeta(1, 2)
+    meta.init_param_list(["gate_proj.weight", "up_proj.weight", "down_proj.weight"])
+    meta.init_from_map({"cache_rate": "0.5", "num_expert_per_token": "1", "num_predict_expert_per_layer": "0"})
+    loader = cw.ModelLoader(meta)
+    ws = {}
+    for e in range(2):
+        for n, shape in (("gate_proj.weight", (64, 128)), ("up_proj.weight", (64, 128)), ("down_proj.weight", (128, 64))):
+            ws[(e, n)] = torch.randn(shape).to(torch.bfloat16)
+            loader.add_one_expert_param(ws[(e, n)], 0, e, n)
+    mngr = cw.PrefetchMngr(meta, loader, cw.PredictorBase.create(meta))
+    mngr.init_gpu_mem_buffer()
+    w = loader.ref_one_expert_param(0, 1, "up_proj.weight")
+    assert w.numel() == 0
+    mngr.temp_move_expert_to_gpu(0, 1)
+    assert w.shape == (64, 128) and torch.equal(w.cpu(), ws[(1, "up_proj.weight")])
+    w.mul_(2)
+    mngr.temp_move_expert_back_to_host(0, 1)
+    addr, n = meta.cache.host_record(0, 1, 1)
+    import ctypes
+    host = torch.frombuffer((ctypes.c_char * n).from_address(addr), dtype=torch.bfloat16).view(64, 128)
+    assert torch.equal(host, ws[(1, "up_proj.weight")] * 2)
+    meta.cache.close()

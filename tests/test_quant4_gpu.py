@@ -100,3 +100,90 @@ def test_q4_fused_layer_mixtral_like(lib):
             np.testing.assert_allclose(got, ref, rtol=RTOL_Q4, atol=RTOL_Q4 * np.abs(ref).max() * 0.25)
     assert cache.events() == oc.events
     cache.close()
+
+
+def test_gptq_checkpoint_layout_through_inject_model(lib):
+    """A Mixtral-style model whose experts carry AutoGPTQ tensors (qweight / qzeros / scales / g_idx):
+    adapt_quantised_linear rewrites them to the library layout, inject_model registers and moves
+    them, the fused layer computes with them; the oracle uses its own GPTQ dequantiser."""
+    from dataclasses import dataclass
+    from torch import nn
+    from promoe_b200.utils import inject_model
+    from tests.test_quant_layouts import gptq_tensors
+
+    @dataclass
+    class Cfg:
+        _name_or_path: str = "mistralai/Mixtral-8x7B-Instruct-v0.1"
+        num_experts_per_tok: int = 2
+
+    class QLinear(nn.Module):
+        def __init__(self, rng, in_f, out_f):
+            super().__init__()
+            qw, qz, sc, _, _ = gptq_tensors(rng, in_f, out_f)
+            self.register_buffer("qweight", torch.from_numpy(qw))
+            self.register_buffer("qzeros", torch.from_numpy(qz))
+            self.register_buffer("scales", torch.from_numpy(sc))
+            self.register_buffer("g_idx", torch.arange(in_f, dtype=torch.int32) // 128)
+            self.dense = oq.dequantize_gptq(qw, qz, sc)          # [out, in] float32, oracle side
+
+    class Expert(nn.Module):
+        def __init__(self, rng, H, I):
+            super().__init__()
+            self.w1, self.w3, self.w2 = QLinear(rng, H, I), QLinear(rng, H, I), QLinear(rng, I, H)
+
+    class Block(nn.Module):
+        def __init__(self, rng, H, E, I):
+            super().__init__()
+            self.gate = nn.Linear(H, E, bias=False)
+            self.experts = nn.ModuleList([Expert(rng, H, I) for _ in range(E)])
+
+        def report_experts(self, ids):
+            return ids
+
+    class Layer(nn.Module):
+        def __init__(self, rng, H, E, I):
+            super().__init__()
+            self.block_sparse_moe = Block(rng, H, E, I)
+
+        def forward(self, h):
+            return (self.block_sparse_moe(h),)
+
+    class Model(nn.Module):
+        def __init__(self, L, H, E, I):
+            super().__init__()
+            rng = np.random.default_rng(9)
+            self.config = Cfg()
+            self.model = nn.Module()
+            self.model.layers = nn.ModuleList([Layer(rng, H, E, I) for _ in range(L)])
+
+        def forward(self, h):
+            return [layer(h)[0] for layer in self.model.layers]
+
+    L, H, E, I, k = 2, 256, 8, 128, 2
+    torch.manual_seed(3)
+    model = Model(L, H, E, I).eval()
+    gates, dense = [], []
+    for layer in model.model.layers:
+        blk = layer.block_sparse_moe
+        with torch.no_grad():
+            blk.gate.weight.copy_((blk.gate.weight * 3).to(torch.bfloat16).float())
+        gates.append(blk.gate.weight.detach().numpy().copy())
+        dense.append([(e.w1.dense, e.w3.dense, e.w2.dense) for e in blk.experts])
+        for e in blk.experts:
+            for lin in (e.w1, e.w3, e.w2):
+                pq.adapt_quantised_linear(lin, "gptq")
+                assert set(lin._buffers) == {"qweight", "scale_zero"}
+    mngr = inject_model(model, num_moe_layer=L, num_expert_per_layer=E, num_expert_per_token=k, cache_rate=0.5,
+                        num_predict_expert_per_layer=0)
+    model.to("cuda")
+    rng = np.random.default_rng(4)
+    for _ in range(3):
+        x = om.bf16_round(rng.standard_normal((5, H)).astype(np.float32))
+        with torch.no_grad():
+            ys = model(dev_bf16(x).view(5, 1, H))
+        torch.cuda.synchronize()
+        for l in range(L):
+            ref, _, _ = om.moe_block_forward(x, gates[l], dense[l], k, True, round_h_bf16=True)
+            got = ys[l].float().cpu().numpy().reshape(5, H)
+            np.testing.assert_allclose(got, ref, rtol=RTOL_Q4, atol=RTOL_Q4 * np.abs(ref).max() * 0.25)
+    assert mngr.metas.cache.stats()["precise_miss"] > 0
