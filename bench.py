@@ -42,6 +42,9 @@ def parse_args():
     ap.add_argument("--cache-rate", type=float, default=None, help="override the configuration's cache_rate")
     ap.add_argument("--prefill-tokens", type=int, default=0,
                     help="run one prefill of this many tokens through the stack first and report its time")
+    ap.add_argument("--profile-steps", type=int, default=16,
+                    help="steps of the separate profiled pass that gives the roofline figures")
+    ap.add_argument("--no-ep-parity", action="store_true", help="skip the untimed parity step of multi-GPU runs")
     return ap.parse_args()
 
 
@@ -152,6 +155,10 @@ def run_reference(args, cfg):
         return
     import torch
     threads = os.cpu_count() or 1
+    num_predict = args.num_predict
+    if num_predict is None:
+        num_predict = cfg.top_k if cfg.predictor_width else 0
+    use_pred = num_predict > 0 and cfg.predictor_width > 0
     steps = max(2, min(args.steps + args.warmup, 64))
     res = cpu_baseline(cfg, args.cpu_sample_layers, steps, threads)
     ms = res["seconds_per_layer_step"] * cfg.num_layer * 1e3
@@ -159,7 +166,9 @@ def run_reference(args, cfg):
         "impl": "reference", "metric": METRIC, "value": res["tokens_per_s"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(cfg, args.gpus, predictor=False),
+        # the same workload description as the GPU arm prints (the CPU arm copies nothing, so the
+        # predictor, which only schedules copies, has nothing to act on there)
+        "config": workload_config(cfg, args.gpus, use_pred, num_predict),
         "cpu_baseline": {"value": res["tokens_per_s"], "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": res["sample"], "torch": torch.__version__, "hit_rate": res["hit_rate"]},
         "e2e": {"value": res["tokens_per_s"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -215,6 +224,92 @@ def roofline_entry(prof, gu_gbs, dn_gbs, fu_gbs, peak, peak_src):
 
 
 # --------------------------------------------------------------------------- our arm
+def h2d_peak(record_bytes: int, dev, copies: int = 64) -> float:
+    """Pinned host -> device bandwidth of this box for copies of one expert record (GB/s): the ceiling of
+    the miss path. Two pinned sources and destinations are alternated on one stream, like the cache does."""
+    import torch
+    n = max(1, record_bytes)
+    src = [torch.empty(n, dtype=torch.uint8).pin_memory() for _ in range(2)]
+    dst = [torch.empty(n, dtype=torch.uint8, device=dev) for _ in range(2)]
+    s = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(s):
+        for i in range(4):
+            dst[i % 2].copy_(src[i % 2], non_blocking=True)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        for i in range(copies):
+            dst[i % 2].copy_(src[i % 2], non_blocking=True)
+        e1.record(s)
+    s.synchronize()
+    return copies * n / (e0.elapsed_time(e1) / 1e3) / 1e9
+
+
+def ep_parity_check(stack, ep, be, cfg, rank, world, x, preds, pmap, n_local_pred):
+    """One untimed decode step through the expert-parallel stack with the event log on, checked outside
+    every timed region: this rank's outputs against the single-process oracle on its tokens, and its
+    cache log against a sequential-schedule cache over its block of experts fed with the ids that
+    arrived from all ranks and the prefetches its summed predictor scores rank."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from oracle import moe_math as om
+    from oracle import srs_policy as sp
+    from promoe_b200 import synth
+    cache = stack.cache
+    cache.enable_event_log(True)
+    L, E, H = cfg.num_layer, cfg.num_expert, cfg.hidden
+    e0, n_local = be.geo.bounds[rank], be.n_local
+    xn = x.float().cpu().numpy()
+    worst = 0.0
+
+    class Lazy:  # experts of one layer, generated from their seeds when the oracle touches them
+        def __init__(self, layer):
+            self.layer = layer
+
+        def __getitem__(self, e):
+            return tuple(synth._randn(sh, synth.seed_for(cfg.name, self.layer, e, nm), stack.device).float().cpu().numpy()
+                         for nm, sh in (("gate", (cfg.inter, H)), ("up", (cfg.inter, H)), ("down", (H, cfg.inter))))
+
+    my_ids, my_scores = [], []
+    for l in range(L):
+        y = ep.forward(l, x)
+        torch.cuda.synchronize()
+        gate_w = stack.gate_w[l].float().cpu().numpy()
+        bias = stack.gate_bias[l].cpu().numpy()
+        ids, w = om.route(om.gate_logits_canonical(xn, gate_w, bias), cfg.top_k, cfg.norm_topk)
+        shared = [t.float().cpu().numpy() for t in stack.shared[l]] if cfg.shared_inter else None
+        sgw = stack.shared_gate_w[l].float().cpu().numpy() if cfg.shared_gate else None
+        ref, ids64, _ = om.moe_block_forward(xn, gate_w, Lazy(l), cfg.top_k, cfg.norm_topk, gate_bias=bias, shared=shared,
+                                             shared_gate_w=sgw, round_h_bf16=True)
+        got = y.float().cpu().numpy()
+        if np.array_equal(ids64, ids):   # a float32 / float64 routing tie would compare different experts
+            worst = max(worst, float(np.linalg.norm(got - ref) / np.linalg.norm(ref)))
+        my_ids.append(sorted(set(int(v) for v in ids.reshape(-1))))
+        sc = {}
+        for d in (range(*pmap[l]) if preds else ()):
+            if (l, d) in preds:
+                w1, b1, w2, b2 = (None if t is None else t.float().cpu().numpy() for t in preds[(l, d)])
+                sc[d] = om.predictor_scores(xn, w1, b1, w2, b2)
+        my_scores.append(sc)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, (my_ids, my_scores))
+    oc = sp.SequentialCache(L, n_local, cfg.top_k, cache_rate=cfg.cache_rate, num_predict=n_local_pred)
+    for l in range(L):
+        for d in sorted(gathered[0][1][l]):
+            total = sum(gathered[r][1][l][d] for r in range(world))
+            oc.prefetch_layer(d, om.rank_experts(total[e0: e0 + n_local], oc.num_predict))
+        act = sorted({e - e0 for r in range(world) for e in gathered[r][0][l] if e0 <= e < e0 + n_local})
+        if act:
+            oc.report_layer(l, act)
+    log_equal = cache.events(clear=True) == oc.events
+    cache.enable_event_log(False)
+    flags = torch.tensor([worst, 0.0 if log_equal else 1.0], device=x.device, dtype=torch.float64)
+    dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+    return {"rel_err": float(flags[0]), "cache_log_equal": bool(flags[1] == 0.0), "layers": L,
+            "checked": "one decode step, every rank: outputs vs the single-process oracle on its tokens, cache log vs "
+                       "a sequential-schedule cache over its experts"}
+
+
 def run_ours(args, cfg):
     import torch
     import torch.distributed as dist
@@ -229,6 +324,7 @@ def run_ours(args, cfg):
     from promoe_b200.numa import bind_to_gpu_numa_node
     numa = bind_to_gpu_numa_node(local_rank)  # before any pinned memory is allocated
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     dev = torch.device("cuda", local_rank)
 
@@ -243,17 +339,25 @@ def run_ours(args, cfg):
         raise SystemExit(f"batch {cfg.batch} does not divide over {world} ranks")
     B = cfg.batch // world
     K, W = args.steps, args.warmup
-    ep = None
+    ep = be = None
+    preds, pmap, n_local_pred = {}, [], 0
     if world > 1:
-        # expert parallel: this rank holds a contiguous block of experts and its own cache over them;
-        # the next-layer predictor is a single-GPU feature of the reference and stays off here
-        from promoe_b200.ep import CudaBackend, ExpertParallelMoE, expert_bounds
-        b = expert_bounds(cfg.num_expert, world)
-        use_pred, num_predict = False, 0
-        stack = synth.SyntheticStack(cfg, dev, expert_range=(b[rank], b[rank + 1] - b[rank]),
-                                     num_predict_expert_per_layer=0)
+        # expert parallel: this rank holds a contiguous block of experts and its own cache over them; every
+        # rank runs the predictor on its tokens, the scores of an owner's experts travel in the dispatch
+        # message, the owner sums them and prefetches its share of the predicted experts
+        from promoe_b200.ep import CudaBackend, ExpertParallelMoE, Geometry, expert_bounds
+        bnd = expert_bounds(cfg.num_expert, world)
+        n_local = bnd[rank + 1] - bnd[rank]
+        n_local_pred = max(1, round(num_predict * n_local / cfg.num_expert)) if use_pred else 0
+        stack = synth.SyntheticStack(cfg, dev, expert_range=(bnd[rank], n_local), num_predict_expert_per_layer=n_local_pred)
         stack.install_routed_only()
-        ep = ExpertParallelMoE(cfg.num_expert, CudaBackend(stack.cache, stack.ep_layers(), dev))
+        if use_pred:
+            preds, pmap = stack.make_predictors()
+        n_pred = max((b - a for a, b in pmap), default=0)
+        geo = Geometry(cfg.num_expert, world, B, cfg.top_k, H, n_pred=n_pred)
+        be = CudaBackend(stack.cache, stack.ep_layers(), dev, geo, rank, predictors=preds, predict_map=pmap,
+                         global_tokens=cfg.batch)
+        ep = ExpertParallelMoE(geo, be)
     else:
         stack = synth.SyntheticStack(cfg, dev, num_predict_expert_per_layer=num_predict,
                                      predict_from_moe_input=use_pred)
@@ -261,7 +365,8 @@ def run_ours(args, cfg):
         if use_pred:
             stack.install_predictors()
     cache = stack.cache
-    xs = synth.hidden_stream(cfg, W + 2 * K + 4, B, dev, seed_tag=f"hidden{rank}")
+    P = min(K, args.profile_steps)  # a separate, profiled pass gives the roofline figures
+    xs = synth.hidden_stream(cfg, W + 2 * K + P + 5, B, dev, seed_tag=f"hidden{rank}")
     y = torch.empty((B, H), dtype=torch.bfloat16, device=dev)
 
     def step_device(t):
@@ -275,6 +380,10 @@ def run_ours(args, cfg):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    ep_parity = None
+    if ep is not None and not args.no_ep_parity:
+        ep_parity = ep_parity_check(stack, ep, be, cfg, rank, world, xs[W + 2 * K + P + 4], preds, pmap, n_local_pred)
 
     prefill = None
     if args.prefill_tokens > 0 and ep is None:
@@ -300,9 +409,10 @@ def run_ours(args, cfg):
     for t in range(W):
         step_device(t)
     barrier()
-    cache.set("profile_ffn", 1)
-    cache.profile(reset=True)
+
+    # ---- timed region: K steps, nothing but the forward calls inside ------------------------------
     s0 = cache.stats()
+    launches0 = be.launches if be is not None else 0
     sampler = ClockSampler(local_rank)
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -313,11 +423,10 @@ def run_ours(args, cfg):
     barrier()
     ms_total = ev0.elapsed_time(ev1)
     clocks = sampler.stop()
-    prof = cache.profile(reset=True)
-    cache.set("profile_ffn", 0)
     s1 = cache.stats()
+    launches1 = be.launches if be is not None else 0
 
-    # end to end: host buffers in, host buffers out, through the same public call
+    # ---- end to end: host buffers in, host buffers out, through the same public call --------------
     xh = xs[W + K: W + 2 * K].cpu().pin_memory()
     yh = torch.empty((B, H), dtype=torch.bfloat16).pin_memory()
     barrier()
@@ -333,6 +442,28 @@ def run_ours(args, cfg):
     barrier()
     ms_e2e = e0.elapsed_time(e1)
 
+    # ---- profiled pass (untimed for the headline): CUDA events around every FFN launch -------------
+    cache.set("profile_ffn", 1)
+    cache.profile(reset=True)
+    for t in range(W + 2 * K, W + 2 * K + P):
+        step_device(t)
+    barrier()
+    prof = cache.profile(reset=True)
+    cache.set("profile_ffn", 0)
+
+    breakdown = None
+    if ep is not None:
+        ep.trace = []
+        for t in range(W + 2 * K + P, W + 2 * K + P + 4):
+            step_device(t)
+        barrier()
+        breakdown = ep.trace_summary()
+        ep.trace = None
+        bt = torch.tensor([breakdown[k] for k in sorted(breakdown)], device=dev, dtype=torch.float64)
+        dist.all_reduce(bt, op=dist.ReduceOp.MAX)
+        breakdown = {k: float(v) for k, v in zip(sorted(breakdown), bt.tolist())}
+        breakdown["note"] = "us per layer call, CUDA events on the compute stream, max over ranks, 4 steps"
+
     if world > 1:
         tt = torch.tensor([ms_total, ms_e2e], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -341,33 +472,57 @@ def run_ours(args, cfg):
     value = tokens / (ms_total / 1e3)
     e2e = tokens / (ms_e2e / 1e3)
 
+    record_bytes = int(cache.get("record_bytes"))
+    h2d_peak_gbs = h2d_peak(record_bytes, dev)
+    h2d_eff = (s1["h2d_bytes"] - s0["h2d_bytes"]) / (ms_total / 1e3) / 1e9
     peak, peak_src = measured_peak_gbs()
     gu_gbs = prof["gateup_bytes"] / (prof["gateup_ms"] / 1e3) / 1e9 if prof["gateup_ms"] > 0 else 0.0
     dn_gbs = prof["down_bytes"] / (prof["down_ms"] / 1e3) / 1e9 if prof["down_ms"] > 0 else 0.0
     fu_gbs = prof["fused_bytes"] / (prof["fused_ms"] / 1e3) / 1e9 if prof["fused_ms"] > 0 else 0.0
     hits, misses = s1["precise_hit"] - s0["precise_hit"], s1["precise_miss"] - s0["precise_miss"]
+    stats_local = [hits, misses, s1["h2d_bytes"] - s0["h2d_bytes"], s1["prefetch_miss"] - s0["prefetch_miss"]]
+    per_rank_h2d = None
+    if world > 1:  # whole-job cache figures: sums over the ranks; H2D rate per rank (one PCIe link each)
+        st = torch.tensor(stats_local, device=dev, dtype=torch.float64)
+        allst = [torch.zeros_like(st) for _ in range(world)]
+        dist.all_gather(allst, st)
+        per_rank_h2d = [float(a[2]) / (ms_total / 1e3) / 1e9 for a in allst]
+        hits, misses = int(sum(a[0] for a in allst)), int(sum(a[1] for a in allst))
+        stats_local[2] = float(sum(a[2] for a in allst))
+        stats_local[3] = int(sum(a[3] for a in allst))
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": workload_config(cfg, world, use_pred, num_predict),
         "clocks": clocks,
-        "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": L * B * H * 2, "d2h_bytes_per_step": L * B * H * 2,
-                "ms_per_step": ms_e2e / K},
-        "gpu_launches": s1["kernel_launches"] - s0["kernel_launches"],
+        "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": L * B * H * 2 * world,
+                "d2h_bytes_per_step": L * B * H * 2 * world, "ms_per_step": ms_e2e / K},
+        "gpu_launches": (s1["kernel_launches"] - s0["kernel_launches"]) + (launches1 - launches0),
         "roofline": roofline_entry(prof, gu_gbs, dn_gbs, fu_gbs, peak, peak_src),
         "cache": {"hit_rate": hits / max(1, hits + misses), "precise_hit": hits, "precise_miss": misses,
-                  "prefetch_miss": s1["prefetch_miss"] - s0["prefetch_miss"],
-                  "h2d_gb_per_step": (s1["h2d_bytes"] - s0["h2d_bytes"]) / K / 1e9,
-                  "h2d_gbs_effective": (s1["h2d_bytes"] - s0["h2d_bytes"]) / (ms_total / 1e3) / 1e9,
+                  "prefetch_miss": stats_local[3],
+                  "h2d_gb_per_step": stats_local[2] / K / 1e9,
+                  "h2d_gbs_effective": h2d_eff, "h2d_peak_gbs": h2d_peak_gbs, "h2d_frac": h2d_eff / h2d_peak_gbs,
+                  "h2d_note": "h2d_gbs_effective = this rank's expert-copy bytes over the timed region; h2d_peak_gbs = "
+                              "pinned host-to-device copies of one expert record, back to back, measured in this run; "
+                              "the headline is bound by this link, so h2d_frac is its roofline",
                   "slab_impl": cache.get("slab_impl"), "numa": numa},
     }
+    if per_rank_h2d is not None:
+        line["cache"]["h2d_gbs_per_rank"] = per_rank_h2d
+    if ep_parity is not None:
+        line["ep_parity"] = ep_parity
+    if breakdown is not None:
+        line["ep_layer_breakdown_us"] = breakdown
     if prefill is not None:
         line["prefill"] = prefill
     if rank == 0 and not args.no_cpu_baseline and world == 1:
         threads = min(8, os.cpu_count() or 1)  # the reference pins torch to 8 threads (utils/__init__.py:343)
         if cfg.quant4:  # the CPU path computes on the dequantised float32 masters: one layer is 5.6 GB
             res = cpu_baseline(cfg, 1, min(args.cpu_sample_steps, 24), threads, stack=None)
+        elif cfg.num_expert * cfg.inter * cfg.hidden * 12 > 8e9:  # float32 copies of one layer above 8 GB: one layer
+            res = cpu_baseline(cfg, 1, min(args.cpu_sample_steps, 16), threads, stack=stack)
         else:
             res = cpu_baseline(cfg, args.cpu_sample_layers, args.cpu_sample_steps, threads, stack=stack)
         line["cpu_baseline"] = {"value": res["tokens_per_s"], "unit": UNIT, "cores": threads, "kind": "port",

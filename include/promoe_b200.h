@@ -75,7 +75,13 @@ int pm_build_slab(pm_ctx* ctx);
 /* Builds the slot pools without any device memory (policy-only use, no GPU needed). */
 int pm_build_policy_only(pm_ctx* ctx);
 /* Device address the tensor currently has in the slab, NULL if the expert is not resident
- * (ModelLoader::ref_one_expert_param, src/cpp_worker/model_loader.hpp:309-314). */
+ * (ModelLoader::ref_one_expert_param, src/cpp_worker/model_loader.hpp:309-314). With the context
+ * option stable_va=1 (set before pm_build_slab; VMM slab only) every expert has an address range of
+ * its own into which the line that holds it is mapped a second time: the address returned here is
+ * then the same for the life of the context, and readable whenever the expert is resident (the
+ * reference's ExpertParamWrapperCUDriver, src/cpp_worker/model_loader.cpp:102-164, for kernels that
+ * capture raw pointers once). In that mode a line that changes hands is remapped on the host,
+ * which waits for the last kernel that read it. */
 int pm_param_device_ptr(pm_ctx* ctx, int layer, int expert, int param_id, void** out);
 /* Slot (index inside the layer's pool, creation order) of an expert, -1 if absent. */
 int pm_expert_slot(pm_ctx* ctx, int layer, int expert, int32_t* slot);
@@ -203,13 +209,20 @@ int pm_layer_set_weights(pm_ctx* ctx, int layer, const pm_layer_weights* w);
  * around it (src/sparse_llm_cache/utils/hooks.py:187-223). */
 int pm_moe_forward(pm_ctx* ctx, int layer, const void* x_dev, int T, void* y_dev, void* stream);
 /* Expert-parallel receive side: the rows were routed elsewhere. x_rows [n_rows, hidden] bf16 and
- * row_expert [n_rows] int32 (expert ids local to this context) are device buffers; rows_out
- * [n_rows, hidden] f32 receives each row's unweighted expert output, in row order. Cache
- * bookkeeping, copies and the grouped FFN are those of pm_moe_forward; there is no router, no
- * shared expert and no combine (gate_w of the layer may be NULL). No counterpart in the
- * reference, which is single-GPU (src/cpp_worker/model_loader.cpp:75-79). */
+ * row_expert [n_rows] int32 (expert ids local to this context; -1 marks a padding row) are device
+ * buffers; rows_out [n_rows, hidden] f32 receives each row's unweighted expert output, in row order
+ * (zeros for padding rows). Cache bookkeeping, copies and the grouped FFN are those of
+ * pm_moe_forward; there is no router, no shared expert and no combine (gate_w of the layer may be
+ * NULL). An id outside [-1, num_expert) is PM_ERR_INVALID. max_rows_per_expert (0 = unknown) is a
+ * bound on the rows one expert can receive that the caller guarantees, e.g. the number of tokens
+ * in flight on all ranks: up to 16, the resident experts start before the host has read the row
+ * counts. pred_scores (device f32 [n_pred, num_expert], may be NULL) are predictor scores for the
+ * layers pred_layers[0..n_pred) (host int32), summed over whoever computed them: they are ranked
+ * and prefetched like the scores of pm_report_hidden, before this layer's own report. No
+ * counterpart in the reference, which is single-GPU (src/cpp_worker/model_loader.cpp:75-79). */
 int pm_moe_forward_routed(pm_ctx* ctx, int layer, const void* x_rows, int n_rows, const int32_t* row_expert,
-                          float* rows_out, void* stream);
+                          float* rows_out, int max_rows_per_expert, const float* pred_scores,
+                          const int32_t* pred_layers, int n_pred, void* stream);
 /* Same with host buffers (pinned or pageable): copies x in and y out on the stream and waits. */
 int pm_moe_forward_host(pm_ctx* ctx, int layer, const void* x_host, int T, void* y_host, void* stream);
 /* Routing of the most recent pm_moe_forward on `layer` (host copies): ids/weights [T, k]. */
@@ -277,6 +290,24 @@ int pm_k_swiglu_ffn(const pm_ffn_group* groups, int n_groups, int quant4, const 
 size_t pm_k_swiglu_ffn_static_capacity(void);
 int pm_k_swiglu_ffn_static(const pm_ffn_group* groups, int n_groups, const void* x, int hidden,
                            const int32_t* row_token, int n_rows, float* yexp, void* stream);
+/* Expert-parallel exchange buffers (no counterpart in the reference, which is single-GPU). One
+ * fixed-size message per peer and direction, so the per-layer dispatch is one all-to-all with
+ * split sizes known in advance. Message of a source to owner g: 1 + cap rows of `hidden` bf16;
+ * row 0 = header (int32 counts[max_block] of the rows for each of g's experts, then float
+ * scores[n_pred][max_block], the source's predictor scores of g's experts), rows 1.. = the token
+ * rows routed to g's experts in expert order. pm_k_ep_pack builds the n_ranks messages from the
+ * permutation's outputs (counts, offsets, row_token, pos; bounds_dev = device int32 [n_ranks + 1],
+ * rank g owns experts [bounds[g], bounds[g+1])) and writes pos_reply [n_pairs]: the row of the
+ * reply buffer [n_ranks * (1 + cap), hidden] f32 where the output of routed pair (t, j) returns.
+ * pm_k_ep_unpack turns a receive buffer into row_expert [n_ranks * (1 + cap)] (local expert id,
+ * -1 for header and unused rows: the row list pm_moe_forward_routed takes) and scores_sum
+ * [n_pred, n_local] (the sources' scores added in rank order). */
+int pm_k_ep_pack(const void* x, int hidden, const int32_t* counts, const int32_t* offsets,
+                 const int32_t* row_token, const int32_t* pos, int n_pairs, const int32_t* bounds_dev,
+                 int n_ranks, int max_block, int cap, const float* scores, int n_pred, int num_expert,
+                 void* send, int32_t* pos_reply, void* stream);
+int pm_k_ep_unpack(const void* recv, int hidden, int n_ranks, int n_local, int max_block, int cap, int n_pred,
+                   int32_t* row_expert, float* scores_sum, int32_t* err_flag, void* stream);
 int pm_k_combine(const float* yexp, const int32_t* pos, const float* topk_w, int T, int H, int k, int R,
                  int n_shared, const float* shared_scale, void* y, void* stream);
 /* scores[e] = sum_b (W2 relu(W1 x_b + b1) + b2)[e]; hidden_scratch is f32 [B, d] device scratch. */

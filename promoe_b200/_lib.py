@@ -94,7 +94,7 @@ SIGNATURES = {
     "pm_profile_read": (_i, [_vp, C.POINTER(pm_profile), _i]),
     "pm_layer_set_weights": (_i, [_vp, _i, C.POINTER(pm_layer_weights)]),
     "pm_moe_forward": (_i, [_vp, _i, _vp, _i, _vp, _vp]),
-    "pm_moe_forward_routed": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
+    "pm_moe_forward_routed": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _vp]),
     "pm_moe_forward_host": (_i, [_vp, _i, _vp, _i, _vp, _vp]),
     "pm_last_routing": (_i, [_vp, _i, C.POINTER(C.c_int32), C.POINTER(_f), _i]),
     "pm_predictor_set": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp]),
@@ -106,6 +106,8 @@ SIGNATURES = {
     "pm_k_swiglu_ffn": (_i, [C.POINTER(pm_ffn_group), _i, _i, _vp, _i, _vp, _i, _vp, _vp, _sz, _vp]),
     "pm_k_swiglu_ffn_static_capacity": (_sz, []),
     "pm_k_swiglu_ffn_static": (_i, [C.POINTER(pm_ffn_group), _i, _vp, _i, _vp, _i, _vp, _vp]),
+    "pm_k_ep_pack": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp]),
+    "pm_k_ep_unpack": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "pm_k_combine": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
     "pm_k_predictor_mlp": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp]),
 }

@@ -284,6 +284,12 @@ class ModelLoader:
             self._slab = cache.slab_tensor()
             self._slab_base = int(cache.get("slab_base"))
             self._offsets = [cache.param_offset(p) for p in range(len(self._names))]
+            self._ranges, self._ranges_base = None, 0
+            if cache.get("stable_va") == "true":  # addresses then lie in the experts' own ranges
+                self._ranges, self._ranges_base = cache.expert_range_tensor(), int(cache.get("expert_va_base"))
+        raw, base = self._slab, self._slab_base
+        if self._ranges is not None and not (base <= line_addr < base + raw.numel()):
+            raw, base = self._ranges, self._ranges_base
         for pid in range(len(self._names)):
             key = (layer_id, expert_id, pid)
             t = self._logical.get(key)
@@ -293,8 +299,8 @@ class ModelLoader:
             n = 1
             for d in shape:
                 n *= d
-            off = line_addr - self._slab_base + self._offsets[pid]
-            view = self._slab[off:off + n * torch.empty(0, dtype=dtype).element_size()].view(dtype).view(shape)
+            off = line_addr - base + self._offsets[pid]
+            view = raw[off:off + n * torch.empty(0, dtype=dtype).element_size()].view(dtype).view(shape)
             with torch.no_grad():
                 t.set_(view)
         self._line[(layer_id, expert_id)] = line_addr

@@ -84,6 +84,8 @@ int pm_ctx_get(pm_ctx* ctx, const char* key, char* buf, size_t cap) {
   }
   else if (k == "slab_impl") v = !ctx->slab_built ? "none" : (ctx->slab_vmm ? "vmm" : "cudamalloc");
   else if (k == "line_stride") v = std::to_string(ctx->line_stride);
+  else if (k == "stable_va") v = ctx->stable_va ? "true" : "false";
+  else if (k == "expert_va_base") v = std::to_string((unsigned long long)(uintptr_t)ctx->expert_va);
   else if (k == "slab_base") v = std::to_string((unsigned long long)(uintptr_t)ctx->slab);
   else if (k == "slab_bytes") v = std::to_string((unsigned long long)ctx->line_stride * (ctx->n_lines + 1));
   else if (k == "num_lines") v = std::to_string(ctx->n_lines);
@@ -108,6 +110,11 @@ int pm_ctx_set(pm_ctx* ctx, const char* key, const char* value) {
   }
   if (k == "tc_prefill") {
     ctx->tc_prefill = (v == "1" || v == "true" || v == "True" || v == "on");
+    return PM_OK;
+  }
+  if (k == "stable_va") {
+    if (ctx->slab_built) return fail(PM_ERR_STATE, "stable_va must be set before build_slab");
+    ctx->stable_va = (v == "1" || v == "true" || v == "True" || v == "on");
     return PM_OK;
   }
   if (k == "device_plan") {
@@ -199,6 +206,10 @@ int pm_param_device_ptr(pm_ctx* ctx, int layer, int expert, int param_id, void**
   if (layer < 0 || layer >= ctx->cfg.num_layer || expert < 0 || expert >= ctx->cfg.num_expert || param_id < 0 ||
       param_id >= ctx->cfg.num_per_expert_param())
     return fail(PM_ERR_INVALID, "layer, expert or tensor index out of range");
+  if (ctx->stable_va) {  // the expert's own range: the same address for the life of the context
+    *out = ctx->expert_va + ((size_t)layer * ctx->cfg.num_expert + expert) * ctx->line_stride + ctx->param_offset[param_id];
+    return PM_OK;
+  }
   int line = ctx->eng->expert(layer, expert).line;
   if (line >= 0) *out = ctx->slab + (size_t)line * ctx->line_stride + ctx->param_offset[param_id];
   return PM_OK;
@@ -423,11 +434,17 @@ int pm_moe_forward(pm_ctx* ctx, int layer, const void* x_dev, int T, void* y_dev
 }
 
 int pm_moe_forward_routed(pm_ctx* ctx, int layer, const void* x_rows, int n_rows, const int32_t* row_expert,
-                          float* rows_out, void* stream) {
+                          float* rows_out, int max_rows_per_expert, const float* pred_scores,
+                          const int32_t* pred_layers, int n_pred, void* stream) {
   if (need(ctx)) return PM_ERR_INVALID;
+  if (n_pred < 0 || (n_pred > 0 && (!pred_scores || !pred_layers))) return fail(PM_ERR_INVALID, "bad prediction arguments");
   RoutedRows r;
   r.row_expert = row_expert;
   r.rows_out = rows_out;
+  r.max_rows_per_expert = max_rows_per_expert;
+  r.pred_scores = pred_scores;
+  r.pred_layers = pred_layers;
+  r.n_pred = n_pred;
   return rt_forward(ctx, layer, x_rows, n_rows, nullptr, (cudaStream_t)stream, &r);
 }
 

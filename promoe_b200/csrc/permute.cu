@@ -35,9 +35,9 @@ permute_kernel(const int32_t* __restrict__ topk_ids, int R, int k, int E, int32_
     int e = topk_ids[i];
     if (e >= 0 && e < E) {
       atomicAdd(&cnt[e], 1);
-    } else {  // id outside [0, E): the pair is dropped and flagged; its position must not keep an old value
-      pos[i] = -1;
-      if (err_flag != nullptr) atomicExch(err_flag, 1);
+    } else {  // -1 = padding, dropped silently; any other id outside [0, E) is dropped and flagged.
+      pos[i] = -1;  // either way the position must not keep an old value
+      if (e != -1 && err_flag != nullptr) atomicExch(err_flag, 1);
     }
   }
   __syncthreads();
@@ -91,7 +91,7 @@ permute_count_kernel(const int32_t* __restrict__ topk_ids, int R, int E, int32_t
       atomicAdd(&cnt[e], 1);
     } else {
       pos[i] = -1;
-      if (err_flag != nullptr) atomicExch(err_flag, 1);
+      if (e != -1 && err_flag != nullptr) atomicExch(err_flag, 1);
     }
   }
   __syncthreads();

@@ -66,9 +66,35 @@ cudaEvent_t next_seg_event(pm_ctx* c) {
   return e;
 }
 
+// stable_va: the line now belongs to expert f, so it leaves the previous owner's address range and
+// appears in f's. Unmapping needs the line idle: the host waits for the last kernel that read it.
+int remap_line(pm_ctx* c, int line, size_t f) {
+  if (c->line_mapped_to[line] == (int32_t)f) return PM_OK;
+  Driver& d = driver();
+  if (c->line_read[line] != nullptr) PM_CUDA(cudaEventSynchronize(c->line_read[line]));
+  if (c->line_mapped_to[line] >= 0) {
+    CUresult r = d.Unmap((CUdeviceptr)(c->expert_va + (size_t)c->line_mapped_to[line] * c->line_stride), c->line_stride);
+    if (r != CUDA_SUCCESS) return fail_cu(r, "cuMemUnmap (expert range)");
+  }
+  const CUdeviceptr va = (CUdeviceptr)(c->expert_va + f * c->line_stride);
+  CUresult r = d.Map(va, c->line_stride, 0, c->line_handles[line], 0);
+  if (r != CUDA_SUCCESS) return fail_cu(r, "cuMemMap (expert range)");
+  CUmemAccessDesc acc{};
+  acc.location = c->line_prop.location;
+  acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  r = d.SetAccess(va, c->line_stride, &acc, 1);
+  if (r != CUDA_SUCCESS) return fail_cu(r, "cuMemSetAccess (expert range)");
+  c->line_mapped_to[line] = (int32_t)f;
+  return PM_OK;
+}
+
 int enqueue_copy(pm_ctx* c, const Action& a) {
   const int E = c->cfg.num_expert;
   const size_t f = (size_t)a.layer * E + a.expert;
+  if (c->stable_va) {
+    int rc = remap_line(c, a.line, f);
+    if (rc != PM_OK) return rc;
+  }
   const size_t b0 = c->param_offset[a.chunk_begin], b1 = c->param_offset[a.chunk_end];
   cudaStream_t cs = c->cfg.cache_only ? c->last_stream : c->copy_stream;
   if (c->line_read[a.line] != nullptr) PM_CUDA(cudaStreamWaitEvent(cs, c->line_read[a.line], 0));
@@ -376,7 +402,17 @@ int rt_build_slab(pm_ctx* c) {
     r = d.SetAccess(base, c->slab_va_bytes, &acc, 1);
     if (r != CUDA_SUCCESS) return fail_cu(r, "cuMemSetAccess");
     c->slab_vmm = true;
+    c->line_prop = prop;
+    if (c->stable_va) {
+      c->expert_va_bytes = c->line_stride * (size_t)c->cfg.num_layer * c->cfg.num_expert;
+      CUdeviceptr eva = 0;
+      r = d.AddressReserve(&eva, c->expert_va_bytes, gran, 0, 0);
+      if (r != CUDA_SUCCESS) return fail_cu(r, "cuMemAddressReserve (expert ranges)");
+      c->expert_va = (unsigned char*)eva;
+      c->line_mapped_to.assign(n_lines, -1);
+    }
   } else {
+    if (c->stable_va) return fail(PM_ERR_UNSUPPORTED, "stable_va needs the VMM slab");
     c->line_stride = align_up(rec, 256);
     PM_CUDA(cudaMalloc((void**)&c->slab, c->line_stride * n_lines));
   }
@@ -594,7 +630,9 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
                              c->d_topk_w, c->d_topk_slot, c->d_shared_scale, nullptr, s));
     c->kernel_launches += 1;
   }
-  const bool spec = c->device_plan && !w.quant4 && resident_ffn_available(T);  // rows per expert <= T
+  // rows per expert <= T, or the bound the caller of the routed-rows form guarantees
+  const int row_bound = (routed && routed->max_rows_per_expert > 0) ? std::min(T, routed->max_rows_per_expert) : T;
+  const bool spec = c->device_plan && !w.quant4 && resident_ffn_available(row_bound);
   PM_CUDA(launch_permute(ids_dev, R, k, E, c->d_counts, c->d_offsets, c->d_row_token, c->d_pos, c->d_err,
                          n_shared * T, T, s, c->d_perm_scratch, c->perm_scratch_ints,
                          spec ? c->d_res_counters : nullptr, kMaxFusedGroups + 1));
@@ -609,8 +647,19 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
   PM_CUDA(cudaEventRecord(c->routed_event, s));
   cudaStream_t rb = c->readback_stream;
   PM_CUDA(cudaStreamWaitEvent(rb, c->routed_event, 0));
-  if (!pred_dsts.empty())
+  if (routed && routed->n_pred > 0 && routed->pred_scores != nullptr && c->seq_len == 1) {
+    // scores computed elsewhere (the expert-parallel sources): they ride to the host with the counts
+    if (routed->n_pred > c->cfg.num_layer) return fail(PM_ERR_INVALID, "more predicted layers than layers");
+    for (int i = 0; i < routed->n_pred; ++i) {
+      const int dst = routed->pred_layers[i];
+      if (dst < 0 || dst >= c->cfg.num_layer) return fail(PM_ERR_INVALID, "predicted layer out of range");
+      PM_CUDA(cudaMemcpyAsync(st.scores + (size_t)dst * E, routed->pred_scores + (size_t)i * E, (size_t)E * 4,
+                              cudaMemcpyDeviceToHost, rb));
+      pred_dsts.push_back(dst);
+    }
+  } else if (!pred_dsts.empty()) {
     PM_CUDA(cudaMemcpyAsync(st.scores, c->d_scores, (size_t)c->cfg.num_layer * E * 4, cudaMemcpyDeviceToHost, rb));
+  }
   PM_CUDA(cudaMemcpyAsync(st.counts, c->d_counts, (size_t)(2 * E + 3) * 4, cudaMemcpyDeviceToHost, rb));
   const bool keep = c->keep_routing && !routed;
   if (keep) {
@@ -667,8 +716,8 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
       PM_CUDA(take_event(&spec_sample.e2));
       PM_CUDA(cudaEventRecord(spec_sample.e0, s));
     }
-    PM_CUDA(launch_resident_ffn(a, c->d_res_counters, c->d_tc_err, T, x, H, c->d_row_token, c->d_hbuf, c->ws_inter,
-                                c->d_yexp, s));
+    PM_CUDA(launch_resident_ffn(a, c->d_res_counters, c->d_tc_err, row_bound, x, H, c->d_row_token, c->d_hbuf,
+                                c->ws_inter, c->d_yexp, s));
     if (c->profile_ffn) PM_CUDA(cudaEventRecord(spec_sample.e2, s));
     c->kernel_launches += 1;
     cudaEvent_t ev = next_seg_event(c);
@@ -848,7 +897,8 @@ int rt_expert_acquire(pm_ctx* c, int layer, int expert, cudaStream_t s, void** l
     c->line_pending[line] = 0;
     c->line_waiter[line] = s;
   }
-  *line_out = line_ptr(c, line);
+  *line_out = c->stable_va ? (void*)(c->expert_va + ((size_t)layer * c->cfg.num_expert + expert) * c->line_stride)
+                           : (void*)line_ptr(c, line);
   return PM_OK;
 }
 
@@ -944,6 +994,11 @@ pm_ctx::~pm_ctx() {
   if (slab_built) {
     if (slab_vmm) {
       pm::Driver& d = pm::driver();
+      if (expert_va != nullptr) {
+        for (size_t i = 0; i < line_mapped_to.size(); ++i)
+          if (line_mapped_to[i] >= 0) d.Unmap((CUdeviceptr)(expert_va + (size_t)line_mapped_to[i] * line_stride), line_stride);
+        d.AddressFree((CUdeviceptr)expert_va, expert_va_bytes);
+      }
       d.Unmap((CUdeviceptr)slab, slab_va_bytes);
       for (auto h : line_handles) d.Release(h);
       d.AddressFree((CUdeviceptr)slab, slab_va_bytes);

@@ -42,6 +42,15 @@ struct pm_ctx {
   int n_lines = 0;  // lines the policy owns; one more (index n_lines) is the spare line of temp_move_expert_*
   std::vector<CUmemGenericAllocationHandle> line_handles;
   size_t slab_va_bytes = 0;
+  // Optional (context option stable_va=1, VMM slab only): every expert also has an address range of
+  // its own that never changes; the line that holds the expert is mapped there a second time, so raw
+  // pointers a caller captured once stay valid across evictions and refetches (what the reference's
+  // ExpertParamWrapperCUDriver gives exllama kernels, src/cpp_worker/model_loader.cpp:102-164).
+  bool stable_va = false;
+  unsigned char* expert_va = nullptr;   // [L * E] ranges of line_stride bytes
+  size_t expert_va_bytes = 0;
+  std::vector<int32_t> line_mapped_to;  // flat expert whose range the line is mapped into, -1 = none
+  CUmemAllocationProp line_prop{};
 
   // ---- streams and events -------------------------------------------------------------
   cudaStream_t copy_stream = nullptr;
@@ -138,9 +147,19 @@ int rt_execute_copies(pm_ctx* c, const std::vector<Action>& actions);
 // routed: the caller supplies one local expert id per row (row_expert, device int32 [T]); there is
 // no router, no shared expert and no weighted combine, and rows_out (device f32 [T, hidden])
 // receives every row's expert output in row order. Used by the expert-parallel receive side.
+// row_expert -1 marks a padding row (no expert runs on it, its output row is zeros).
+// max_rows_per_expert (0 = unknown): an upper bound on the rows any one expert receives that the
+// caller guarantees (e.g. the global number of tokens); with a bound of at most 16 the resident
+// experts are launched without waiting for the host. pred_scores (optional): device f32
+// [n_pred, num_expert], predictor scores of layers pred_layers[i] that travel to the host with
+// the row counts; each is ranked and prefetched before this layer's own report.
 struct RoutedRows {
   const int32_t* row_expert = nullptr;
   float* rows_out = nullptr;
+  int max_rows_per_expert = 0;
+  const float* pred_scores = nullptr;
+  const int32_t* pred_layers = nullptr;  // host
+  int n_pred = 0;
 };
 int rt_forward(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStream_t s, const RoutedRows* routed = nullptr);
 int rt_forward_host(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStream_t s);

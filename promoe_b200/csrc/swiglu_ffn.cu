@@ -468,10 +468,12 @@ __device__ __forceinline__ void tile_setup(TileCtx<NT>& t, const FusedGroup& d, 
                                    : nullptr;
 }
 
-template <int NT, int DEPTH>
+// The DEPTH register slots of a lane hold the k-steps s0 .. s0 + DEPTH - 1 of the tile; the helpers
+// below work on the slots [FIRST, FIRST + COUNT), so that the two halves can be refilled separately.
+template <int NT, int DEPTH, int FIRST = 0, int COUNT = DEPTH>
 __device__ __forceinline__ void tile_issue_a(const TileCtx<NT>& t, int s0, uint4 (&a)[DEPTH][4]) {
 #pragma unroll
-  for (int d = 0; d < DEPTH; ++d) {
+  for (int d = FIRST; d < FIRST + COUNT; ++d) {
     if (s0 + d < t.s_end) {
       const size_t off = (size_t)(s0 + d) * 64;
 #pragma unroll
@@ -480,10 +482,10 @@ __device__ __forceinline__ void tile_issue_a(const TileCtx<NT>& t, int s0, uint4
   }
 }
 
-template <int NT, int DEPTH, bool COHERENT_B>
+template <int NT, int DEPTH, bool COHERENT_B, int FIRST = 0, int COUNT = DEPTH>
 __device__ __forceinline__ void tile_issue_b(const TileCtx<NT>& t, int s0, uint4 (&b)[DEPTH][NT]) {
 #pragma unroll
-  for (int d = 0; d < DEPTH; ++d) {
+  for (int d = FIRST; d < FIRST + COUNT; ++d) {
     if (s0 + d < t.s_end) {
       const size_t off = (size_t)(s0 + d) * 64;
 #pragma unroll
@@ -493,11 +495,11 @@ __device__ __forceinline__ void tile_issue_b(const TileCtx<NT>& t, int s0, uint4
   }
 }
 
-template <int NT, int DEPTH>
+template <int NT, int DEPTH, int FIRST = 0, int COUNT = DEPTH>
 __device__ __forceinline__ void tile_compute(const TileCtx<NT>& t, int s0, const uint4 (&a)[DEPTH][4],
                                              const uint4 (&b)[DEPTH][NT], float (&acc)[2][NT][4]) {
 #pragma unroll
-  for (int d = 0; d < DEPTH; ++d) {
+  for (int d = FIRST; d < FIRST + COUNT; ++d) {
     if (s0 + d < t.s_end) {
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
@@ -660,16 +662,25 @@ __device__ __forceinline__ void stream_run(StreamState<NT, DEPTH>& st, const Fus
     const int gi_next = has_next ? find_group<GATEUP>(sg, n_groups, t.gi, next) : 0;
     int src_row[NT];
     bool rows_loaded = false;
-    for (int s0 = 0; s0 < t.s_end;) {
-      tile_compute<NT, DEPTH>(t, s0, st.a, st.b, acc);
+    // Two half-batches of k-steps are in flight per lane; whenever one has been consumed it is refilled
+    // with the steps DEPTH further on, so a warp always has loads outstanding while it waits.
+    constexpr int HALF = DEPTH / 2;
+    for (int s0 = 0; s0 < t.s_end; s0 += DEPTH) {
+      tile_compute<NT, DEPTH, 0, HALF>(t, s0, st.a, st.b, acc);
+      if (s0 + DEPTH < t.s_end) {
+        tile_issue_a<NT, DEPTH, 0, HALF>(t, s0 + DEPTH, st.a);
+        tile_issue_b<NT, DEPTH, COH, 0, HALF>(t, s0 + DEPTH, st.b);
+      }
       if (has_next && !rows_loaded) {  // fetch the next tile's token row numbers under this tile's loads
         load_src_rows<NT, GATEUP>(src_row, sg[gi_next], row_token);
         rows_loaded = true;
       }
-      s0 += DEPTH;
-      if (s0 < t.s_end) {
-        tile_issue_a<NT, DEPTH>(t, s0, st.a);
-        tile_issue_b<NT, DEPTH, COH>(t, s0, st.b);
+      if (s0 + HALF < t.s_end) {
+        tile_compute<NT, DEPTH, HALF, HALF>(t, s0, st.a, st.b, acc);
+        if (s0 + DEPTH + HALF < t.s_end) {
+          tile_issue_a<NT, DEPTH, HALF, HALF>(t, s0 + DEPTH, st.a);
+          tile_issue_b<NT, DEPTH, COH, HALF, HALF>(t, s0 + DEPTH, st.b);
+        }
       }
     }
     if (has_next && !rows_loaded) load_src_rows<NT, GATEUP>(src_row, sg[gi_next], row_token);

@@ -139,6 +139,16 @@ class ExpertCache:
     def temp_move_expert_back_to_host(self, layer: int, expert: int, stream: int) -> None:
         _lib.call("pm_temp_move_expert_back_to_host", self._ctx, layer, expert, stream)
 
+    def expert_range_tensor(self) -> torch.Tensor:
+        """stable_va=1: the experts' own address ranges ([L * E] x line_stride bytes) as one uint8 CUDA
+        tensor. Only the ranges of resident experts are mapped; touching another part faults."""
+        base = int(self.get("expert_va_base"))
+        nbytes = int(self.get("line_stride")) * self.num_layer * self.num_expert
+
+        class _Raw:
+            __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (base, False), "version": 3}
+        return torch.as_tensor(_Raw(), device=torch.device("cuda", torch.cuda.current_device()))
+
     def slab_tensor(self) -> torch.Tensor:
         """The whole slab (policy lines + the spare line) as one uint8 CUDA tensor that aliases it."""
         base, nbytes = int(self.get("slab_base")), int(self.get("slab_bytes"))

@@ -195,21 +195,30 @@ class SyntheticStack:
                      top_k=cfg.top_k, norm_topk=cfg.norm_topk, routed_scale=1.0, inter=cfg.inter)
                 for l in range(self.num_layer)]
 
-    def install_predictors(self):
-        """Random-initialised MLPs hidden -> width -> num_expert (ReLU) for every (source, target)
-        pair of the reference's default prediction window (predictor.cpp:8-46)."""
+    def make_predictors(self):
+        """Random-initialised MLPs hidden -> width -> num_expert (ReLU, over ALL experts) for every
+        (source, target) pair of the reference's default prediction window (predictor.cpp:8-46).
+        Returns (dict (src, dst) -> (w1, b1, w2, b2), list of (first, last + 1) per source index)."""
         cfg = self.cfg
         if not cfg.predictor_width:
-            return
+            return {}, []
         L, W, E = self.num_layer, cfg.predictor_width, cfg.num_expert
-        for src, (a, b) in enumerate(predict_layer_mapping(L, window0=int(self.cache.get("limit_layer_0_window")))):
+        mapping = predict_layer_mapping(L, window0=int(self.cache.get("limit_layer_0_window")))
+        for src, (a, b) in enumerate(mapping):
             for dst in range(a, b):
+                if (src, dst) in self.predictors:
+                    continue
                 w1 = _randn((W, cfg.hidden), seed_for(cfg.name, "pred", src, dst, "w1"), self.device)
                 w2 = _randn((E, W), seed_for(cfg.name, "pred", src, dst, "w2"), self.device)
                 b1 = torch.zeros(W, device=self.device)
                 b2 = torch.zeros(E, device=self.device)
                 self.predictors[(src, dst)] = (w1, b1, w2, b2)
-                self.cache.set_predictor(src, dst, w1, b1, w2, b2)
+        return self.predictors, mapping
+
+    def install_predictors(self):
+        """Single-GPU use: the predictors run inside the context's own forward."""
+        for (src, dst), (w1, b1, w2, b2) in self.make_predictors()[0].items():
+            self.cache.set_predictor(src, dst, w1, b1, w2, b2)
 
     def host_expert(self, layer: int, expert: int):
         """The bf16 tensors of one expert as float32 CPU tensors (for the CPU baseline)."""

@@ -53,3 +53,37 @@ def test_numa_helpers():
     assert numa._cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
     assert numa._cpulist("") == set()
     assert numa.gpu_numa_node(0) is None or isinstance(numa.gpu_numa_node(0), int)  # no GPU here: None
+
+
+def test_numa_binding_with_a_fake_sysfs(tmp_path, monkeypatch):
+    """numa_node present -> that node's CPUs; numa_node -1 -> the device's local_cpulist when it is
+    a proper subset of the usable CPUs; otherwise nothing is bound and the reason is reported."""
+    import os
+    from promoe_b200 import numa
+    allowed = sorted(os.sched_getaffinity(0))
+    if len(allowed) < 2:
+        import pytest
+        pytest.skip("needs two usable CPUs")
+    bdf = "0000:1b:00.0"
+    monkeypatch.setattr(numa, "_gpu_bdf", lambda i: bdf)
+    dev = tmp_path / "bus/pci/devices" / bdf
+    dev.mkdir(parents=True)
+    node = tmp_path / "devices/system/node/node1"
+    node.mkdir(parents=True)
+    try:
+        (dev / "numa_node").write_text("1\n")
+        (node / "cpulist").write_text(f"{allowed[0]}\n")
+        r = numa.bind_to_gpu_numa_node(0, sysfs=str(tmp_path))
+        assert r == {"numa_node": 1, "bound": True, "cpus": 1, "source": "numa_node"}
+        assert os.sched_getaffinity(0) == {allowed[0]}
+        os.sched_setaffinity(0, allowed)
+        (dev / "numa_node").write_text("-1\n")
+        (dev / "local_cpulist").write_text(f"{allowed[1]}\n")
+        r = numa.bind_to_gpu_numa_node(0, sysfs=str(tmp_path))
+        assert r["bound"] and r["source"] == "local_cpulist" and os.sched_getaffinity(0) == {allowed[1]}
+        os.sched_setaffinity(0, allowed)
+        (dev / "local_cpulist").write_text(f"{allowed[0]}-{allowed[-1]}\n")
+        r = numa.bind_to_gpu_numa_node(0, sysfs=str(tmp_path))
+        assert not r["bound"] and "reason" in r and os.sched_getaffinity(0) == set(allowed)
+    finally:
+        os.sched_setaffinity(0, allowed)

@@ -1,7 +1,8 @@
-"""Expert parallelism, host logic: two gloo ranks on the CPU run ExpertParallelMoE with a test
-backend that does the arithmetic with the numpy oracle. Checked: every rank's output equals the
-single-process oracle on its tokens, and every rank's cache log equals a single cache over its
-block of experts fed with the ids that arrived (ascending, unique)."""
+"""Expert parallelism, host logic: gloo ranks on the CPU run ExpertParallelMoE with a test backend
+that restates the device kernels in numpy (message layout included). Checked: every rank's output
+equals the single-process oracle on its tokens, and every rank's cache log equals a single cache
+over its block of experts fed with the ids that arrived (ascending, unique) and with the predictor
+scores of its experts summed over all ranks' tokens."""
 import os
 import socket
 
@@ -13,71 +14,157 @@ import torch.multiprocessing as mp
 
 from oracle import moe_math as om
 from oracle import srs_policy as sp
-from promoe_b200.ep import ExpertParallelMoE, expert_bounds, split_counts
+from promoe_b200.ep import ExpertParallelMoE, Geometry, expert_bounds, split_counts
 from tests.helpers import TinyModel
 
 
 class OracleBackend:
-    """Stand-in for CudaBackend: same methods, numpy arithmetic, a python cache per rank."""
+    """Stand-in for CudaBackend: same methods, numpy arithmetic, a python cache per rank. pack and
+    unpack follow the message layout documented in promoe_b200/csrc/ep_exchange.cu."""
 
-    def __init__(self, model, rank, world, cache_rate):
-        self.model, self.layers = model, [{"shared": model.shared} for _ in range(model.L)]
-        b = expert_bounds(model.E, world)
-        self.e0, self.n_local = b[rank], b[rank + 1] - b[rank]
-        self.cache = sp.SequentialCache(model.L, self.n_local, model.k, cache_rate=cache_rate, num_predict=0)
-        self.reported = []
+    def __init__(self, model, geo: Geometry, rank, cache_rate, preds=None, n_predict=0):
+        self.model, self.geo, self.rank = model, geo, rank
+        self.e0 = geo.bounds[rank]
+        self.n_local = geo.bounds[rank + 1] - self.e0
+        self.cache = sp.SequentialCache(model.L, self.n_local, model.k, cache_rate=cache_rate, num_predict=n_predict)
+        self.reported, self.prefetched = [], []
+        self.preds = preds or {}
+        self.recv = torch.zeros((geo.rows, geo.hidden), dtype=torch.bfloat16)
+        self._b = {}
 
-    def route(self, layer, x):
+    def buffers(self, T):
+        return self._b.setdefault(T, {"reply": torch.zeros((self.geo.rows + T, self.geo.hidden), dtype=torch.float32)})
+
+    def route(self, layer, x, b):
         ids, w = self.model.canonical_routing(layer, x.float().numpy())
+        b["ids"], b["x"] = ids, x
         return torch.from_numpy(ids.astype(np.int32)), torch.from_numpy(w.astype(np.float32)), None
 
-    def permute(self, ids, num_expert):
-        c, o, rt, pos = om.permute(ids.numpy(), num_expert)
-        return torch.from_numpy(c), torch.from_numpy(o), torch.from_numpy(rt), torch.from_numpy(pos)
+    def permute(self, ids, b):
+        b["counts"], b["offsets"], b["row_token"], b["pos"] = om.permute(ids.numpy(), self.geo.num_expert)
 
-    def gather_rows(self, src, index):
-        return src[index.long()].contiguous()
+    def predict(self, layer, x):
+        dsts = sorted(d for (s, d) in self.preds if s == layer)
+        if not dsts:
+            return None, []
+        xs = x.float().numpy()
+        return np.stack([om.predictor_scores(xs, *self.preds[(layer, d)]) for d in dsts]).astype(np.float32), dsts
 
-    def expert_rows(self, layer, x_rows, row_expert):
-        ids = sorted(set(row_expert.tolist()))
+    def shared_begin(self, layer, x, b):
+        if self.model.shared is None:
+            return 0
+        s = om.swiglu_mlp(x.float().numpy(), *self.model.shared[layer], round_h_bf16=True)
+        b["reply"][self.geo.rows:] = torch.from_numpy(s.astype(np.float32))
+        return 1
+
+    def shared_end(self):
+        pass
+
+    def pack(self, x, b, scores, n_pred):
+        g = self.geo
+        send = torch.zeros((g.rows, g.hidden), dtype=torch.bfloat16)
+        raw = send.view(torch.int16).numpy()          # one row = hidden 16-bit words = hidden / 2 32-bit words
+        for r in range(g.world):
+            e0, e1 = g.bounds[r], g.bounds[r + 1]
+            hdr = np.zeros(g.hidden // 2, np.int32)
+            hdr[: e1 - e0] = b["counts"][e0:e1]
+            if n_pred:
+                sc = np.zeros((n_pred, g.max_block), np.float32)
+                sc[:, : e1 - e0] = scores[:, e0:e1]
+                hdr[g.max_block: g.max_block + n_pred * g.max_block] = sc.reshape(-1).view(np.int32)
+            raw[r * g.seg_rows] = hdr.view(np.int16)
+            start, n = b["offsets"][e0], b["offsets"][e1] - b["offsets"][e0]
+            for i in range(n):
+                send[r * g.seg_rows + 1 + i] = x[int(b["row_token"][start + i])]
+        owner = np.searchsorted(np.array([b["offsets"][e] for e in g.bounds[1:]]), b["pos"], side="right")
+        pos_reply = owner * g.seg_rows + 1 + (b["pos"] - np.array([b["offsets"][g.bounds[o]] for o in owner]))
+        return send, torch.from_numpy(pos_reply.astype(np.int32))
+
+    def unpack(self, recv, n_pred):
+        g = self.geo
+        raw = recv.view(torch.int16).numpy()
+        row_expert = np.full(g.rows, -1, np.int32)
+        sums = np.zeros((max(1, n_pred), self.n_local), np.float32)
+        for s in range(g.world):
+            hdr = np.ascontiguousarray(raw[s * g.seg_rows]).view(np.int32)
+            counts = hdr[: self.n_local]
+            row_expert[s * g.seg_rows + 1: s * g.seg_rows + 1 + counts.sum()] = np.repeat(np.arange(self.n_local), counts)
+            if n_pred:
+                sc = hdr[g.max_block: g.max_block + n_pred * g.max_block].view(np.float32).reshape(n_pred, g.max_block)
+                sums += sc[:, : self.n_local]       # rank order, float32, like the kernel
+        return torch.from_numpy(row_expert), (sums if n_pred else None)
+
+    def expert_rows(self, layer, recv, row_expert, scores_sum, dsts):
+        for i, d in enumerate(dsts):                 # prediction first, as in the single-GPU forward
+            ids = om.rank_experts(scores_sum[i], self.cache.num_predict)
+            self.prefetched.append((d, [int(v) for v in ids]))
+            self.cache.prefetch_layer(d, ids)
+        re = row_expert.numpy()
+        ids = sorted(set(int(e) for e in re if e >= 0))
         self.reported.append((layer, ids))
-        self.cache.report_layer(layer, ids)
-        out = np.zeros((x_rows.shape[0], x_rows.shape[1]), np.float32)
-        xr = x_rows.float().numpy()
+        if ids:
+            self.cache.report_layer(layer, ids)
+        out = np.zeros((recv.shape[0], recv.shape[1]), np.float32)
+        xr = recv.float().numpy()
         for e in ids:
-            sel = (row_expert == e).numpy()
+            sel = re == e
             out[sel] = om.swiglu_mlp(xr[sel], *self.model.experts[layer][self.e0 + e], round_h_bf16=True)
         return torch.from_numpy(out)
 
-    def shared_rows(self, layer, x, yexp, first_row):
-        s = self.model.shared[layer]
-        yexp[first_row:] = torch.from_numpy(om.swiglu_mlp(x.float().numpy(), *s, round_h_bf16=True).astype(np.float32))
-
-    def combine(self, yexp, pos, w, T, H, n_routed_rows, n_shared, shared_scale):
-        y = (yexp[pos.long().view(T, -1)] * w[:, :, None]).sum(1)
+    def combine(self, b, pos_reply, w, T, n_shared, shared_scale):
+        y = (b["reply"][pos_reply.long().view(T, -1)] * w[:, :, None]).sum(1)
         if n_shared:
-            y = y + yexp[n_routed_rows:]
+            y = y + b["reply"][self.geo.rows:]
         return y
 
 
-def worker(rank, world, port, seed, out_q):
+def make_preds(model, rng, D=16):
+    preds = {}
+    for src in range(model.L - 1):                  # index l predicts layer l + 1
+        w1 = om.bf16_round((rng.standard_normal((D, model.H)) * 0.1).astype(np.float32))
+        w2 = om.bf16_round((rng.standard_normal((model.E, D)) * 0.3).astype(np.float32))
+        preds[(src, src + 1)] = (w1, None, w2, None)
+    return preds
+
+
+def worker(rank, world, port, seed, with_pred, out_q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    model = TinyModel(seed=seed, L=2, E=8, H=64, I=32, k=2, shared_I=64)
-    be = OracleBackend(model, rank, world, cache_rate=0.5)
-    ep = ExpertParallelMoE(model.E, be)
+    model = TinyModel(seed=seed, L=3, E=8, H=64, I=32, k=2, shared_I=64)
+    preds = make_preds(model, np.random.default_rng(seed + 1)) if with_pred else {}
+    geo = Geometry(model.E, world, max_tokens_per_rank=3 + world, top_k=model.k, hidden=model.H, n_pred=1 if with_pred else 0)
+    be = OracleBackend(model, geo, rank, cache_rate=0.5, preds=preds, n_predict=1 if with_pred else 0)
+    ep = ExpertParallelMoE(geo, be)
     rng = np.random.default_rng(100 + rank)
-    errs = []
+    errs, all_x = [], []
     for step in range(4):
         x = om.bf16_round(rng.standard_normal((3 + rank, model.H)).astype(np.float32))
+        all_x.append(x)
         for l in range(model.L):
-            y = ep.forward(l, torch.from_numpy(x))
+            y = ep.forward(l, torch.from_numpy(x).to(torch.bfloat16))
             ref, _, _ = model.oracle_forward(l, x)
             errs.append(float(np.abs(y.numpy() - ref).max() / np.abs(ref).max()))
-    oc = sp.SequentialCache(model.L, be.n_local, model.k, cache_rate=0.5, num_predict=0)
-    for l, ids in be.reported:
-        oc.report_layer(l, ids)
-    out_q.put((rank, max(errs), be.cache.events == oc.events, len(be.cache.events), ep.bytes_dispatched))
+    # the same cache driven directly: prefetches (from the scores summed over ALL ranks' tokens), then ids
+    oc = sp.SequentialCache(model.L, be.n_local, model.k, cache_rate=0.5, num_predict=1 if with_pred else 0)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, all_x)
+    pf = iter(be.prefetched)
+    ok_scores = True
+    call = 0
+    for step in range(4):
+        for l in range(model.L):
+            for (s, d), p in sorted(preds.items()):
+                if s == l:
+                    total = sum(om.predictor_scores(gathered[r][step], *p) for r in range(world))
+                    want = [int(v) for v in om.rank_experts(total[be.e0: be.e0 + be.n_local], 1)]
+                    got_d, got = next(pf)
+                    ok_scores &= got_d == d and got == want
+                    oc.prefetch_layer(d, want)
+            lyr, ids = be.reported[call]
+            call += 1
+            if ids:
+                oc.report_layer(lyr, ids)
+    out_q.put((rank, max(errs), be.cache.events == oc.events, len(be.cache.events), ep.bytes_dispatched, ok_scores))
     dist.destroy_process_group()
 
 
@@ -87,22 +174,22 @@ def free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_two_rank_exchange_matches_single_process_oracle(world):
+@pytest.mark.parametrize("world,with_pred", [(2, False), (3, False), (2, True)])
+def test_exchange_matches_single_process_oracle(world, with_pred):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = free_port()
-    procs = [ctx.Process(target=worker, args=(r, world, port, 7, q)) for r in range(world)]
+    procs = [ctx.Process(target=worker, args=(r, world, port, 7, with_pred, q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [q.get(timeout=120) for _ in range(world)]
+    results = [q.get(timeout=180) for _ in range(world)]
     for p in procs:
         p.join(timeout=30)
         assert p.exitcode == 0
-    for rank, err, log_ok, n_events, sent in results:
+    for rank, err, log_ok, n_events, sent, ok_scores in results:
         assert err < 1e-5, f"rank {rank}: output differs from the oracle ({err})"
         assert log_ok and n_events > 0
-        assert sent > 0
+        assert sent > 0 and ok_scores
 
 
 def test_bounds_and_splits():
@@ -111,3 +198,7 @@ def test_bounds_and_splits():
     counts = torch.tensor([1, 0, 2, 3, 0, 0, 4, 1])
     assert split_counts(counts, expert_bounds(8, 2)) == [6, 5]
     assert split_counts(counts, expert_bounds(8, 1)) == [11]
+    g = Geometry(60, 8, max_tokens_per_rank=1, top_k=4, hidden=2048, n_pred=3)
+    assert (g.max_block, g.cap, g.seg_rows, g.rows) == (8, 4, 5, 40)
+    with pytest.raises(ValueError):
+        Geometry(64, 1, 1, 4, hidden=64, n_pred=3)       # 64 counts + 3 x 64 scores need 1 KiB, a row has 128 B

