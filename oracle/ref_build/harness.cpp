@@ -18,7 +18,11 @@
 //   seq <id>                             CacheMngr::set_cur_seq
 // Output (stdout): "plan <lens...>", then per decision
 //   "ev <kind> <layer> <expert> <slot> <evicted_expert> <evicted_layer>", and per layer request
-//   "order <l> <ids...>" (the list after the in-place reorder).
+//   "order <l> <ids...>" (the list after the in-place reorder). At the end, the per-forward series of
+//   the reference's TimeProfiler, "series <name> <v0> <v1> ..." for activated, hit, miss,
+//   prefetch_hit and prefetch_miss: the scheduler adds to them as it decides
+//   (prefetcher.hpp:71-78) and a new entry starts after the last layer of every iteration, as in
+//   PrefetchMngr::one_moe_layer_done (prefetcher.cpp:209-218).
 // System and torch headers first, so that the access overrides below touch only the
 // reference's own headers (whose members are otherwise private to their threads).
 #include <ATen/cuda/CUDAContext.h>
@@ -223,6 +227,7 @@ int main() {
       std::vector<int64_t> ids(n);
       for (auto& v : ids) in >> v;
       r.stats->forward();
+      r.profiler->add(TimeProfiler::kCntActivatedExpert, n);  // PrefetchMngr::report_one_layer, prefetcher.cpp:199
       PreemptTask t;
       t.layer_idx = l;
       t.expert_idxs = ids.data();
@@ -245,6 +250,12 @@ int main() {
         auto e = r.loader->get_source(l, v);
         CHECK(e->expert_status.get() == kLaunching) << "expert not launchable after its fetch";
         r.release_expert(e);
+      }
+      if (l == r.metas->num_layer - 1) {  // PrefetchMngr::one_moe_layer_done of the last layer
+        for (auto kind : {TimeProfiler::kCntActivatedExpert, TimeProfiler::kHitCnt, TimeProfiler::kMissCnt,
+                          TimeProfiler::kReadyCnt, TimeProfiler::kUnreadyCnt, TimeProfiler::kPrefetchHitCnt,
+                          TimeProfiler::kPrefetchMissCnt, TimeProfiler::kWaitTime})
+          r.profiler->push(kind, 0);
       }
     } else if (cmd == "prefetch") {
       int l, n;
@@ -279,6 +290,17 @@ int main() {
     } else {
       std::cerr << "unknown request " << cmd << "\n";
       return 2;
+    }
+  }
+  if (r.profiler) {
+    const std::pair<const char*, TimeProfiler::TimeType> kinds[] = {
+        {"activated", TimeProfiler::kCntActivatedExpert}, {"hit", TimeProfiler::kHitCnt}, {"miss", TimeProfiler::kMissCnt},
+        {"prefetch_hit", TimeProfiler::kPrefetchHitCnt}, {"prefetch_miss", TimeProfiler::kPrefetchMissCnt}};
+    for (auto& k : kinds) {
+      auto t = r.profiler->to_tensor(k.second);  // drops the open entry of the iteration in progress
+      std::cout << "series " << k.first;
+      for (int64_t i = 0; i < t.numel(); ++i) std::cout << ' ' << t[i].item<int64_t>();
+      std::cout << '\n';
     }
   }
   std::cout.flush();

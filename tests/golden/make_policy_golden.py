@@ -89,7 +89,7 @@ def run_reference(cfg: dict, L: int, E: int, n_param: int, stream, traces):
     r = subprocess.run([str(REF_BIN)], input="\n".join(lines) + "\n", capture_output=True, text=True, env=env)
     if r.returncode != 0:
         raise RuntimeError(f"reference harness failed ({r.returncode}):\n{r.stderr[-2000:]}")
-    plan, events, orders = None, [], []
+    plan, events, orders, series = None, [], [], {}
     for ln in r.stdout.splitlines():
         tok = ln.split()
         if not tok:
@@ -100,7 +100,9 @@ def run_reference(cfg: dict, L: int, E: int, n_param: int, stream, traces):
             events.append([int(v) for v in tok[1:]])
         elif tok[0] == "order":
             orders.append([int(v) for v in tok[2:]])
-    return plan, events, orders
+        elif tok[0] == "series":
+            series[tok[1]] = [int(v) for v in tok[2:]]
+    return plan, events, orders, series
 
 
 def main():
@@ -119,11 +121,12 @@ def main():
                "num_predict_expert_per_layer": n_pred, "per_layer_cache": per_layer}
         cfg.update(extra)
         # the harness issues each prefetch with min(n_predict, lines of pool 0) ids, as PredictWorker does
-        plan, events, orders = run_reference(cfg, L, E, 3, clamp_prefetch(stream, L, E, rate, per_layer, n_pred), traces)
+        plan, events, orders, series = run_reference(cfg, L, E, 3, clamp_prefetch(stream, L, E, rate, per_layer, n_pred),
+                                                     traces)
         fixture = {"name": name, "num_layer": L, "num_expert": E, "num_expert_per_token": k, "cache_rate": rate,
                    "cache_policy": policy, "num_predict": n_pred, "per_layer_cache": per_layer, "extra": extra,
                    "num_per_expert_param": 3, "stream": [[a, b, c] for a, b, c in stream], "traces": traces,
-                   "plan": plan, "events": [v for ev in events for v in ev], "orders": orders}
+                   "plan": plan, "events": [v for ev in events for v in ev], "orders": orders, "series": series}
         path = out_dir / f"policy_ref_{name}.json"
         path.write_text(json.dumps(fixture, separators=(",", ":")))
         print(f"{path.name}: {len(events)} events, {path.stat().st_size / 1024:.0f} KiB")

@@ -124,6 +124,18 @@ def run_product(stream, num_layer, num_expert, num_expert_per_token, cache_rate=
         events = [(e.kind, e.layer, e.expert, e.slot, e.evicted, e.evicted_layer) for e in evs[: n.value]]
         stats = _lib.pm_stats()
         _lib.call("pm_stats_read", ctx, C.byref(stats))
+        _lib.call("pm_iter_marks_read", ctx, None, 0, C.byref(n))
+        marks = (_lib.pm_stats * max(1, n.value))()
+        _lib.call("pm_iter_marks_read", ctx, marks, n.value, C.byref(n))
+        series = {name: [] for name in ("activated", "hit", "miss", "prefetch_hit", "prefetch_miss")}
+        prev = dict.fromkeys(series, 0)
+        for m in marks[: n.value]:   # per-forward values = differences of the end-of-iteration snapshots
+            now = {"activated": m.activated_experts, "hit": m.precise_hit, "miss": m.precise_miss,
+                   "prefetch_hit": m.prefetch_hit, "prefetch_miss": m.prefetch_miss}
+            for k in series:
+                series[k].append(now[k] - prev[k])
+            prev = now
+        stats.series = series
         return events, out_orders, stats
     finally:
         _lib.call("pm_ctx_destroy", ctx)

@@ -52,6 +52,8 @@ def test_product_reproduces_reference(lib, path):
     kinds = [e[0] for e in ref_events]
     assert (stats.precise_hit, stats.precise_miss, stats.prefetch_hit, stats.prefetch_miss) == tuple(
         kinds.count(k) for k in range(4))
+    # the per-forward series the reference's own TimeProfiler recorded for the same requests
+    assert stats.series == fx["series"]
 
 
 def test_heap_remove_never_sifts_up():
