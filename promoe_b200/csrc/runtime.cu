@@ -937,6 +937,15 @@ int rt_temp_move(pm_ctx* c, int layer, int expert, bool to_gpu, cudaStream_t s, 
 int rt_report_hidden(pm_ctx* c, int index, const void* hidden, int B, int seq, cudaStream_t s) {
   if (index < 0 || index > c->cfg.num_layer) return fail(PM_ERR_INVALID, "hidden-state index out of range");
   if (seq != 1 || B <= 0) return PM_OK;  // prefill or empty: nothing is captured (predictor.cpp:657-661)
+  {
+    // nothing to run for this index (no predictor registered, or prediction off): not an error, the
+    // hook reports every layer's hidden states whether or not a predictor exists
+    const int L = c->cfg.num_layer;
+    bool any = false;
+    if (c->cfg.predict_input_mode == "moe_layer_logits" && c->cfg.num_predict_expert_per_layer > 0)
+      for (int dst = 0; dst < L && !any; ++dst) any = c->predictors[(size_t)index * L + dst].w1 != nullptr;
+    if (!any) return PM_OK;
+  }
   if (!c->slab_built) return fail(PM_ERR_STATE, "report_hidden before build_slab");
   int H = 0;
   for (auto& l : c->layers)

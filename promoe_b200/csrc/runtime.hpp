@@ -53,6 +53,8 @@ struct pm_ctx {
   CUmemAllocationProp line_prop{};
 
   // ---- streams and events -------------------------------------------------------------
+  // One copy stream: back-to-back expert copies on it already run at the link's rate (alternating
+  // two streams measured the same 51.4 GB/s against 52.4 GB/s for bare pinned copies).
   cudaStream_t copy_stream = nullptr;
   cudaStream_t last_stream = nullptr;
   bool have_last_stream = false;

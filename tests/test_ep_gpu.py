@@ -35,9 +35,10 @@ def test_pack_and_unpack_kernels_follow_the_message_layout(lib):
     pos_reply = torch.full((ids.size,), -7, dtype=torch.int32, device="cuda")
     bounds = dev(np.array(geo.bounds, np.int32))
     keep = [dev(b[n].astype(np.int32)) for n in ("counts", "offsets", "row_token", "pos")]
-    _lib.call("pm_k_ep_pack", dev_bf16(x).data_ptr(), geo.hidden, keep[0].data_ptr(), keep[1].data_ptr(),
+    xd, scores_d = dev_bf16(x), dev(scores)          # held in variables: the kernel reads them after the call returns
+    _lib.call("pm_k_ep_pack", xd.data_ptr(), geo.hidden, keep[0].data_ptr(), keep[1].data_ptr(),
               keep[2].data_ptr(), keep[3].data_ptr(), ids.size, bounds.data_ptr(), 3, geo.max_block, geo.cap,
-              dev(scores).data_ptr(), 2, model.E, send.data_ptr(), pos_reply.data_ptr(), None)
+              scores_d.data_ptr(), 2, model.E, send.data_ptr(), pos_reply.data_ptr(), None)
     torch.cuda.synchronize()
     np.testing.assert_array_equal(pos_reply.cpu().numpy(), want_pos.numpy())
     got, want = send.cpu().view(torch.int16).numpy(), want_send.view(torch.int16).numpy()
@@ -60,7 +61,8 @@ def test_pack_and_unpack_kernels_follow_the_message_layout(lib):
     row_expert = torch.full((geo.rows,), 99, dtype=torch.int32, device="cuda")
     sums = torch.zeros((2, ob.n_local), dtype=torch.float32, device="cuda")
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
-    _lib.call("pm_k_ep_unpack", recv.cuda().data_ptr(), geo.hidden, 3, ob.n_local, geo.max_block, geo.cap, 2,
+    recv_d = recv.cuda()
+    _lib.call("pm_k_ep_unpack", recv_d.data_ptr(), geo.hidden, 3, ob.n_local, geo.max_block, geo.cap, 2,
               row_expert.data_ptr(), sums.data_ptr(), err.data_ptr(), None)
     torch.cuda.synchronize()
     np.testing.assert_array_equal(row_expert.cpu().numpy(), want_re.numpy())
@@ -69,7 +71,8 @@ def test_pack_and_unpack_kernels_follow_the_message_layout(lib):
     # a header whose counts exceed the capacity voids its segment and raises the flag
     bad = recv.clone()
     bad.view(torch.int16).numpy().view(np.int32)[0, 0] = 1000
-    _lib.call("pm_k_ep_unpack", bad.cuda().data_ptr(), geo.hidden, 3, ob.n_local, geo.max_block, geo.cap, 2,
+    bad_d = bad.cuda()
+    _lib.call("pm_k_ep_unpack", bad_d.data_ptr(), geo.hidden, 3, ob.n_local, geo.max_block, geo.cap, 2,
               row_expert.data_ptr(), sums.data_ptr(), err.data_ptr(), None)
     torch.cuda.synchronize()
     assert int(err.item()) == 1 and (row_expert.cpu().numpy()[: geo.seg_rows] == -1).all()

@@ -208,13 +208,19 @@ def test_routed_rows_reject_an_expert_id_out_of_range(lib):
     out = torch.full((4, 128), float("nan"), dtype=torch.float32, device="cuda")
     bad = torch.tensor([0, 3, 8, 1], dtype=torch.int32, device="cuda")
     with pytest.raises(_lib.PromoeError) as e:
-        _lib.call("pm_moe_forward_routed", cache.handle, 0, xd.data_ptr(), 4, bad.data_ptr(), out.data_ptr(), None)
+        _lib.call("pm_moe_forward_routed", cache.handle, 0, xd.data_ptr(), 4, bad.data_ptr(), out.data_ptr(), 0, None,
+                  None, 0, None)
     assert "expert id" in str(e.value)
-    good = torch.tensor([0, 3, 7, 1], dtype=torch.int32, device="cuda")
-    _lib.call("pm_moe_forward_routed", cache.handle, 0, xd.data_ptr(), 4, good.data_ptr(), out.data_ptr(), None)
+    # -1 marks a padding row: no expert runs on it and its output row is zeros
+    good = torch.tensor([0, 3, -1, 1], dtype=torch.int32, device="cuda")
+    _lib.call("pm_moe_forward_routed", cache.handle, 0, xd.data_ptr(), 4, good.data_ptr(), out.data_ptr(), 4, None,
+              None, 0, None)
     torch.cuda.synchronize()
     got = out.cpu().numpy()
-    for r, e_id in enumerate([0, 3, 7, 1]):
+    for r, e_id in enumerate([0, 3, -1, 1]):
+        if e_id < 0:
+            assert (got[r] == 0).all()
+            continue
         ref = om.swiglu_mlp(x[r:r + 1], *model.experts[0][e_id], round_h_bf16=True)
         np.testing.assert_allclose(got[r:r + 1], ref, rtol=RTOL, atol=RTOL * np.abs(ref).max() * 0.25)
     cache.close()
