@@ -45,6 +45,8 @@ def parse_args():
     ap.add_argument("--profile-steps", type=int, default=16,
                     help="steps of the separate profiled pass that gives the roofline figures")
     ap.add_argument("--no-ep-parity", action="store_true", help="skip the untimed parity step of multi-GPU runs")
+    ap.add_argument("--no-pool", action="store_true",
+                    help="multi-GPU: every rank fetches its missing experts over its own host link only")
     return ap.parse_args()
 
 
@@ -358,7 +360,9 @@ def run_ours(args, cfg):
         bnd = expert_bounds(cfg.num_expert, world)
         n_local = bnd[rank + 1] - bnd[rank]
         n_local_pred = max(1, round(num_predict * n_local / cfg.num_expert)) if use_pred else 0
-        stack = synth.SyntheticStack(cfg, dev, expert_range=(bnd[rank], n_local), num_predict_expert_per_layer=n_local_pred)
+        pool_tag = None if args.no_pool else f"b{os.environ.get('MASTER_PORT', '0')}"
+        stack = synth.SyntheticStack(cfg, dev, expert_range=(bnd[rank], n_local), num_predict_expert_per_layer=n_local_pred,
+                                     shared_arena=None if pool_tag is None else f"/pm_{pool_tag}_{rank}")
         stack.install_routed_only()
         if use_pred:
             preds, pmap = stack.make_predictors()
@@ -366,6 +370,9 @@ def run_ours(args, cfg):
         geo = Geometry(cfg.num_expert, world, B, cfg.top_k, H, n_pred=n_pred)
         be = CudaBackend(stack.cache, stack.ep_layers(), dev, geo, rank, predictors=preds, predict_map=pmap,
                          global_tokens=cfg.batch)
+        if pool_tag is not None:
+            be.enable_pool([f"/pm_{pool_tag}_{r}" for r in range(world)], [bnd[r + 1] - bnd[r] for r in range(world)],
+                           f"/pm_{pool_tag}_mail")
         ep = ExpertParallelMoE(geo, be)
     else:
         stack = synth.SyntheticStack(cfg, dev, num_predict_expert_per_layer=num_predict,
@@ -520,6 +527,12 @@ def run_ours(args, cfg):
     }
     if per_rank_h2d is not None:
         line["cache"]["h2d_gbs_per_rank"] = per_rank_h2d
+    if be is not None:
+        line["cache"]["pooled_miss_fetch"] = (
+            {"on": True, "exchanges": be.pool["exchanges"], "local_fallbacks": be.pool["local_fallbacks"],
+             "note": "every rank pulls 1/n_gpus of each missing expert over its own host link; the slices meet at the "
+                     "owner over NVLink (one all-to-all per layer call that has misses)"}
+            if be.pool is not None else {"on": False})
     if ep_parity is not None:
         line["ep_parity"] = ep_parity
     if breakdown is not None:

@@ -223,6 +223,42 @@ int pm_moe_forward(pm_ctx* ctx, int layer, const void* x_dev, int T, void* y_dev
 int pm_moe_forward_routed(pm_ctx* ctx, int layer, const void* x_rows, int n_rows, const int32_t* row_expert,
                           float* rows_out, int max_rows_per_expert, const float* pred_scores,
                           const int32_t* pred_layers, int n_pred, void* stream);
+/* ---- pooled miss fetch for expert-parallel ranks of one node (no counterpart in the reference,
+ *      which is single-GPU) -------------------------------------------------------------------
+ * A layer call of an expert-parallel stack ends when the rank with the most missing experts has
+ * them, and each rank's misses arrive over that rank's host link alone. With the pool every rank
+ * pulls 1/world of every missing record over ITS link and the slices meet at the owner over
+ * NVLink, so a layer call costs the node's total miss bytes over all links. Cache decisions are
+ * the same as without it. Set-up: context option shared_arena=<name> before pm_pin_all (the
+ * pinned records then live in POSIX shared memory "<name>_L<layer>"), pm_pool_init on every rank
+ * with one mailbox name, then, after every rank has pinned, pm_pool_open_peer for every other rank.
+ * Per layer call on every rank, in this order:
+ *   pm_moe_forward_routed_begin  as pm_moe_forward_routed, but the copies of missing activated
+ *                                experts are not enqueued: their local expert ids come back in
+ *                                miss_experts (n_miss <= miss_cap; if there are more, the rank
+ *                                copies them itself and reports 0)
+ *   pm_pool_exchange             host-to-host exchange of the miss lists; lists_out is int32
+ *                                [world][1 + 64]: count, then ids; waits at most timeout_s per peer
+ *   pm_pool_stage                this rank's slice of every listed record, host to device into
+ *                                send_dev, grouped by owner; returns the all-to-all's byte splits
+ *   (the caller's all-to-all of send_dev into recv_dev with those splits, on `stream`)
+ *   pm_pool_scatter              slices of this rank's records from recv_dev into their cache
+ *                                lines; records the lines' ready events
+ *   pm_moe_forward_routed_end    the launches that waited for those lines, then the output rows
+ * pm_pool_fetch_locally makes this rank copy its collected misses itself (when the ranks agree
+ * that an exchange does not fit the buffers). */
+int pm_moe_forward_routed_begin(pm_ctx* ctx, int layer, const void* x_rows, int n_rows, const int32_t* row_expert,
+                                float* rows_out, int max_rows_per_expert, const float* pred_scores,
+                                const int32_t* pred_layers, int n_pred, void* stream, int32_t* miss_experts,
+                                int miss_cap, int* n_miss);
+int pm_moe_forward_routed_end(pm_ctx* ctx);
+int pm_pool_init(pm_ctx* ctx, int rank, int world, const char* mailbox_name);
+int pm_pool_open_peer(pm_ctx* ctx, int peer, const char* arena_prefix, int peer_num_expert);
+int pm_pool_exchange(pm_ctx* ctx, int64_t seq, const int32_t* experts, int n, int32_t* lists_out, double timeout_s);
+int pm_pool_stage(pm_ctx* ctx, int layer, const int32_t* lists, void* send_dev, size_t send_cap, size_t recv_cap,
+                  int64_t* send_split, int64_t* recv_split, void* stream);
+int pm_pool_scatter(pm_ctx* ctx, const void* recv_dev, void* stream);
+int pm_pool_fetch_locally(pm_ctx* ctx);
 /* Same with host buffers (pinned or pageable): copies x in and y out on the stream and waits. */
 int pm_moe_forward_host(pm_ctx* ctx, int layer, const void* x_host, int T, void* y_host, void* stream);
 /* Routing of the most recent pm_moe_forward on `layer` (host copies): ids/weights [T, k]. */

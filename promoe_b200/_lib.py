@@ -95,6 +95,15 @@ SIGNATURES = {
     "pm_layer_set_weights": (_i, [_vp, _i, C.POINTER(pm_layer_weights)]),
     "pm_moe_forward": (_i, [_vp, _i, _vp, _i, _vp, _vp]),
     "pm_moe_forward_routed": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _vp]),
+    "pm_moe_forward_routed_begin": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _vp, C.POINTER(C.c_int32), _i,
+                                         C.POINTER(_i)]),
+    "pm_moe_forward_routed_end": (_i, [_vp]),
+    "pm_pool_init": (_i, [_vp, _i, _i, _cp]),
+    "pm_pool_open_peer": (_i, [_vp, _i, _cp, _i]),
+    "pm_pool_exchange": (_i, [_vp, _i64, C.POINTER(C.c_int32), _i, C.POINTER(C.c_int32), C.c_double]),
+    "pm_pool_stage": (_i, [_vp, _i, C.POINTER(C.c_int32), _vp, _sz, _sz, C.POINTER(_i64), C.POINTER(_i64), _vp]),
+    "pm_pool_scatter": (_i, [_vp, _vp, _vp]),
+    "pm_pool_fetch_locally": (_i, [_vp]),
     "pm_moe_forward_host": (_i, [_vp, _i, _vp, _i, _vp, _vp]),
     "pm_last_routing": (_i, [_vp, _i, C.POINTER(C.c_int32), C.POINTER(_f), _i]),
     "pm_predictor_set": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp]),

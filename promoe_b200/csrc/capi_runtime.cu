@@ -85,6 +85,9 @@ int pm_ctx_get(pm_ctx* ctx, const char* key, char* buf, size_t cap) {
   else if (k == "slab_impl") v = !ctx->slab_built ? "none" : (ctx->slab_vmm ? "vmm" : "cudamalloc");
   else if (k == "line_stride") v = std::to_string(ctx->line_stride);
   else if (k == "stable_va") v = ctx->stable_va ? "true" : "false";
+  else if (k == "shared_arena") v = ctx->shared_prefix;
+  else if (k == "pool_slice") v = std::to_string(ctx->pool_slice);
+  else if (k == "pool_bytes_pulled") v = std::to_string(ctx->pool_bytes_pulled);
   else if (k == "expert_va_base") v = std::to_string((unsigned long long)(uintptr_t)ctx->expert_va);
   else if (k == "slab_base") v = std::to_string((unsigned long long)(uintptr_t)ctx->slab);
   else if (k == "slab_bytes") v = std::to_string((unsigned long long)ctx->line_stride * (ctx->n_lines + 1));
@@ -110,6 +113,11 @@ int pm_ctx_set(pm_ctx* ctx, const char* key, const char* value) {
   }
   if (k == "tc_prefill") {
     ctx->tc_prefill = (v == "1" || v == "true" || v == "True" || v == "on");
+    return PM_OK;
+  }
+  if (k == "shared_arena") {
+    if (ctx->pinned) return fail(PM_ERR_STATE, "shared_arena must be set before pin_all");
+    ctx->shared_prefix = v;
     return PM_OK;
   }
   if (k == "stable_va") {
@@ -446,6 +454,75 @@ int pm_moe_forward_routed(pm_ctx* ctx, int layer, const void* x_rows, int n_rows
   r.pred_layers = pred_layers;
   r.n_pred = n_pred;
   return rt_forward(ctx, layer, x_rows, n_rows, nullptr, (cudaStream_t)stream, &r);
+}
+
+int pm_moe_forward_routed_begin(pm_ctx* ctx, int layer, const void* x_rows, int n_rows, const int32_t* row_expert,
+                                float* rows_out, int max_rows_per_expert, const float* pred_scores,
+                                const int32_t* pred_layers, int n_pred, void* stream, int32_t* miss_experts,
+                                int miss_cap, int* n_miss) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  if (n_pred < 0 || (n_pred > 0 && (!pred_scores || !pred_layers))) return fail(PM_ERR_INVALID, "bad prediction arguments");
+  if (!n_miss || (miss_cap > 0 && !miss_experts)) return fail(PM_ERR_INVALID, "null miss list");
+  *n_miss = 0;
+  RoutedRows r;
+  r.row_expert = row_expert;
+  r.rows_out = rows_out;
+  r.max_rows_per_expert = max_rows_per_expert;
+  r.pred_scores = pred_scores;
+  r.pred_layers = pred_layers;
+  r.n_pred = n_pred;
+  r.collect_demand_copies = true;
+  int rc = rt_forward(ctx, layer, x_rows, n_rows, nullptr, (cudaStream_t)stream, &r);
+  if (rc != PM_OK) return rc;
+  const std::vector<Action>& pooled = rt_pending_pooled(ctx);
+  if ((int)pooled.size() > miss_cap || pooled.size() > (size_t)kPoolMaxMiss) {
+    rc = rt_pool_fetch_locally(ctx);  // more than the exchange can carry: this rank copies them itself
+    return rc;
+  }
+  for (size_t i = 0; i < pooled.size(); ++i) miss_experts[i] = pooled[i].expert;
+  *n_miss = (int)pooled.size();
+  return PM_OK;
+}
+
+int pm_moe_forward_routed_end(pm_ctx* ctx) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  return rt_forward_end(ctx);
+}
+
+int pm_pool_init(pm_ctx* ctx, int rank, int world, const char* mailbox_name) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  if (!mailbox_name) return fail(PM_ERR_INVALID, "null mailbox name");
+  return rt_pool_init(ctx, rank, world, mailbox_name);
+}
+
+int pm_pool_open_peer(pm_ctx* ctx, int peer, const char* arena_prefix, int peer_num_expert) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  if (!arena_prefix) return fail(PM_ERR_INVALID, "null arena prefix");
+  return rt_pool_open_peer(ctx, peer, arena_prefix, peer_num_expert);
+}
+
+int pm_pool_exchange(pm_ctx* ctx, int64_t seq, const int32_t* experts, int n, int32_t* lists_out, double timeout_s) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  if ((n > 0 && !experts) || !lists_out) return fail(PM_ERR_INVALID, "null list");
+  return rt_pool_exchange(ctx, seq, experts, n, lists_out, timeout_s);
+}
+
+int pm_pool_stage(pm_ctx* ctx, int layer, const int32_t* lists, void* send_dev, size_t send_cap, size_t recv_cap,
+                  int64_t* send_split, int64_t* recv_split, void* stream) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  if (!lists || !send_dev || !send_split || !recv_split) return fail(PM_ERR_INVALID, "null argument");
+  return rt_pool_stage(ctx, layer, lists, send_dev, send_cap, recv_cap, send_split, recv_split, (cudaStream_t)stream);
+}
+
+int pm_pool_scatter(pm_ctx* ctx, const void* recv_dev, void* stream) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  if (!recv_dev) return fail(PM_ERR_INVALID, "null receive buffer");
+  return rt_pool_scatter(ctx, recv_dev, (cudaStream_t)stream);
+}
+
+int pm_pool_fetch_locally(pm_ctx* ctx) {
+  if (need(ctx)) return PM_ERR_INVALID;
+  return rt_pool_fetch_locally(ctx);
 }
 
 int pm_moe_forward_host(pm_ctx* ctx, int layer, const void* x_host, int T, void* y_host, void* stream) {

@@ -96,8 +96,11 @@ int enqueue_copy(pm_ctx* c, const Action& a) {
     if (rc != PM_OK) return rc;
   }
   const size_t b0 = c->param_offset[a.chunk_begin], b1 = c->param_offset[a.chunk_end];
-  cudaStream_t cs = c->cfg.cache_only ? c->last_stream : c->copy_stream;
+  cudaStream_t cs = c->cfg.cache_only ? c->last_stream : (a.precise ? c->copy_stream : c->prefetch_stream);
   if (c->line_read[a.line] != nullptr) PM_CUDA(cudaStreamWaitEvent(cs, c->line_read[a.line], 0));
+  if (c->line_copy_stream[a.line] != nullptr && c->line_copy_stream[a.line] != cs)
+    PM_CUDA(cudaStreamWaitEvent(cs, c->line_ready[a.line], 0));  // behind the previous copy into this line
+  c->line_copy_stream[a.line] = cs;
   PM_CUDA(cudaMemcpyAsync(line_ptr(c, a.line) + b0, c->host_rec[f] + b0, b1 - b0, cudaMemcpyHostToDevice, cs));
   PM_CUDA(cudaEventRecord(c->line_ready[a.line], cs));
   c->line_pending[a.line] = 1;
@@ -340,7 +343,13 @@ int rt_pin_all(pm_ctx* c) {
   c->host_rec.assign((size_t)L * E, nullptr);
   for (int l = 0; l < L; ++l) {
     void* block = nullptr;
-    PM_CUDA(cudaHostAlloc(&block, rec * E, cudaHostAllocDefault));
+    if (!c->shared_prefix.empty()) {  // shared memory that other ranks of the node can map and register too
+      std::string err;
+      block = rt_shared_block(c, c->shared_prefix + "_L" + std::to_string(l), rec * E, true, &err);
+      if (block == nullptr) return fail(PM_ERR_STATE, err);
+    } else {
+      PM_CUDA(cudaHostAlloc(&block, rec * E, cudaHostAllocDefault));
+    }
     c->arena_blocks.push_back(block);
     for (int e = 0; e < E; ++e) {
       unsigned char* dst = (unsigned char*)block + rec * e;
@@ -418,7 +427,11 @@ int rt_build_slab(pm_ctx* c) {
   }
   c->n_lines = n_policy_lines;
   // cache_only: copies run on the caller's compute stream (src/cpp_worker/prefetcher.cpp:420-424)
-  if (!c->cfg.cache_only) PM_CUDA(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+  if (!c->cfg.cache_only) {
+    PM_CUDA(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+    PM_CUDA(cudaStreamCreateWithFlags(&c->prefetch_stream, cudaStreamNonBlocking));
+  }
+  c->line_copy_stream.assign(n_lines, nullptr);
   c->line_ready.resize(n_lines);
   for (auto& e : c->line_ready) PM_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   c->line_read.assign(n_lines, nullptr);
@@ -449,6 +462,36 @@ struct Segment {
   bool has_line(int line) const { return std::find(lines.begin(), lines.end(), line) != lines.end(); }
   bool empty() const { return groups.empty(); }
 };
+
+}  // namespace
+
+// The part of a layer call that follows the cache decisions: the ordered actions (copy an expert into
+// a line, use an expert from a line), the launch being assembled, and where the walk over the
+// actions stands. A call made through pm_moe_forward_routed_begin can stop here, hand the demand
+// copies it has collected to the caller (who fetches them over all ranks' host links) and go on in
+// pm_moe_forward_routed_end once the data is in the lines.
+struct PendingForward {
+  bool active = false;
+  int layer = 0, T = 0, R = 0, n_shared = 0, k = 1, H = 0;
+  bool spec = false, is_routed = false;
+  pm_layer_weights w{};
+  const __nv_bfloat16* x = nullptr;
+  void* yv = nullptr;
+  float* rows_out = nullptr;
+  cudaStream_t s = nullptr;
+  std::vector<Action> acts;
+  size_t next = 0;
+  std::vector<int64_t> ids;
+  std::vector<int32_t> counts, offsets;
+  std::vector<int> resident_line;
+  Segment seg;
+  size_t desc_used = 0;
+  std::vector<Action> pooled;       // demand copies left to the caller
+  std::vector<char> line_is_pooled;  // per cache line: its copy is among `pooled`
+  bool seg_waits_for_pooled = false;
+};
+
+namespace {
 
 // Prefill-size segment on the tcgen05 path: gather the token rows once per layer call, plan the
 // 128 x 128 tiles, upload groups and tiles, launch the gate/up and the down kernel.
@@ -589,9 +632,103 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
 
 }  // namespace
 
+namespace {
+
+pm_ffn_group group_of_line(pm_ctx* c, const PendingForward& p, int e, int line) {
+  const unsigned char* base = line_ptr(c, line);
+  pm_ffn_group g{};
+  g.w_gate = base + c->param_offset[c->role_gate];
+  g.w_up = base + c->param_offset[c->role_up];
+  g.w_down = base + c->param_offset[c->role_down];
+  if (p.w.quant4) {
+    g.q_gate = base + c->param_offset[c->role_qgate];
+    g.q_up = base + c->param_offset[c->role_qup];
+    g.q_down = base + c->param_offset[c->role_qdown];
+  }
+  g.row_start = p.offsets[e];
+  g.row_count = p.counts[e];
+  g.inter = p.w.inter;
+  return g;
+}
+
+// Walks the actions from p.next on. With `collect`, full-record demand copies are not enqueued but
+// collected in p.pooled (their lines are marked pending, so the launches that read them wait for
+// the lines' ready events, which the caller's fetch records). The walk stops (*stopped = true)
+// where a launch would have to be enqueued that waits for a collected copy; the caller resumes it
+// with collect = false once those events have been recorded.
+int run_actions(pm_ctx* c, PendingForward& p, bool collect, bool* stopped) {
+  const int n_rows = p.R + p.n_shared * p.T;
+  const int N = c->cfg.num_per_expert_param();
+  cudaStream_t s = p.s;
+  *stopped = false;
+  for (; p.next < p.acts.size(); ++p.next) {
+    const Action& a = p.acts[p.next];
+    if (a.type == Action::kCopy) {
+      if (p.seg.has_line(a.line)) {  // the victim is still waiting to run in the open segment
+        if (collect && p.seg_waits_for_pooled) {
+          *stopped = true;
+          return PM_OK;
+        }
+        int rc = flush_segment(c, &p.seg, p.w, p.x, n_rows, &p.desc_used, s);
+        if (rc != PM_OK) return rc;
+        p.seg_waits_for_pooled = false;
+      }
+      if (collect && a.precise && a.chunk_begin == 0 && a.chunk_end == N && !c->stable_va) {
+        p.pooled.push_back(a);
+        p.line_is_pooled[a.line] = 1;
+        c->line_pending[a.line] = 1;
+        c->line_waiter[a.line] = nullptr;
+        c->h2d_bytes += (int64_t)c->param_offset[N];
+        c->h2d_copies += 1;
+      } else {
+        int rc = enqueue_copy(c, a);
+        if (rc != PM_OK) return rc;
+      }
+    } else {
+      // Already computed by the device-planned launch from the line it occupied at that time.
+      if (p.spec && p.resident_line[a.expert] >= 0) continue;
+      const bool must_wait = c->line_pending[a.line] || (c->line_waiter[a.line] != nullptr && c->line_waiter[a.line] != s);
+      if (must_wait && p.seg.waits.empty() && !p.seg.empty()) {
+        // let everything that is already resident run while the copies are in flight
+        int rc = flush_segment(c, &p.seg, p.w, p.x, n_rows, &p.desc_used, s);
+        if (rc != PM_OK) return rc;
+      }
+      p.seg.groups.push_back(group_of_line(c, p, a.expert, a.line));
+      p.seg.group_line.push_back(a.line);
+      p.seg.lines.push_back(a.line);
+      if (must_wait) {
+        p.seg.waits.push_back(a.line);
+        if (p.line_is_pooled[a.line]) p.seg_waits_for_pooled = true;
+      }
+    }
+  }
+  if (collect && p.seg_waits_for_pooled) {
+    *stopped = true;
+    return PM_OK;
+  }
+  return flush_segment(c, &p.seg, p.w, p.x, n_rows, &p.desc_used, s);
+}
+
+int finish_forward(pm_ctx* c, PendingForward& p) {
+  if (p.is_routed) {
+    PM_CUDA(launch_gather_rows(c->d_yexp, c->d_pos, p.T, (size_t)p.H * 4, p.rows_out, p.s));
+  } else {
+    PM_CUDA(launch_combine(c->d_yexp, c->d_pos, c->d_topk_w, p.T, p.H, p.k, p.R, p.n_shared,
+                           p.w.shared_gate_w ? c->d_shared_scale : nullptr, (__nv_bfloat16*)p.yv, p.s));
+  }
+  c->kernel_launches += 1;
+  for (int64_t id : p.ids) c->eng->expert_done(p.layer, (int)id);
+  c->eng->layer_done(p.layer);
+  return PM_OK;
+}
+
+}  // namespace
+
 int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream_t s, const RoutedRows* routed) {
   if (!c->slab_built) return fail(PM_ERR_STATE, "moe_forward before build_slab");
   if (layer < 0 || layer >= c->cfg.num_layer) return fail(PM_ERR_INVALID, "layer out of range");
+  if (!c->pending) c->pending = new PendingForward();
+  if (c->pending->active) return fail(PM_ERR_STATE, "a layer call begun with pm_moe_forward_routed_begin has not been ended");
   pm_ctx::Layer& ly = c->layers[layer];
   if (!ly.set) return fail(PM_ERR_STATE, "moe_forward before layer_set_weights");
   if (T < 0) return fail(PM_ERR_INVALID, "negative token count");
@@ -778,23 +915,6 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
   }
   rt_mark_dirty(c, acts);
 
-  auto group_of = [&](int e, int line) {
-    const unsigned char* base = line_ptr(c, line);
-    pm_ffn_group g{};
-    g.w_gate = base + c->param_offset[c->role_gate];
-    g.w_up = base + c->param_offset[c->role_up];
-    g.w_down = base + c->param_offset[c->role_down];
-    if (w.quant4) {
-      g.q_gate = base + c->param_offset[c->role_qgate];
-      g.q_up = base + c->param_offset[c->role_qup];
-      g.q_down = base + c->param_offset[c->role_qdown];
-    }
-    g.row_start = offsets[e];
-    g.row_count = counts[e];
-    g.inter = w.inter;
-    return g;
-  };
-
   if (spec && c->profile_ffn) {  // weight bytes the device-planned launch read: shared + activated residents
     const int64_t routed = (int64_t)w.inter * H * 2, sh = (int64_t)w.shared_inter * H * 2;
     int64_t n_res = 0;
@@ -805,8 +925,17 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
     c->ffn_samples.push_back(spec_sample);
   }
 
-  Segment seg;
-  size_t desc_used = 0;
+  PendingForward& p = *c->pending;
+  p = PendingForward();
+  p.layer = layer; p.T = T; p.R = R; p.n_shared = n_shared; p.k = k; p.H = H;
+  p.spec = spec; p.is_routed = routed != nullptr;
+  p.w = w; p.x = x; p.yv = yv; p.rows_out = routed ? routed->rows_out : nullptr; p.s = s;
+  p.acts = std::move(acts);
+  p.ids = ids;
+  p.counts.assign(counts, counts + E);
+  p.offsets.assign(offsets, offsets + E + 1);
+  p.resident_line = resident_line;
+  p.line_is_pooled.assign(c->line_pending.size(), 0);
   if (n_shared && !spec) {
     const int slice = sliced ? shared_slice_width(w.inter, w.shared_inter) : w.shared_inter;
     for (int j = 0; j < n_shared; ++j) {
@@ -818,47 +947,36 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
       g.row_count = T;
       g.inter = std::min(slice, w.shared_inter - j * slice);
       g.ld_down = w.shared_inter;
-      seg.groups.push_back(g);
-      seg.group_line.push_back(-1);
+      p.seg.groups.push_back(g);
+      p.seg.group_line.push_back(-1);
     }
   }
-  for (const Action& a : acts) {
-    if (a.type == Action::kCopy) {
-      if (seg.has_line(a.line)) {  // the victim is still waiting to run in the open segment
-        rc = flush_segment(c, &seg, w, x, R + n_shared * T, &desc_used, s);
-        if (rc != PM_OK) return rc;
-      }
-      rc = enqueue_copy(c, a);
-      if (rc != PM_OK) return rc;
-    } else {
-      // Already computed by the device-planned launch from the line it occupied at that time.
-      if (spec && resident_line[a.expert] >= 0) continue;
-      const bool must_wait = c->line_pending[a.line] || (c->line_waiter[a.line] != nullptr && c->line_waiter[a.line] != s);
-      if (must_wait && seg.waits.empty() && !seg.empty()) {
-        // let everything that is already resident run while the copies are in flight
-        rc = flush_segment(c, &seg, w, x, R + n_shared * T, &desc_used, s);
-        if (rc != PM_OK) return rc;
-      }
-      seg.groups.push_back(group_of(a.expert, a.line));
-      seg.group_line.push_back(a.line);
-      seg.lines.push_back(a.line);
-      if (must_wait) seg.waits.push_back(a.line);
-    }
-  }
-  rc = flush_segment(c, &seg, w, x, R + n_shared * T, &desc_used, s);
+  const bool collect = routed != nullptr && routed->collect_demand_copies && !c->cfg.cache_only;
+  bool stopped = false;
+  rc = run_actions(c, p, collect, &stopped);
   if (rc != PM_OK) return rc;
-
-  if (routed) {
-    PM_CUDA(launch_gather_rows(c->d_yexp, c->d_pos, T, (size_t)H * 4, routed->rows_out, s));
-  } else {
-    PM_CUDA(launch_combine(c->d_yexp, c->d_pos, c->d_topk_w, T, H, k, R, n_shared,
-                           w.shared_gate_w ? c->d_shared_scale : nullptr, (__nv_bfloat16*)yv, s));
+  if (stopped) {  // the caller fetches p.pooled, then calls rt_forward_end
+    p.active = true;
+    return PM_OK;
   }
-  c->kernel_launches += 1;
-  for (int64_t id : ids) c->eng->expert_done(layer, (int)id);
-  c->eng->layer_done(layer);
   (void)N;
-  return PM_OK;
+  return finish_forward(c, p);
+}
+
+int rt_forward_end(pm_ctx* c) {
+  if (!c->pending || !c->pending->active) return PM_OK;  // the begin call had nothing left to do
+  PendingForward& p = *c->pending;
+  if (!p.active) return PM_OK;  // the begin call had nothing left to do
+  p.active = false;
+  bool stopped = false;
+  int rc = run_actions(c, p, false, &stopped);
+  if (rc != PM_OK) return rc;
+  return finish_forward(c, p);
+}
+
+const std::vector<Action>& rt_pending_pooled(pm_ctx* c) {
+  static const std::vector<Action> none;
+  return c->pending ? c->pending->pooled : none;
 }
 
 int rt_forward_host(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStream_t s) {
@@ -975,12 +1093,14 @@ int rt_report_hidden(pm_ctx* c, int index, const void* hidden, int B, int seq, c
 }  // namespace pm
 
 pm_ctx::~pm_ctx() {
+  delete pending;
   // Best effort: the context may die with work in flight only if the caller ignored errors.
   if (have_last_stream) cudaStreamSynchronize(last_stream);
-  if (copy_stream) {
-    cudaStreamSynchronize(copy_stream);
-    cudaStreamDestroy(copy_stream);
-  }
+  for (cudaStream_t cs : {copy_stream, prefetch_stream})
+    if (cs) {
+      cudaStreamSynchronize(cs);
+      cudaStreamDestroy(cs);
+    }
   for (auto e : line_ready) cudaEventDestroy(e);
   for (auto e : seg_events) cudaEventDestroy(e);
   if (sync_event) cudaEventDestroy(sync_event);
@@ -1015,5 +1135,8 @@ pm_ctx::~pm_ctx() {
       cudaFree(slab);
     }
   }
-  for (void* b : arena_blocks) cudaFreeHost(b);
+  if (shared_prefix.empty()) {
+    for (void* b : arena_blocks) cudaFreeHost(b);
+  }
+  pm::rt_release_shared_blocks(this);
 }

@@ -16,8 +16,13 @@
 #include "cache_engine.hpp"
 #include "pm_common.cuh"
 
+namespace pm {
+struct PendingForward;
+}
+
 struct pm_ctx {
   pm::Config cfg;
+  pm::PendingForward* pending = nullptr;  // the layer call in progress (defined and freed in runtime.cu)
   std::unique_ptr<pm::CacheEngine> eng;
   std::string error;  // scratch for building messages
 
@@ -30,6 +35,22 @@ struct pm_ctx {
   std::vector<size_t> param_offset;     // [N + 1] offsets inside a record; [N] = record size
   std::vector<unsigned char*> host_rec; // [L * E] pinned record of each expert
   std::vector<void*> arena_blocks;      // one pinned block per layer
+  // ---- pooled miss fetch (expert-parallel ranks of one node; see pool_fetch.cu) ------------
+  std::string shared_prefix;            // non-empty: the arena blocks live in POSIX shared memory "<prefix>_L<layer>"
+  struct SharedBlock {
+    void* ptr;
+    size_t bytes;
+    std::string unlink_name;            // set by the creator, who removes the name at destruction
+  };
+  std::vector<SharedBlock> shared_blocks;
+  void* pool_mail = nullptr;            // mailbox through which ranks exchange their miss lists
+  std::string pool_mail_name;           // rank 0 removes the name at destruction
+  size_t pool_mail_bytes = 0;
+  int pool_rank = 0, pool_world = 0;
+  size_t pool_slice = 0;                // bytes of one rank's slice of a record (the last may be shorter)
+  std::vector<std::vector<void*>> peer_arena;  // [rank][layer] mapped, CUDA-registered arena blocks
+  std::vector<int> peer_num_expert;
+  int64_t pool_bytes_pulled = 0;        // host-to-device bytes this rank pulled for the pool
   bool pinned = false;
   int role_gate = 0, role_up = 1, role_down = 2;        // which tensor plays which part
   int role_qgate = -1, role_qup = -1, role_qdown = -1;  // uint4 experts: scale/zero tensors
@@ -53,9 +74,16 @@ struct pm_ctx {
   CUmemAllocationProp line_prop{};
 
   // ---- streams and events -------------------------------------------------------------
-  // One copy stream: back-to-back expert copies on it already run at the link's rate (alternating
-  // two streams measured the same 51.4 GB/s against 52.4 GB/s for bare pinned copies).
-  cudaStream_t copy_stream = nullptr;
+  // Demand copies (an activated expert is missing) and prefetch copies (a predicted expert) run on
+  // separate streams: a demand copy then starts at once and shares the link with a prefetch in
+  // flight instead of queueing behind every prefetch issued before it, which is what the
+  // reference's scheduler achieves by popping demand tasks first (src/cpp_worker/prefetcher.cpp:143-161).
+  // Back-to-back copies on one stream already run at the link's rate (51.4 GB/s against 52.4 GB/s
+  // for bare pinned copies), so this changes latency, not throughput. Two copies into the same
+  // line from different streams are ordered through the line's ready event.
+  cudaStream_t copy_stream = nullptr;      // demand copies
+  cudaStream_t prefetch_stream = nullptr;  // prefetch copies
+  std::vector<cudaStream_t> line_copy_stream;  // stream of the last copy into the line
   cudaStream_t last_stream = nullptr;
   bool have_last_stream = false;
   std::vector<cudaEvent_t> line_ready;    // recorded on the copy stream after a copy into the line
@@ -162,7 +190,23 @@ struct RoutedRows {
   const float* pred_scores = nullptr;
   const int32_t* pred_layers = nullptr;  // host
   int n_pred = 0;
+  // Leave the copies of missing activated experts to the caller: the call returns after the cache
+  // decisions and the launches that need no such copy; rt_pending_pooled lists the copies, and
+  // rt_forward_end finishes the call once the lines' ready events have been recorded.
+  bool collect_demand_copies = false;
 };
+int rt_forward_end(pm_ctx* c);
+const std::vector<Action>& rt_pending_pooled(pm_ctx* c);
+constexpr int kPoolMaxMiss = 64;  // most demand copies one rank can put into one exchange
+void* rt_shared_block(pm_ctx* c, const std::string& name, size_t bytes, bool create, std::string* err);
+void rt_release_shared_blocks(pm_ctx* c);
+int rt_pool_init(pm_ctx* c, int rank, int world, const char* mailbox_name);
+int rt_pool_open_peer(pm_ctx* c, int peer, const char* prefix, int peer_num_expert);
+int rt_pool_exchange(pm_ctx* c, int64_t seq, const int32_t* experts, int n, int32_t* out, double timeout_s);
+int rt_pool_stage(pm_ctx* c, int layer, const int32_t* lists, void* send_dev, size_t send_cap, size_t recv_cap,
+                  int64_t* send_split, int64_t* recv_split, cudaStream_t s);
+int rt_pool_scatter(pm_ctx* c, const void* recv_dev, cudaStream_t s);
+int rt_pool_fetch_locally(pm_ctx* c);
 int rt_forward(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStream_t s, const RoutedRows* routed = nullptr);
 int rt_forward_host(pm_ctx* c, int layer, const void* x, int T, void* y, cudaStream_t s);
 int rt_report_hidden(pm_ctx* c, int index, const void* hidden, int B, int seq, cudaStream_t s);

@@ -88,6 +88,30 @@ class CudaBackend:
         self.side = torch.cuda.Stream(device=dev)
         self._shared_scratch = None
         self.launches = 0   # kernels this backend launched itself (the cache counts its own)
+        self.pool = None    # set by enable_pool
+
+    def enable_pool(self, arena_prefixes, n_local_of, mailbox_name: str, group=None, max_misses: int = 48):
+        """Pooled miss fetch: every rank pulls 1/world of each missing expert record over its own host
+        link and the slices meet at the owner over NVLink (see include/promoe_b200.h). The cache must
+        have been pinned with the context option shared_arena = arena_prefixes[rank]; every rank calls
+        this at the same point (it contains barriers)."""
+        world, rank, h = self.geo.world, self.rank, self.cache.handle
+        self._lib.call("pm_pool_init", h, rank, world, mailbox_name.encode())
+        if world > 1:
+            dist.barrier(group=group)      # every arena exists and is filled
+            for peer in range(world):
+                if peer != rank:
+                    self._lib.call("pm_pool_open_peer", h, peer, arena_prefixes[peer].encode(), int(n_local_of[peer]))
+            dist.barrier(group=group)
+        slice_bytes = int(self.cache.get("pool_slice"))
+        cap = max_misses * slice_bytes
+        self.pool = dict(seq=0, cap=cap, max_misses=max_misses, slice=slice_bytes, group=group,
+                         send=torch.empty(cap, dtype=torch.uint8, device=self.device),
+                         recv=torch.empty(cap, dtype=torch.uint8, device=self.device),
+                         stream=torch.cuda.Stream(device=self.device),
+                         miss=(C.c_int32 * 64)(), lists=(C.c_int32 * (world * 65))(),
+                         send_split=(C.c_int64 * world)(), recv_split=(C.c_int64 * world)(),
+                         exchanges=0, local_fallbacks=0)
 
     def _stream(self):
         return torch.cuda.current_stream(self.device).cuda_stream
@@ -172,9 +196,35 @@ class CudaBackend:
     def expert_rows(self, layer, recv, row_expert, scores_sum, dsts):
         """Unweighted expert output (f32) of every received row, in place of the row (padding -> zeros)."""
         arr = (C.c_int32 * max(1, len(dsts)))(*dsts)
-        self._lib.call("pm_moe_forward_routed", self.cache.handle, layer, recv.data_ptr(), self.geo.rows,
-                       row_expert.data_ptr(), self.out.data_ptr(), self.global_tokens,
-                       None if scores_sum is None else scores_sum.data_ptr(), arr, len(dsts), self._stream())
+        if self.pool is None:
+            self._lib.call("pm_moe_forward_routed", self.cache.handle, layer, recv.data_ptr(), self.geo.rows,
+                           row_expert.data_ptr(), self.out.data_ptr(), self.global_tokens,
+                           None if scores_sum is None else scores_sum.data_ptr(), arr, len(dsts), self._stream())
+            return self.out
+        p, h, world = self.pool, self.cache.handle, self.geo.world
+        n = C.c_int(0)
+        self._lib.call("pm_moe_forward_routed_begin", h, layer, recv.data_ptr(), self.geo.rows, row_expert.data_ptr(),
+                       self.out.data_ptr(), self.global_tokens, None if scores_sum is None else scores_sum.data_ptr(),
+                       arr, len(dsts), self._stream(), p["miss"], min(64, p["max_misses"]), C.byref(n))
+        p["seq"] += 1
+        self._lib.call("pm_pool_exchange", h, p["seq"], p["miss"], n.value, p["lists"], 20.0)
+        total = sum(p["lists"][r * 65] for r in range(world))
+        if total > p["max_misses"]:          # every rank sees the same lists and takes the same branch
+            self._lib.call("pm_pool_fetch_locally", h)
+            p["local_fallbacks"] += 1
+        elif total > 0:
+            ps = p["stream"]
+            with torch.cuda.stream(ps):
+                self._lib.call("pm_pool_stage", h, layer, p["lists"], p["send"].data_ptr(), p["cap"], p["cap"],
+                               p["send_split"], p["recv_split"], ps.cuda_stream)
+                ins, outs = list(p["send_split"]), list(p["recv_split"])
+                if world > 1:
+                    dist.all_to_all_single(p["recv"][: sum(outs)], p["send"][: sum(ins)], outs, ins, group=p["group"])
+                else:
+                    p["recv"][: sum(outs)].copy_(p["send"][: sum(ins)])
+                self._lib.call("pm_pool_scatter", h, p["recv"].data_ptr(), ps.cuda_stream)
+            p["exchanges"] += 1
+        self._lib.call("pm_moe_forward_routed_end", h)
         return self.out
 
     def shared_begin(self, layer, x, b):

@@ -115,7 +115,7 @@ class SyntheticStack:
     """Builds the cache, the pinned expert records and the resident weights of one config."""
 
     def __init__(self, cfg: StackConfig, device="cuda", num_layer: int | None = None, expert_range=None,
-                 **cache_config):
+                 shared_arena: str | None = None, **cache_config):
         self.cfg = cfg
         self.device = torch.device(device)
         L = cfg.num_layer if num_layer is None else num_layer
@@ -136,6 +136,8 @@ class SyntheticStack:
         for l in range(L):
             for e in range(self.n_local):
                 self.cache.register_expert_sizes(l, e, sizes)
+        if shared_arena:  # records in POSIX shared memory, so the other ranks of the node can pull them too
+            self.cache.set("shared_arena", shared_arena)
         self.cache.pin_all()
         self.gate_w, self.gate_bias, self.shared, self.shared_gate_w = [], [], [], []
         for l in range(L):

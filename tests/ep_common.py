@@ -23,7 +23,8 @@ def make_preds(model, seed=3, D=32):
     return preds
 
 
-def build_rank(rank, world, with_pred, tokens=6, seed=11):
+def build_rank(rank, world, with_pred, tokens=6, seed=11, pool_tag=None):
+    """pool_tag: a string shared by all ranks of the run switches the pooled miss fetch on."""
     model = TinyModel(seed=seed, L=3, E=16, H=256, I=128, k=4, shared_I=256, shared_gate=True)
     preds = make_preds(model) if with_pred else {}
     geo = Geometry(model.E, world, max_tokens_per_rank=tokens, top_k=model.k, hidden=model.H, n_pred=1 if with_pred else 0)
@@ -34,6 +35,8 @@ def build_rank(rank, world, with_pred, tokens=6, seed=11):
     for l in range(model.L):
         for e in range(n_local):
             cache.register_expert(l, e, [om.to_bf16_bits(w) for w in model.experts[l][e0 + e]])
+    if pool_tag is not None:
+        cache.set("shared_arena", f"/pm_{pool_tag}_{rank}")
     cache.pin_all()
     cache.build_slab()
     cache.enable_event_log(True)
@@ -47,6 +50,9 @@ def build_rank(rank, world, with_pred, tokens=6, seed=11):
     pmap = [(l + 1, l + 2) if l + 1 < model.L else (model.L, model.L) for l in range(model.L)]
     be = CudaBackend(cache, layers, torch.device("cuda"), geo, rank, predictors=dev_preds, predict_map=pmap,
                      global_tokens=tokens * world)
+    if pool_tag is not None:
+        be.enable_pool([f"/pm_{pool_tag}_{r}" for r in range(world)],
+                       [geo.bounds[r + 1] - geo.bounds[r] for r in range(world)], f"/pm_{pool_tag}_mail")
     return model, preds, ExpertParallelMoE(geo, be), be, cache
 
 

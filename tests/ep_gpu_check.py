@@ -28,7 +28,8 @@ def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
-    model, preds, ep, be, cache = build_rank(rank, world, with_pred=True)
+    pool_tag = f"c{os.environ.get('MASTER_PORT', '0')}" if "--pool" in sys.argv else None   # pooled miss fetch
+    model, preds, ep, be, cache = build_rank(rank, world, with_pred=True, pool_tag=pool_tag)
     rng = np.random.default_rng(50 + rank)
     worst, xs = 0.0, []
     for step in range(5):
@@ -45,8 +46,9 @@ def main():
     oc = oracle_replay(model, preds, gathered, rank, world)
     ok_log = cache.events() == oc.events
     ok = worst < 5e-3 and ok_log and int(be.unpack_err.item()) == 0
+    pooled = f" pool exchanges {be.pool['exchanges']} pulled {cache.get('pool_bytes_pulled')} B" if be.pool else ""
     print(f"rank {rank}/{world}: rel_err {worst:.2e} cache_log_equal {ok_log} events {len(oc.events)} "
-          f"dispatched {ep.bytes_dispatched} B {'OK' if ok else 'MISMATCH'}", flush=True)
+          f"dispatched {ep.bytes_dispatched} B{pooled} {'OK' if ok else 'MISMATCH'}", flush=True)
     flag = torch.tensor([0 if ok else 1], device="cuda")
     dist.all_reduce(flag)
     cache.close()

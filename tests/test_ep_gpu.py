@@ -78,13 +78,15 @@ def test_pack_and_unpack_kernels_follow_the_message_layout(lib):
     assert int(err.item()) == 1 and (row_expert.cpu().numpy()[: geo.seg_rows] == -1).all()
 
 
-@pytest.mark.parametrize("with_pred", [False, True])
-def test_layer_with_world_size_one(lib, with_pred):
+@pytest.mark.parametrize("with_pred,pool", [(False, False), (True, False), (True, True)])
+def test_layer_with_world_size_one(lib, with_pred, pool):
     """The whole expert-parallel layer on one rank: pack, (copy), unpack, padded routed rows with the
     device-planned launch, shared expert on the side stream, combine; outputs and cache log against
-    the oracles."""
+    the oracles. With the pooled miss fetch on, the demand copies travel through the shared-memory
+    arena, the staging buffer, the (degenerate) exchange and the scatter kernel instead."""
+    import os
     from tests.ep_common import build_rank, oracle_replay
-    model, preds, ep, be, cache = build_rank(0, 1, with_pred)
+    model, preds, ep, be, cache = build_rank(0, 1, with_pred, pool_tag=f"t{os.getpid()}" if pool else None)
     rng = np.random.default_rng(9)
     xs = []
     for step in range(5):
@@ -102,6 +104,11 @@ def test_layer_with_world_size_one(lib, with_pred):
     assert int(be.unpack_err.item()) == 0
     if with_pred:
         assert cache.stats()["prefetch_miss"] > 0
+    if pool:
+        assert be.pool["exchanges"] > 0 and int(cache.get("pool_bytes_pulled")) > 0
+        st = cache.stats()
+        # every miss moved one whole record, whichever route its bytes took
+        assert st["h2d_bytes"] == (st["precise_miss"] + st["prefetch_miss"]) * int(cache.get("record_bytes"))
     cache.close()
 
 
@@ -112,8 +119,9 @@ def test_two_rank_nccl_exchange(lib):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     script = Path(__file__).with_name("ep_gpu_check.py")
-    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-                        "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
-                       capture_output=True, text=True, timeout=600)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert r.stdout.count(" OK") == 2
+    for extra in ([], ["--pool"]):
+        r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                            "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), *extra],
+                           capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+        assert r.stdout.count(" OK") == 2
