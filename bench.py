@@ -255,7 +255,7 @@ def h2d_peak(record_bytes: int, dev, copies: int = 96) -> float:
     return copies * n / (e0.elapsed_time(e1) / 1e3) / 1e9
 
 
-def ep_parity_check(stack, ep, be, cfg, rank, world, x, preds, pmap, n_local_pred):
+def ep_parity_check(stack, ep, be, cfg, rank, world, x, preds, pmap, num_predict):
     """One untimed decode step through the expert-parallel stack with the event log on, checked outside
     every timed region: this rank's outputs against the single-process oracle on its tokens, and its
     cache log against a sequential-schedule cache over its block of experts fed with the ids that
@@ -304,11 +304,14 @@ def ep_parity_check(stack, ep, be, cfg, rank, world, x, preds, pmap, n_local_pre
         my_scores.append(sc)
     gathered = [None] * world
     dist.all_gather_object(gathered, (my_ids, my_scores))
-    oc = sp.SequentialCache(L, n_local, cfg.top_k, cache_rate=cfg.cache_rate, num_predict=n_local_pred)
+    oc = sp.SequentialCache(L, n_local, cfg.top_k, cache_rate=cfg.cache_rate, num_predict=num_predict)
     for l in range(L):
         for d in sorted(gathered[0][1][l]):
             total = sum(gathered[r][1][l][d] for r in range(world))
-            oc.prefetch_layer(d, om.rank_experts(total[e0: e0 + n_local], oc.num_predict))
+            # the global top num_predict; this rank prefetches the ones it holds (up to its own limit)
+            mine = [int(e) - e0 for e in om.rank_experts(total, num_predict) if e0 <= e < e0 + n_local][: oc.num_predict]
+            if mine:
+                oc.prefetch_layer(d, mine)
         act = sorted({e - e0 for r in range(world) for e in gathered[r][0][l] if e0 <= e < e0 + n_local})
         if act:
             oc.report_layer(l, act)
@@ -351,17 +354,17 @@ def run_ours(args, cfg):
     B = cfg.batch // world
     K, W = args.steps, args.warmup
     ep = be = None
-    preds, pmap, n_local_pred = {}, [], 0
+    preds, pmap = {}, []
     if world > 1:
         # expert parallel: this rank holds a contiguous block of experts and its own cache over them; every
-        # rank runs the predictor on its tokens, the scores of an owner's experts travel in the dispatch
-        # message, the owner sums them and prefetches its share of the predicted experts
+        # rank runs the predictor on its tokens, the scores travel in the dispatch message, every owner
+        # sums them and prefetches those of the global top num_predict experts that it holds
         from promoe_b200.ep import CudaBackend, ExpertParallelMoE, Geometry, expert_bounds
         bnd = expert_bounds(cfg.num_expert, world)
         n_local = bnd[rank + 1] - bnd[rank]
-        n_local_pred = max(1, round(num_predict * n_local / cfg.num_expert)) if use_pred else 0
         pool_tag = None if args.no_pool else f"b{os.environ.get('MASTER_PORT', '0')}"
-        stack = synth.SyntheticStack(cfg, dev, expert_range=(bnd[rank], n_local), num_predict_expert_per_layer=n_local_pred,
+        stack = synth.SyntheticStack(cfg, dev, expert_range=(bnd[rank], n_local),
+                                     num_predict_expert_per_layer=num_predict if use_pred else 0,
                                      shared_arena=None if pool_tag is None else f"/pm_{pool_tag}_{rank}")
         stack.install_routed_only()
         if use_pred:
@@ -369,7 +372,7 @@ def run_ours(args, cfg):
         n_pred = max((b - a for a, b in pmap), default=0)
         geo = Geometry(cfg.num_expert, world, B, cfg.top_k, H, n_pred=n_pred)
         be = CudaBackend(stack.cache, stack.ep_layers(), dev, geo, rank, predictors=preds, predict_map=pmap,
-                         global_tokens=cfg.batch)
+                         global_tokens=cfg.batch, n_predict=num_predict if use_pred else 0)
         if pool_tag is not None:
             be.enable_pool([f"/pm_{pool_tag}_{r}" for r in range(world)], [bnd[r + 1] - bnd[r] for r in range(world)],
                            f"/pm_{pool_tag}_mail")
@@ -399,7 +402,8 @@ def run_ours(args, cfg):
 
     ep_parity = None
     if ep is not None and not args.no_ep_parity:
-        ep_parity = ep_parity_check(stack, ep, be, cfg, rank, world, xs[W + 2 * K + P + 4], preds, pmap, n_local_pred)
+        ep_parity = ep_parity_check(stack, ep, be, cfg, rank, world, xs[W + 2 * K + P + 4], preds, pmap,
+                                    num_predict if use_pred else 0)
 
     prefill = None
     if args.prefill_tokens > 0 and ep is None:

@@ -216,13 +216,19 @@ int pm_moe_forward(pm_ctx* ctx, int layer, const void* x_dev, int T, void* y_dev
  * NULL). An id outside [-1, num_expert) is PM_ERR_INVALID. max_rows_per_expert (0 = unknown) is a
  * bound on the rows one expert can receive that the caller guarantees, e.g. the number of tokens
  * in flight on all ranks: up to 16, the resident experts start before the host has read the row
- * counts. pred_scores (device f32 [n_pred, num_expert], may be NULL) are predictor scores for the
- * layers pred_layers[0..n_pred) (host int32), summed over whoever computed them: they are ranked
- * and prefetched like the scores of pm_report_hidden, before this layer's own report. No
- * counterpart in the reference, which is single-GPU (src/cpp_worker/model_loader.cpp:75-79). */
+ * counts. pred_scores (device f32 [n_pred, pred_width], may be NULL) are predictor scores for the
+ * layers pred_layers[0..n_pred) (host int32) over the pred_width experts of the WHOLE model, of
+ * which this context holds [pred_first, pred_first + num_expert): the pred_top best of the whole
+ * list are taken (descending score, ties to the lower id) and those among them that this context
+ * holds are prefetched in that order, before this layer's own report, so that all the contexts
+ * of an expert-parallel run together prefetch what one context holding every expert would.
+ * pred_width = num_expert, pred_first = 0 and pred_top = num_predict_expert_per_layer give the
+ * ranking of pm_report_hidden. No counterpart in the reference, which is single-GPU
+ * (src/cpp_worker/model_loader.cpp:75-79). */
 int pm_moe_forward_routed(pm_ctx* ctx, int layer, const void* x_rows, int n_rows, const int32_t* row_expert,
                           float* rows_out, int max_rows_per_expert, const float* pred_scores,
-                          const int32_t* pred_layers, int n_pred, void* stream);
+                          const int32_t* pred_layers, int n_pred, int pred_width, int pred_first, int pred_top,
+                          void* stream);
 /* ---- pooled miss fetch for expert-parallel ranks of one node (no counterpart in the reference,
  *      which is single-GPU) -------------------------------------------------------------------
  * A layer call of an expert-parallel stack ends when the rank with the most missing experts has
@@ -249,8 +255,8 @@ int pm_moe_forward_routed(pm_ctx* ctx, int layer, const void* x_rows, int n_rows
  * that an exchange does not fit the buffers). */
 int pm_moe_forward_routed_begin(pm_ctx* ctx, int layer, const void* x_rows, int n_rows, const int32_t* row_expert,
                                 float* rows_out, int max_rows_per_expert, const float* pred_scores,
-                                const int32_t* pred_layers, int n_pred, void* stream, int32_t* miss_experts,
-                                int miss_cap, int* n_miss);
+                                const int32_t* pred_layers, int n_pred, int pred_width, int pred_first, int pred_top,
+                                void* stream, int32_t* miss_experts, int miss_cap, int* n_miss);
 int pm_moe_forward_routed_end(pm_ctx* ctx);
 int pm_pool_init(pm_ctx* ctx, int rank, int world, const char* mailbox_name);
 int pm_pool_open_peer(pm_ctx* ctx, int peer, const char* arena_prefix, int peer_num_expert);
@@ -330,20 +336,20 @@ int pm_k_swiglu_ffn_static(const pm_ffn_group* groups, int n_groups, const void*
  * fixed-size message per peer and direction, so the per-layer dispatch is one all-to-all with
  * split sizes known in advance. Message of a source to owner g: 1 + cap rows of `hidden` bf16;
  * row 0 = header (int32 counts[max_block] of the rows for each of g's experts, then float
- * scores[n_pred][max_block], the source's predictor scores of g's experts), rows 1.. = the token
+ * scores[n_pred][num_expert], the source's predictor scores of all experts), rows 1.. = the token
  * rows routed to g's experts in expert order. pm_k_ep_pack builds the n_ranks messages from the
  * permutation's outputs (counts, offsets, row_token, pos; bounds_dev = device int32 [n_ranks + 1],
  * rank g owns experts [bounds[g], bounds[g+1])) and writes pos_reply [n_pairs]: the row of the
  * reply buffer [n_ranks * (1 + cap), hidden] f32 where the output of routed pair (t, j) returns.
  * pm_k_ep_unpack turns a receive buffer into row_expert [n_ranks * (1 + cap)] (local expert id,
  * -1 for header and unused rows: the row list pm_moe_forward_routed takes) and scores_sum
- * [n_pred, n_local] (the sources' scores added in rank order). */
+ * [n_pred, num_expert] (the sources' scores added in rank order: identical on every owner). */
 int pm_k_ep_pack(const void* x, int hidden, const int32_t* counts, const int32_t* offsets,
                  const int32_t* row_token, const int32_t* pos, int n_pairs, const int32_t* bounds_dev,
                  int n_ranks, int max_block, int cap, const float* scores, int n_pred, int num_expert,
                  void* send, int32_t* pos_reply, void* stream);
 int pm_k_ep_unpack(const void* recv, int hidden, int n_ranks, int n_local, int max_block, int cap, int n_pred,
-                   int32_t* row_expert, float* scores_sum, int32_t* err_flag, void* stream);
+                   int num_expert, int32_t* row_expert, float* scores_sum, int32_t* err_flag, void* stream);
 int pm_k_combine(const float* yexp, const int32_t* pos, const float* topk_w, int T, int H, int k, int R,
                  int n_shared, const float* shared_scale, void* y, void* stream);
 /* scores[e] = sum_b (W2 relu(W1 x_b + b1) + b2)[e]; hidden_scratch is f32 [B, d] device scratch. */

@@ -94,9 +94,9 @@ SIGNATURES = {
     "pm_profile_read": (_i, [_vp, C.POINTER(pm_profile), _i]),
     "pm_layer_set_weights": (_i, [_vp, _i, C.POINTER(pm_layer_weights)]),
     "pm_moe_forward": (_i, [_vp, _i, _vp, _i, _vp, _vp]),
-    "pm_moe_forward_routed": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _vp]),
-    "pm_moe_forward_routed_begin": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _vp, C.POINTER(C.c_int32), _i,
-                                         C.POINTER(_i)]),
+    "pm_moe_forward_routed": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "pm_moe_forward_routed_begin": (_i, [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp,
+                                         C.POINTER(C.c_int32), _i, C.POINTER(_i)]),
     "pm_moe_forward_routed_end": (_i, [_vp]),
     "pm_pool_init": (_i, [_vp, _i, _i, _cp]),
     "pm_pool_open_peer": (_i, [_vp, _i, _cp, _i]),
@@ -116,7 +116,7 @@ SIGNATURES = {
     "pm_k_swiglu_ffn_static_capacity": (_sz, []),
     "pm_k_swiglu_ffn_static": (_i, [C.POINTER(pm_ffn_group), _i, _vp, _i, _vp, _i, _vp, _vp]),
     "pm_k_ep_pack": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp]),
-    "pm_k_ep_unpack": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "pm_k_ep_unpack": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "pm_k_combine": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
     "pm_k_predictor_mlp": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp]),
 }

@@ -441,36 +441,50 @@ int pm_moe_forward(pm_ctx* ctx, int layer, const void* x_dev, int T, void* y_dev
   return rt_forward(ctx, layer, x_dev, T, y_dev, (cudaStream_t)stream);
 }
 
+namespace {
+int fill_routed(pm_ctx* ctx, RoutedRows* r, const int32_t* row_expert, float* rows_out, int max_rows_per_expert,
+                const float* pred_scores, const int32_t* pred_layers, int n_pred, int pred_width, int pred_first,
+                int pred_top) {
+  if (n_pred < 0 || (n_pred > 0 && (!pred_scores || !pred_layers))) return fail(PM_ERR_INVALID, "bad prediction arguments");
+  if (n_pred > 0 && (pred_width < ctx->cfg.num_expert || pred_width > 4096 || pred_first < 0 ||
+                     pred_first + ctx->cfg.num_expert > pred_width || pred_top < 0))
+    return fail(PM_ERR_INVALID, "the prediction's expert range does not contain this context's experts");
+  r->row_expert = row_expert;
+  r->rows_out = rows_out;
+  r->max_rows_per_expert = max_rows_per_expert;
+  r->pred_scores = pred_scores;
+  r->pred_layers = pred_layers;
+  r->n_pred = n_pred;
+  r->pred_width = pred_width;
+  r->pred_first = pred_first;
+  r->pred_top = pred_top;
+  return PM_OK;
+}
+}  // namespace
+
 int pm_moe_forward_routed(pm_ctx* ctx, int layer, const void* x_rows, int n_rows, const int32_t* row_expert,
                           float* rows_out, int max_rows_per_expert, const float* pred_scores,
-                          const int32_t* pred_layers, int n_pred, void* stream) {
+                          const int32_t* pred_layers, int n_pred, int pred_width, int pred_first, int pred_top,
+                          void* stream) {
   if (need(ctx)) return PM_ERR_INVALID;
-  if (n_pred < 0 || (n_pred > 0 && (!pred_scores || !pred_layers))) return fail(PM_ERR_INVALID, "bad prediction arguments");
   RoutedRows r;
-  r.row_expert = row_expert;
-  r.rows_out = rows_out;
-  r.max_rows_per_expert = max_rows_per_expert;
-  r.pred_scores = pred_scores;
-  r.pred_layers = pred_layers;
-  r.n_pred = n_pred;
+  int rc0 = fill_routed(ctx, &r, row_expert, rows_out, max_rows_per_expert, pred_scores, pred_layers, n_pred, pred_width,
+                        pred_first, pred_top);
+  if (rc0 != PM_OK) return rc0;
   return rt_forward(ctx, layer, x_rows, n_rows, nullptr, (cudaStream_t)stream, &r);
 }
 
 int pm_moe_forward_routed_begin(pm_ctx* ctx, int layer, const void* x_rows, int n_rows, const int32_t* row_expert,
                                 float* rows_out, int max_rows_per_expert, const float* pred_scores,
-                                const int32_t* pred_layers, int n_pred, void* stream, int32_t* miss_experts,
-                                int miss_cap, int* n_miss) {
+                                const int32_t* pred_layers, int n_pred, int pred_width, int pred_first, int pred_top,
+                                void* stream, int32_t* miss_experts, int miss_cap, int* n_miss) {
   if (need(ctx)) return PM_ERR_INVALID;
-  if (n_pred < 0 || (n_pred > 0 && (!pred_scores || !pred_layers))) return fail(PM_ERR_INVALID, "bad prediction arguments");
   if (!n_miss || (miss_cap > 0 && !miss_experts)) return fail(PM_ERR_INVALID, "null miss list");
   *n_miss = 0;
   RoutedRows r;
-  r.row_expert = row_expert;
-  r.rows_out = rows_out;
-  r.max_rows_per_expert = max_rows_per_expert;
-  r.pred_scores = pred_scores;
-  r.pred_layers = pred_layers;
-  r.n_pred = n_pred;
+  int rc0 = fill_routed(ctx, &r, row_expert, rows_out, max_rows_per_expert, pred_scores, pred_layers, n_pred, pred_width,
+                        pred_first, pred_top);
+  if (rc0 != PM_OK) return rc0;
   r.collect_demand_copies = true;
   int rc = rt_forward(ctx, layer, x_rows, n_rows, nullptr, (cudaStream_t)stream, &r);
   if (rc != PM_OK) return rc;

@@ -7,7 +7,8 @@
 //
 // Message of source rank s to owner rank g: `seg_rows` = 1 + cap rows of `hidden` bf16.
 //   row 0      header: int32 counts[max_block] (rows for each of g's experts, ascending expert id),
-//              then float scores[n_pred][max_block] (this source's predictor scores of g's experts)
+//              then float scores[n_pred][num_expert] (this source's predictor scores of ALL experts:
+//              every owner adds up the same vectors, so all owners rank the same global list)
 //   row 1 + i  the i-th token row routed to one of g's experts, sorted by expert id; i < sum(counts)
 //   the rest   unused
 // The owner treats the whole receive buffer [G * seg_rows, hidden] as its row list: header rows
@@ -38,10 +39,7 @@ ep_pack_kernel(const uint4* __restrict__ x, int row_vec, const int32_t* __restri
     int32_t* hdr_counts = reinterpret_cast<int32_t*>(seg);
     float* hdr_scores = reinterpret_cast<float*>(seg) + max_block;
     for (int i = threadIdx.x; i < max_block; i += blockDim.x) hdr_counts[i] = (e0 + i < e1) ? counts[e0 + i] : 0;
-    for (int i = threadIdx.x; i < n_pred * max_block; i += blockDim.x) {
-      const int p = i / max_block, e = i - p * max_block;
-      hdr_scores[i] = (e0 + e < e1) ? scores[(size_t)p * num_expert + e0 + e] : 0.f;
-    }
+    for (int i = threadIdx.x; i < n_pred * num_expert; i += blockDim.x) hdr_scores[i] = scores[i];
   }
   // rows, dealt to the CTAs of the segment
   for (int i = blockIdx.y; i < n; i += gridDim.y) {
@@ -61,7 +59,7 @@ ep_pack_kernel(const uint4* __restrict__ x, int row_vec, const int32_t* __restri
 
 __global__ void __launch_bounds__(256)
 ep_unpack_kernel(const uint4* __restrict__ recv, int row_vec, int n_ranks, int n_local, int max_block, int cap,
-                 int n_pred, int32_t* __restrict__ row_expert, float* __restrict__ scores_sum,
+                 int n_pred, int num_expert, int32_t* __restrict__ row_expert, float* __restrict__ scores_sum,
                  int32_t* __restrict__ err) {
   __shared__ int prefix[257];
   const int seg_rows = 1 + cap;
@@ -94,13 +92,12 @@ ep_unpack_kernel(const uint4* __restrict__ recv, int row_vec, int n_ranks, int n
       out[1 + i] = e;
     }
   }
-  // predictor scores of this rank's experts, summed over the sources in rank order
-  for (int i = threadIdx.x; i < n_pred * n_local; i += blockDim.x) {
-    const int p = i / n_local, e = i - p * n_local;
+  // predictor scores of all experts, summed over the sources in rank order (the same on every owner)
+  for (int i = threadIdx.x; i < n_pred * num_expert; i += blockDim.x) {
     float sum = 0.f;
     for (int s = 0; s < n_ranks; ++s) {
       const float* sc = reinterpret_cast<const float*>(recv + (size_t)s * seg_rows * row_vec) + max_block;
-      sum += sc[p * max_block + e];
+      sum += sc[i];
     }
     scores_sum[i] = sum;
   }
@@ -120,7 +117,7 @@ int pm_k_ep_pack(const void* x, int hidden, const int32_t* counts, const int32_t
   if (hidden <= 0 || hidden % 8 != 0 || n_ranks <= 0 || n_ranks > kMaxRanks || max_block <= 0 || max_block > 256 ||
       cap < 0 || n_pairs < 0 || n_pred < 0)
     return fail(PM_ERR_INVALID, "ep_pack: bad sizes");
-  if ((size_t)(max_block + n_pred * max_block) * 4 > (size_t)hidden * 2)
+  if ((size_t)(max_block + n_pred * num_expert) * 4 > (size_t)hidden * 2)
     return fail(PM_ERR_INVALID, "ep_pack: the header (counts and predictor scores) does not fit one row");
   if (!x || !counts || !offsets || !row_token || !pos || !bounds_dev || !send || !pos_reply || (n_pred > 0 && !scores))
     return fail(PM_ERR_INVALID, "ep_pack: null pointer");
@@ -133,13 +130,15 @@ int pm_k_ep_pack(const void* x, int hidden, const int32_t* counts, const int32_t
 }
 
 int pm_k_ep_unpack(const void* recv, int hidden, int n_ranks, int n_local, int max_block, int cap, int n_pred,
-                   int32_t* row_expert, float* scores_sum, int32_t* err_flag, void* stream) {
+                   int num_expert, int32_t* row_expert, float* scores_sum, int32_t* err_flag, void* stream) {
   if (hidden <= 0 || hidden % 8 != 0 || n_ranks <= 0 || n_ranks > kMaxRanks || n_local <= 0 || n_local > max_block ||
-      max_block > 256 || cap < 0 || n_pred < 0)
+      max_block > 256 || cap < 0 || n_pred < 0 || num_expert < n_local ||
+      (size_t)(max_block + n_pred * num_expert) * 4 > (size_t)hidden * 2)
     return fail(PM_ERR_INVALID, "ep_unpack: bad sizes");
   if (!recv || !row_expert || (n_pred > 0 && !scores_sum)) return fail(PM_ERR_INVALID, "ep_unpack: null pointer");
   ep_unpack_kernel<<<1, 256, 0, (cudaStream_t)stream>>>((const uint4*)recv, hidden * 2 / 16, n_ranks, n_local,
-                                                        max_block, cap, n_pred, row_expert, scores_sum, err_flag);
+                                                        max_block, cap, n_pred, num_expert, row_expert, scores_sum,
+                                                        err_flag);
   PM_CUDA(cudaGetLastError());
   return PM_OK;
 }

@@ -231,20 +231,29 @@ Stage stage_of(pm_ctx* c) {
 }
 
 // Ranks one predicted layer and issues its prefetch (PredictWorker::do_one_task_impl,
-// src/cpp_worker/worker.cpp:6-77).
-int issue_prediction(pm_ctx* c, int dst, const float* scores) {
+// src/cpp_worker/worker.cpp:6-77). `scores` covers `width` experts of which this context holds
+// [first, first + num_expert): the `top` best of the whole list are taken and those this context
+// holds are prefetched in rank order (width = num_expert, first = 0: the plain single-context case).
+int issue_prediction(pm_ctx* c, int dst, const float* scores, int width = 0, int first = 0, int top = -1) {
   const int E = c->cfg.num_expert;
+  if (width <= 0) width = E;
   if (c->cfg.cache_policy == "nn") {
-    std::string err = c->eng->update_priority(scores, 1, dst);
+    std::string err = c->eng->update_priority(scores + first, 1, dst);
     if (!err.empty()) return fail(PM_ERR_STATE, err);
   }
-  int n = std::min(c->cfg.num_predict_expert_per_layer, E);
+  int n = std::min(top >= 0 ? top : c->cfg.num_predict_expert_per_layer, width);
   if (dst == 0 && c->cfg.limit_layer_0_num_predict != -1) n = std::min(n, c->cfg.limit_layer_0_num_predict);
-  std::vector<int64_t> order(E);
-  for (int i = 0; i < E; ++i) order[i] = i;
+  std::vector<int64_t> order(width);
+  for (int i = 0; i < width; ++i) order[i] = i;
   std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return scores[a] > scores[b]; });
+  std::vector<int64_t> mine;
+  for (int i = 0; i < n; ++i)
+    if (order[i] >= first && order[i] < first + E) mine.push_back(order[i] - first);
+  // the cache clamps a prefetch to its own num_predict (the lines of pool 0, src/cpp_worker/cache.cpp:130-131)
+  if ((int)mine.size() > c->cfg.num_predict_expert_per_layer) mine.resize(c->cfg.num_predict_expert_per_layer);
+  if (mine.empty()) return PM_OK;
   std::vector<Action> acts;
-  std::string err = c->eng->prefetch_layer(dst, order.data(), n, &acts);
+  std::string err = c->eng->prefetch_layer(dst, mine.data(), (int64_t)mine.size(), &acts);
   if (!err.empty()) return fail(PM_ERR_STATE, err);
   rt_mark_dirty(c, acts);
   return rt_execute_copies(c, acts);
@@ -784,16 +793,21 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
   PM_CUDA(cudaEventRecord(c->routed_event, s));
   cudaStream_t rb = c->readback_stream;
   PM_CUDA(cudaStreamWaitEvent(rb, c->routed_event, 0));
-  if (routed && routed->n_pred > 0 && routed->pred_scores != nullptr && c->seq_len == 1) {
+  const bool routed_pred = routed && routed->n_pred > 0 && routed->pred_scores != nullptr && c->seq_len == 1;
+  if (routed_pred) {
     // scores computed elsewhere (the expert-parallel sources): they ride to the host with the counts
+    const size_t bytes = (size_t)routed->n_pred * routed->pred_width * 4;
     if (routed->n_pred > c->cfg.num_layer) return fail(PM_ERR_INVALID, "more predicted layers than layers");
-    for (int i = 0; i < routed->n_pred; ++i) {
-      const int dst = routed->pred_layers[i];
-      if (dst < 0 || dst >= c->cfg.num_layer) return fail(PM_ERR_INVALID, "predicted layer out of range");
-      PM_CUDA(cudaMemcpyAsync(st.scores + (size_t)dst * E, routed->pred_scores + (size_t)i * E, (size_t)E * 4,
-                              cudaMemcpyDeviceToHost, rb));
-      pred_dsts.push_back(dst);
+    for (int i = 0; i < routed->n_pred; ++i)
+      if (routed->pred_layers[i] < 0 || routed->pred_layers[i] >= c->cfg.num_layer)
+        return fail(PM_ERR_INVALID, "predicted layer out of range");
+    if (c->h_routed_scores_cap < bytes) {
+      if (c->h_routed_scores) PM_CUDA(cudaFreeHost(c->h_routed_scores));
+      c->h_routed_scores = nullptr;
+      PM_CUDA(cudaHostAlloc((void**)&c->h_routed_scores, bytes, cudaHostAllocDefault));
+      c->h_routed_scores_cap = bytes;
     }
+    PM_CUDA(cudaMemcpyAsync(c->h_routed_scores, routed->pred_scores, bytes, cudaMemcpyDeviceToHost, rb));
   } else if (!pred_dsts.empty()) {
     PM_CUDA(cudaMemcpyAsync(st.scores, c->d_scores, (size_t)c->cfg.num_layer * E * 4, cudaMemcpyDeviceToHost, rb));
   }
@@ -898,6 +912,12 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
     rc = issue_prediction(c, dst, st.scores + (size_t)dst * E);
     if (rc != PM_OK) return rc;
   }
+  if (routed_pred)
+    for (int i = 0; i < routed->n_pred; ++i) {
+      rc = issue_prediction(c, routed->pred_layers[i], c->h_routed_scores + (size_t)i * routed->pred_width,
+                            routed->pred_width, routed->pred_first, routed->pred_top);
+      if (rc != PM_OK) return rc;
+    }
 
   const int32_t* counts = st.counts;
   const int32_t* offsets = st.counts + E;
@@ -1120,6 +1140,7 @@ pm_ctx::~pm_ctx() {
   if (ws_dev) cudaFree(ws_dev);
   if (h_stage) cudaFreeHost(h_stage);
   if (h_tc_plan) cudaFreeHost(h_tc_plan);
+  if (h_routed_scores) cudaFreeHost(h_routed_scores);
   if (slab_built) {
     if (slab_vmm) {
       pm::Driver& d = pm::driver();

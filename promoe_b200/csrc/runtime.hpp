@@ -127,6 +127,8 @@ struct pm_ctx {
   __nv_bfloat16 *d_hbuf = nullptr, *d_xin = nullptr, *d_yout = nullptr;
   unsigned char* d_plan = nullptr;  // launch plans of one layer call (descriptors + tile tables)
   size_t plan_cap = 0;              // bytes
+  float* h_routed_scores = nullptr;  // pinned: predictor scores handed to the routed-rows form
+  size_t h_routed_scores_cap = 0;
   unsigned char* h_stage = nullptr;  // pinned: counts+offsets, scores, descriptors, slot tables, routing
   size_t h_stage_bytes = 0;
 
@@ -181,15 +183,17 @@ int rt_execute_copies(pm_ctx* c, const std::vector<Action>& actions);
 // max_rows_per_expert (0 = unknown): an upper bound on the rows any one expert receives that the
 // caller guarantees (e.g. the global number of tokens); with a bound of at most 16 the resident
 // experts are launched without waiting for the host. pred_scores (optional): device f32
-// [n_pred, num_expert], predictor scores of layers pred_layers[i] that travel to the host with
-// the row counts; each is ranked and prefetched before this layer's own report.
+// [n_pred, pred_width], predictor scores of layers pred_layers[i] over the experts of the whole
+// model (this context holds [pred_first, pred_first + num_expert) of them); they travel to the
+// host with the row counts, the pred_top best of the whole list are taken and those this context
+// holds are prefetched, before this layer's own report.
 struct RoutedRows {
   const int32_t* row_expert = nullptr;
   float* rows_out = nullptr;
   int max_rows_per_expert = 0;
   const float* pred_scores = nullptr;
   const int32_t* pred_layers = nullptr;  // host
-  int n_pred = 0;
+  int n_pred = 0, pred_width = 0, pred_first = 0, pred_top = 0;
   // Leave the copies of missing activated experts to the caller: the call returns after the cache
   // decisions and the launches that need no such copy; rt_pending_pooled lists the copies, and
   // rt_forward_end finishes the call once the lines' ready events have been recorded.

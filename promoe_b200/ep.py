@@ -8,16 +8,19 @@ Per layer there is ONE collective each way, with split sizes fixed in advance:
     pack: one fixed-size message per owner = header row (per-expert row counts, predictor scores
           of the owner's experts) + the token rows routed to the owner's experts
     -> all-to-all                                                 (dispatch)
-    owner: unpack the headers into a row list (padding rows = -1), sum the predictor scores,
-           pm_moe_forward_routed: prefetch the predicted experts, cache bookkeeping, copies,
-           grouped FFN; the one host <-> device sync of the layer is its read of the row counts
+    owner: unpack the headers into a row list (padding rows = -1), sum the predictor scores of all
+           experts over the sources (every owner gets the same sums, hence the same global ranking),
+           pm_moe_forward_routed: prefetch those of the globally best-ranked experts that it owns,
+           cache bookkeeping, copies, grouped FFN; the one host <-> device sync of the layer is its
+           read of the row counts
     -> all-to-all of the expert outputs (f32, same geometry)      (combine traffic)
     source: shared expert (on a side stream, under the exchange) + weighted combine
 
 The reference has no multi-GPU path (device 0 is hard-coded, src/cpp_worker/model_loader.cpp:75-79),
 so there is nothing to mirror: each rank's cache behaves exactly like a single-GPU cache over its
-block of experts, fed with the union of the ids that arrive from all ranks and with the predictor
-scores of its experts summed over all ranks' tokens.
+block of experts, fed with the union of the ids that arrive from all ranks; and all ranks together
+prefetch exactly the experts a single cache over all experts would: the top n of the predictor
+scores summed over all ranks' tokens, each prefetched by its owner.
 
 Collectives go through torch.distributed (NCCL over NVLink for CUDA tensors, gloo for the CPU
 tests); all device compute goes through the C ABI via a backend object, so the host logic
@@ -53,7 +56,7 @@ class Geometry:
         self.cap = max_tokens_per_rank * top_k
         self.seg_rows = 1 + self.cap
         self.rows = world * self.seg_rows
-        if (self.max_block + n_pred * self.max_block) * 4 > hidden * 2:
+        if (self.max_block + n_pred * num_expert) * 4 > hidden * 2:
             raise ValueError("the message header (counts and predictor scores) does not fit one row")
 
 
@@ -61,18 +64,19 @@ class CudaBackend:
     """Device work of one rank through the C ABI (stateless kernels + the rank's ExpertCache)."""
 
     def __init__(self, cache, layers, device, geometry: Geometry, rank: int, predictors=None, predict_map=None,
-                 global_tokens: int = 0):
+                 global_tokens: int = 0, n_predict: int = 0):
         """layers[l] = dict(gate_w, gate_bias, shared (3 tensors or None), shared_gate_w, top_k, norm_topk,
         routed_scale, inter) with full-width (all experts) router weights. predictors[(src, dst)] =
         (w1, b1, w2, b2) device tensors over ALL experts; predict_map[src] = (first, last + 1) of the
-        layers index src predicts. global_tokens: tokens in flight on all ranks per layer call (the
-        bound on the rows one expert can receive), 0 if unknown."""
+        layers index src predicts; n_predict: experts prefetched per predicted layer over ALL ranks
+        (the global top n_predict; every owner prefetches the ones it holds). global_tokens: tokens in
+        flight on all ranks per layer call (the bound on the rows one expert can receive), 0 if unknown."""
         from . import _lib
         self._lib, self.cache, self.layers, self.device = _lib, cache, layers, torch.device(device)
         self.geo, self.rank = geometry, rank
         self.n_local = geometry.bounds[rank + 1] - geometry.bounds[rank]
         self.predictors, self.predict_map = predictors or {}, predict_map
-        self.global_tokens = global_tokens
+        self.global_tokens, self.n_predict = global_tokens, n_predict
         g, dev = geometry, self.device
         i32 = dict(dtype=torch.int32, device=dev)
         self.bounds_dev = torch.tensor(g.bounds, **i32)
@@ -82,7 +86,7 @@ class CudaBackend:
         self.row_expert = torch.empty(g.rows, **i32)
         self.unpack_err = torch.zeros(1, **i32)
         self.scores = torch.zeros((max(1, g.n_pred), g.num_expert), dtype=torch.float32, device=dev)
-        self.scores_sum = torch.zeros((max(1, g.n_pred), self.n_local), dtype=torch.float32, device=dev)
+        self.scores_sum = torch.zeros((max(1, g.n_pred), g.num_expert), dtype=torch.float32, device=dev)
         self.pred_hidden = None
         self._per_tokens = {}
         self.side = torch.cuda.Stream(device=dev)
@@ -189,23 +193,24 @@ class CudaBackend:
     def unpack(self, recv, n_pred):
         g = self.geo
         self._lib.call("pm_k_ep_unpack", recv.data_ptr(), g.hidden, g.world, self.n_local, g.max_block, g.cap, n_pred,
-                       self.row_expert.data_ptr(), self.scores_sum.data_ptr(), self.unpack_err.data_ptr(), self._stream())
+                       g.num_expert, self.row_expert.data_ptr(), self.scores_sum.data_ptr(), self.unpack_err.data_ptr(), self._stream())
         self.launches += 1
         return self.row_expert, (self.scores_sum if n_pred else None)
 
     def expert_rows(self, layer, recv, row_expert, scores_sum, dsts):
         """Unweighted expert output (f32) of every received row, in place of the row (padding -> zeros)."""
         arr = (C.c_int32 * max(1, len(dsts)))(*dsts)
+        pred = (None if scores_sum is None else scores_sum.data_ptr(), arr, len(dsts), self.geo.num_expert,
+                self.geo.bounds[self.rank], self.n_predict)
         if self.pool is None:
             self._lib.call("pm_moe_forward_routed", self.cache.handle, layer, recv.data_ptr(), self.geo.rows,
-                           row_expert.data_ptr(), self.out.data_ptr(), self.global_tokens,
-                           None if scores_sum is None else scores_sum.data_ptr(), arr, len(dsts), self._stream())
+                           row_expert.data_ptr(), self.out.data_ptr(), self.global_tokens, *pred, self._stream())
             return self.out
         p, h, world = self.pool, self.cache.handle, self.geo.world
         n = C.c_int(0)
         self._lib.call("pm_moe_forward_routed_begin", h, layer, recv.data_ptr(), self.geo.rows, row_expert.data_ptr(),
-                       self.out.data_ptr(), self.global_tokens, None if scores_sum is None else scores_sum.data_ptr(),
-                       arr, len(dsts), self._stream(), p["miss"], min(64, p["max_misses"]), C.byref(n))
+                       self.out.data_ptr(), self.global_tokens, *pred, self._stream(), p["miss"],
+                       min(64, p["max_misses"]), C.byref(n))
         p["seq"] += 1
         self._lib.call("pm_pool_exchange", h, p["seq"], p["miss"], n.value, p["lists"], 20.0)
         total = sum(p["lists"][r * 65] for r in range(world))

@@ -49,7 +49,7 @@ def build_rank(rank, world, with_pred, tokens=6, seed=11, pool_tag=None):
     dev_preds = {key: (dev_bf16(w1), None, dev_bf16(w2), torch.from_numpy(b2).cuda()) for key, (w1, _, w2, b2) in preds.items()}
     pmap = [(l + 1, l + 2) if l + 1 < model.L else (model.L, model.L) for l in range(model.L)]
     be = CudaBackend(cache, layers, torch.device("cuda"), geo, rank, predictors=dev_preds, predict_map=pmap,
-                     global_tokens=tokens * world)
+                     global_tokens=tokens * world, n_predict=N_PREDICT if with_pred else 0)
     if pool_tag is not None:
         be.enable_pool([f"/pm_{pool_tag}_{r}" for r in range(world)],
                        [geo.bounds[r + 1] - geo.bounds[r] for r in range(world)], f"/pm_{pool_tag}_mail")
@@ -57,8 +57,9 @@ def build_rank(rank, world, with_pred, tokens=6, seed=11, pool_tag=None):
 
 
 def oracle_replay(model, preds, xs_by_rank, rank, world):
-    """What this rank's cache must have decided: per layer call, the prefetch of the top experts by the
-    predictor scores summed over every rank's tokens, then the ascending unique ids that arrived."""
+    """What this rank's cache must have decided: per layer call, the prefetch of those of the globally
+    best-ranked experts (predictor scores summed over every rank's tokens) that this rank holds, then
+    the ascending unique ids that arrived."""
     geo_bounds = [r * model.E // world for r in range(world + 1)]
     e0, n_local = geo_bounds[rank], geo_bounds[rank + 1] - geo_bounds[rank]
     oc = sp.SequentialCache(model.L, n_local, model.k, cache_rate=0.5, num_predict=N_PREDICT if preds else 0)
@@ -68,7 +69,9 @@ def oracle_replay(model, preds, xs_by_rank, rank, world):
                 if s == l:
                     # each rank adds its bias-free partial sums; the output bias enters once per token
                     total = sum(om.predictor_scores(xs_by_rank[r][step], w1, b1, w2, b2) for r in range(world))
-                    oc.prefetch_layer(d, om.rank_experts(total[e0: e0 + n_local], oc.num_predict))
+                    mine = [int(e) - e0 for e in om.rank_experts(total, N_PREDICT) if e0 <= e < e0 + n_local][: oc.num_predict]
+                    if mine:
+                        oc.prefetch_layer(d, mine)
             act = set()
             for r in range(world):
                 ids, _ = model.canonical_routing(l, xs_by_rank[r][step])

@@ -18,6 +18,12 @@ from promoe_b200.ep import ExpertParallelMoE, Geometry, expert_bounds, split_cou
 from tests.helpers import TinyModel
 
 
+def local_share(global_top, e0, n_local, clamp):
+    """Those of the globally best-ranked experts that the owner of [e0, e0 + n_local) holds, as local
+    ids in rank order, cut to the owner's own prefetch limit."""
+    return [int(e) - e0 for e in global_top if e0 <= e < e0 + n_local][:clamp]
+
+
 class OracleBackend:
     """Stand-in for CudaBackend: same methods, numpy arithmetic, a python cache per rank. pack and
     unpack follow the message layout documented in promoe_b200/csrc/ep_exchange.cu."""
@@ -27,6 +33,7 @@ class OracleBackend:
         self.e0 = geo.bounds[rank]
         self.n_local = geo.bounds[rank + 1] - self.e0
         self.cache = sp.SequentialCache(model.L, self.n_local, model.k, cache_rate=cache_rate, num_predict=n_predict)
+        self.n_predict_global = n_predict
         self.reported, self.prefetched = [], []
         self.preds = preds or {}
         self.recv = torch.zeros((geo.rows, geo.hidden), dtype=torch.bfloat16)
@@ -68,10 +75,8 @@ class OracleBackend:
             e0, e1 = g.bounds[r], g.bounds[r + 1]
             hdr = np.zeros(g.hidden // 2, np.int32)
             hdr[: e1 - e0] = b["counts"][e0:e1]
-            if n_pred:
-                sc = np.zeros((n_pred, g.max_block), np.float32)
-                sc[:, : e1 - e0] = scores[:, e0:e1]
-                hdr[g.max_block: g.max_block + n_pred * g.max_block] = sc.reshape(-1).view(np.int32)
+            if n_pred:   # the source's scores of ALL experts go to every owner
+                hdr[g.max_block: g.max_block + n_pred * g.num_expert] = np.ascontiguousarray(scores, np.float32).reshape(-1).view(np.int32)
             raw[r * g.seg_rows] = hdr.view(np.int16)
             start, n = b["offsets"][e0], b["offsets"][e1] - b["offsets"][e0]
             for i in range(n):
@@ -84,21 +89,23 @@ class OracleBackend:
         g = self.geo
         raw = recv.view(torch.int16).numpy()
         row_expert = np.full(g.rows, -1, np.int32)
-        sums = np.zeros((max(1, n_pred), self.n_local), np.float32)
+        sums = np.zeros((max(1, n_pred), g.num_expert), np.float32)
         for s in range(g.world):
             hdr = np.ascontiguousarray(raw[s * g.seg_rows]).view(np.int32)
             counts = hdr[: self.n_local]
             row_expert[s * g.seg_rows + 1: s * g.seg_rows + 1 + counts.sum()] = np.repeat(np.arange(self.n_local), counts)
             if n_pred:
-                sc = hdr[g.max_block: g.max_block + n_pred * g.max_block].view(np.float32).reshape(n_pred, g.max_block)
-                sums += sc[:, : self.n_local]       # rank order, float32, like the kernel
+                sc = hdr[g.max_block: g.max_block + n_pred * g.num_expert].view(np.float32).reshape(n_pred, g.num_expert)
+                sums += sc                          # rank order, float32, like the kernel
         return torch.from_numpy(row_expert), (sums if n_pred else None)
 
     def expert_rows(self, layer, recv, row_expert, scores_sum, dsts):
         for i, d in enumerate(dsts):                 # prediction first, as in the single-GPU forward
-            ids = om.rank_experts(scores_sum[i], self.cache.num_predict)
-            self.prefetched.append((d, [int(v) for v in ids]))
-            self.cache.prefetch_layer(d, ids)
+            ids = local_share(om.rank_experts(scores_sum[i], self.n_predict_global), self.e0, self.n_local,
+                              self.cache.num_predict)
+            self.prefetched.append((d, ids))
+            if ids:
+                self.cache.prefetch_layer(d, ids)
         re = row_expert.numpy()
         ids = sorted(set(int(e) for e in re if e >= 0))
         self.reported.append((layer, ids))
@@ -133,7 +140,7 @@ def worker(rank, world, port, seed, with_pred, out_q):
     model = TinyModel(seed=seed, L=3, E=8, H=64, I=32, k=2, shared_I=64)
     preds = make_preds(model, np.random.default_rng(seed + 1)) if with_pred else {}
     geo = Geometry(model.E, world, max_tokens_per_rank=3 + world, top_k=model.k, hidden=model.H, n_pred=1 if with_pred else 0)
-    be = OracleBackend(model, geo, rank, cache_rate=0.5, preds=preds, n_predict=1 if with_pred else 0)
+    be = OracleBackend(model, geo, rank, cache_rate=0.5, preds=preds, n_predict=2 if with_pred else 0)
     ep = ExpertParallelMoE(geo, be)
     rng = np.random.default_rng(100 + rank)
     errs, all_x = [], []
@@ -145,7 +152,7 @@ def worker(rank, world, port, seed, with_pred, out_q):
             ref, _, _ = model.oracle_forward(l, x)
             errs.append(float(np.abs(y.numpy() - ref).max() / np.abs(ref).max()))
     # the same cache driven directly: prefetches (from the scores summed over ALL ranks' tokens), then ids
-    oc = sp.SequentialCache(model.L, be.n_local, model.k, cache_rate=0.5, num_predict=1 if with_pred else 0)
+    oc = sp.SequentialCache(model.L, be.n_local, model.k, cache_rate=0.5, num_predict=2 if with_pred else 0)
     gathered = [None] * world
     dist.all_gather_object(gathered, all_x)
     pf = iter(be.prefetched)
@@ -156,10 +163,11 @@ def worker(rank, world, port, seed, with_pred, out_q):
             for (s, d), p in sorted(preds.items()):
                 if s == l:
                     total = sum(om.predictor_scores(gathered[r][step], *p) for r in range(world))
-                    want = [int(v) for v in om.rank_experts(total[be.e0: be.e0 + be.n_local], 1)]
+                    want = local_share(om.rank_experts(total, 2), be.e0, be.n_local, oc.num_predict)
                     got_d, got = next(pf)
                     ok_scores &= got_d == d and got == want
-                    oc.prefetch_layer(d, want)
+                    if want:
+                        oc.prefetch_layer(d, want)
             lyr, ids = be.reported[call]
             call += 1
             if ids:
@@ -199,6 +207,6 @@ def test_bounds_and_splits():
     assert split_counts(counts, expert_bounds(8, 2)) == [6, 5]
     assert split_counts(counts, expert_bounds(8, 1)) == [11]
     g = Geometry(60, 8, max_tokens_per_rank=1, top_k=4, hidden=2048, n_pred=3)
-    assert (g.max_block, g.cap, g.seg_rows, g.rows) == (8, 4, 5, 40)
+    assert (g.max_block, g.cap, g.seg_rows, g.rows) == (8, 4, 5, 40)   # header: 8 counts + 3 x 60 scores = 752 B of 4 KiB
     with pytest.raises(ValueError):
         Geometry(64, 1, 1, 4, hidden=64, n_pred=3)       # 64 counts + 3 x 64 scores need 1 KiB, a row has 128 B

@@ -44,7 +44,7 @@ def test_pack_and_unpack_kernels_follow_the_message_layout(lib):
     got, want = send.cpu().view(torch.int16).numpy(), want_send.view(torch.int16).numpy()
     for g in range(3):
         n = int(b["offsets"][geo.bounds[g + 1]] - b["offsets"][geo.bounds[g]])
-        hdr_words = 2 * (geo.max_block + 2 * geo.max_block)
+        hdr_words = 2 * (geo.max_block + 2 * geo.num_expert)
         np.testing.assert_array_equal(got[g * geo.seg_rows, :hdr_words], want[g * geo.seg_rows, :hdr_words])
         np.testing.assert_array_equal(got[g * geo.seg_rows + 1: g * geo.seg_rows + 1 + n],
                                       want[g * geo.seg_rows + 1: g * geo.seg_rows + 1 + n])
@@ -59,10 +59,10 @@ def test_pack_and_unpack_kernels_follow_the_message_layout(lib):
         recv[s * geo.seg_rows: (s + 1) * geo.seg_rows] = msg[1 * geo.seg_rows: 2 * geo.seg_rows]   # the part addressed to rank 1
     want_re, want_sums = ob.unpack(recv, 2)
     row_expert = torch.full((geo.rows,), 99, dtype=torch.int32, device="cuda")
-    sums = torch.zeros((2, ob.n_local), dtype=torch.float32, device="cuda")
+    sums = torch.zeros((2, geo.num_expert), dtype=torch.float32, device="cuda")
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
     recv_d = recv.cuda()
-    _lib.call("pm_k_ep_unpack", recv_d.data_ptr(), geo.hidden, 3, ob.n_local, geo.max_block, geo.cap, 2,
+    _lib.call("pm_k_ep_unpack", recv_d.data_ptr(), geo.hidden, 3, ob.n_local, geo.max_block, geo.cap, 2, geo.num_expert,
               row_expert.data_ptr(), sums.data_ptr(), err.data_ptr(), None)
     torch.cuda.synchronize()
     np.testing.assert_array_equal(row_expert.cpu().numpy(), want_re.numpy())
@@ -72,7 +72,7 @@ def test_pack_and_unpack_kernels_follow_the_message_layout(lib):
     bad = recv.clone()
     bad.view(torch.int16).numpy().view(np.int32)[0, 0] = 1000
     bad_d = bad.cuda()
-    _lib.call("pm_k_ep_unpack", bad_d.data_ptr(), geo.hidden, 3, ob.n_local, geo.max_block, geo.cap, 2,
+    _lib.call("pm_k_ep_unpack", bad_d.data_ptr(), geo.hidden, 3, ob.n_local, geo.max_block, geo.cap, 2, geo.num_expert,
               row_expert.data_ptr(), sums.data_ptr(), err.data_ptr(), None)
     torch.cuda.synchronize()
     assert int(err.item()) == 1 and (row_expert.cpu().numpy()[: geo.seg_rows] == -1).all()

@@ -209,12 +209,12 @@ def test_routed_rows_reject_an_expert_id_out_of_range(lib):
     bad = torch.tensor([0, 3, 8, 1], dtype=torch.int32, device="cuda")
     with pytest.raises(_lib.PromoeError) as e:
         _lib.call("pm_moe_forward_routed", cache.handle, 0, xd.data_ptr(), 4, bad.data_ptr(), out.data_ptr(), 0, None,
-                  None, 0, None)
+                  None, 0, 0, 0, 0, None)
     assert "expert id" in str(e.value)
     # -1 marks a padding row: no expert runs on it and its output row is zeros
     good = torch.tensor([0, 3, -1, 1], dtype=torch.int32, device="cuda")
     _lib.call("pm_moe_forward_routed", cache.handle, 0, xd.data_ptr(), 4, good.data_ptr(), out.data_ptr(), 4, None,
-              None, 0, None)
+              None, 0, 0, 0, 0, None)
     torch.cuda.synchronize()
     got = out.cpu().numpy()
     for r, e_id in enumerate([0, 3, -1, 1]):
