@@ -76,6 +76,7 @@ int pm_ctx_get(pm_ctx* ctx, const char* key, char* buf, size_t cap) {
   if (k == "keep_routing") v = ctx->keep_routing ? "true" : "false";
   else if (k == "seq_len") v = std::to_string(ctx->seq_len);
   else if (k == "tc_launches") v = std::to_string(ctx->tc_launches);
+  else if (k == "q4_expanded") v = std::to_string(ctx->q4_expanded);
   else if (k == "tc_error") {
     int32_t code = 0;
     if (ctx->have_last_stream) cudaStreamSynchronize(ctx->last_stream);

@@ -90,6 +90,7 @@ int plan_groups_size(const pm_ffn_group* groups, int n_groups, int hidden, FfnPl
 
 constexpr int kMaxSharedSlices = 8;
 constexpr int kMaxFusedGroups = 256 + kMaxSharedSlices;  // groups of one fused launch
+constexpr int kMaxFusedGroupsQ4 = 128;                    // same for uint4 experts (larger table records)
 
 // What the fused kernel needs to describe, on the device, the shared expert and the routed experts
 // a layer's slot table shows resident (no host round trip between the router and this launch).
@@ -129,18 +130,23 @@ cudaError_t launch_resident_ffn(const ResidentArgs& a, int32_t* counters, int32_
                                 __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s);
 bool resident_ffn_available(int max_rows);
 
-// bf16 launches of at most kSplitMaxRows rows per chunk run as ONE cooperative kernel (gate/up
-// tiles, then down tiles, a chunk's down tiles waiting on its gate/up tiles through the blob's
-// counters); uint4 launches and larger chunks run as a gate/up and a down launch, and mid_event
-// (optional) is recorded between the two. err (optional): device word that receives a code when a
-// bounded wait of the fused kernel gives up (default: the blob's own error word).
+// Launches of at most kSplitMaxRows rows per chunk run as ONE cooperative kernel (gate/up tiles,
+// then down tiles, a chunk's down tiles waiting on its gate/up tiles through the blob's counters),
+// bf16 and uint4 alike (uint4: up to kMaxFusedGroupsQ4 chunks); anything else runs as a gate/up and
+// a down launch, and mid_event (optional) is recorded between the two. err (optional): device word
+// that receives a code when a bounded wait of the fused kernel gives up (default: the blob's own
+// error word).
 cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& info, int quant4,
                               const __nv_bfloat16* x, int H, const int32_t* row_token,
                               __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s,
                               cudaEvent_t mid_event = nullptr, int32_t* err = nullptr);
 inline bool ffn_launch_is_fused(const FfnPlanInfo& info, int quant4) {
-  return !quant4 && info.max_rows <= kSplitMaxRows;
+  return info.max_rows <= kSplitMaxRows && (!quant4 || info.n_desc <= kMaxFusedGroupsQ4);
 }
+
+// uint4 group-128 matrix [rows, K] (packed words + {scale, zero} fp16 pairs) -> bf16 [rows, K].
+cudaError_t launch_dequant_q4(const void* packed, const void* scale_zero, int rows, int K, __nv_bfloat16* out,
+                              cudaStream_t s);
 
 cudaError_t launch_gather_rows(const void* src, const int32_t* index, int n_rows, size_t row_bytes, void* dst,
                                cudaStream_t s);

@@ -505,13 +505,19 @@ namespace {
 // Prefill-size segment on the tcgen05 path: gather the token rows once per layer call, plan the
 // 128 x 128 tiles, upload groups and tiles, launch the gate/up and the down kernel.
 int flush_segment_tc(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv_bfloat16* x, int n_rows,
-                     cudaStream_t s) {
+                     cudaStream_t s, bool q4 = false) {
   if (!c->xperm_ready) {
     PM_CUDA(launch_gather_rows(x, c->d_row_token, n_rows, (size_t)w.hidden * 2, c->d_xperm, s));
     c->kernel_launches += 1;
     c->xperm_ready = true;
   }
-  if (!c->tc_maps_ready) {
+  if (q4) {
+    if (!c->tc_maps_q4_ready) {
+      int rc = tc_build_maps_q4(c, w, c->ws_tokens * (c->ws_topk + 1), &c->tc_maps_q4);
+      if (rc != PM_OK) return rc;
+      c->tc_maps_q4_ready = true;
+    }
+  } else if (!c->tc_maps_ready) {
     int rc = tc_build_maps(c, w, c->ws_tokens * (c->ws_topk + 1), &c->tc_maps);
     if (rc != PM_OK) return rc;
     c->tc_maps_ready = true;
@@ -520,8 +526,22 @@ int flush_segment_tc(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const _
   for (size_t i = 0; i < seg->groups.size(); ++i) {
     const pm_ffn_group& g = seg->groups[i];
     if (g.row_count <= 0) continue;
-    groups.push_back(TcGroup{g.row_start, g.row_count, g.inter, seg->group_line[i]});
+    int line = seg->group_line[i];
+    if (q4 && line >= 0) {
+      // expand the expert's packed matrices into scratch line n (stream order keeps the line's earlier
+      // readers ahead of this write); the tensor-core kernels then read bf16 as for any other expert
+      line = (int)groups.size();
+      unsigned char* dst = c->q4_scratch + (size_t)line * c->q4_scratch_stride;
+      const size_t mat = (size_t)w.inter * w.hidden * 2;
+      PM_CUDA(launch_dequant_q4(g.w_gate, g.q_gate, w.inter, w.hidden, (__nv_bfloat16*)dst, s));
+      PM_CUDA(launch_dequant_q4(g.w_up, g.q_up, w.inter, w.hidden, (__nv_bfloat16*)(dst + mat), s));
+      PM_CUDA(launch_dequant_q4(g.w_down, g.q_down, w.hidden, w.inter, (__nv_bfloat16*)(dst + 2 * mat), s));
+      c->kernel_launches += 3;
+      c->q4_expanded += 1;
+    }
+    groups.push_back(TcGroup{g.row_start, g.row_count, g.inter, line});
   }
+  const TcMaps& maps = q4 ? c->tc_maps_q4 : c->tc_maps;
   std::vector<TcTile> gu, dn;
   tc_plan(groups, w.hidden, &gu, &dn);
   const size_t g_bytes = align_up(groups.size() * sizeof(TcGroup), 256);
@@ -546,7 +566,7 @@ int flush_segment_tc(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const _
     }
     PM_CUDA(cudaEventRecord(sample.e0, s));
   }
-  PM_CUDA(launch_prefill_ffn(c->tc_maps, (const TcGroup*)d, (const TcTile*)(d + g_bytes), (int)gu.size(),
+  PM_CUDA(launch_prefill_ffn(maps, (const TcGroup*)d, (const TcTile*)(d + g_bytes), (int)gu.size(),
                              (const TcTile*)(d + g_bytes + gu_bytes), (int)dn.size(), w.hidden, c->d_hbuf, c->ws_inter,
                              c->d_yexp, c->d_tc_err, s, c->profile_ffn ? sample.e1 : nullptr));
   if (c->profile_ffn) {
@@ -556,6 +576,34 @@ int flush_segment_tc(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const _
   c->kernel_launches += 2;
   c->tc_launches += 1;
   return PM_OK;
+}
+
+// Rows per expert from which a segment of uint4 experts is expanded to bf16 and run on the tensor
+// cores: below it, re-reading the packed weights once per 16 rows is cheaper than writing and
+// re-reading four times as many bf16 bytes.
+constexpr int kQ4ExpandMinRows = 64;
+
+// The bf16 scratch slab for `n` expanded experts (grown on demand, at least one line per expert of
+// a layer). False if the device cannot provide it: the caller then stays on the split-K tiles.
+bool q4_scratch_ready(pm_ctx* c, const pm_layer_weights& w, int n) {
+  const size_t stride = align_up((size_t)3 * w.inter * w.hidden * 2, 256);
+  const size_t lines = (size_t)std::max(n, c->cfg.num_expert);
+  if (c->q4_scratch != nullptr && c->q4_scratch_stride == stride && c->q4_scratch_lines >= lines) return true;
+  if (c->q4_scratch != nullptr) {
+    cudaDeviceSynchronize();  // earlier launches may still read the old slab
+    cudaFree(c->q4_scratch);
+    c->q4_scratch = nullptr;
+    c->q4_scratch_lines = 0;
+  }
+  if (cudaMalloc((void**)&c->q4_scratch, stride * lines) != cudaSuccess) {
+    cudaGetLastError();
+    c->q4_scratch = nullptr;
+    return false;
+  }
+  c->q4_scratch_stride = stride;
+  c->q4_scratch_lines = lines;
+  c->tc_maps_q4_ready = false;
+  return true;
 }
 
 int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv_bfloat16* x, int n_rows,
@@ -568,18 +616,44 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
       c->line_waiter[line] = s;
     }
   }
-  int seg_max_rows = 0;
-  for (const pm_ffn_group& g : seg->groups) seg_max_rows = std::max(seg_max_rows, g.row_count);
-  if (seg_max_rows > kSplitMaxRows && tc_prefill_usable(c, w)) {
-    int rc = flush_segment_tc(c, seg, w, x, n_rows, s);
+  // Groups with many rows go to the tensor cores; the others stay on the split-K tiles, which stream
+  // the weights faster when there are only a few rows to use them for (a large decode batch has both
+  // kinds in one layer call). uint4 groups change over later: expanding an expert to bf16 costs more
+  // than re-reading its packed weights a few times.
+  const bool tc_ok = w.quant4 ? tc_prefill_usable_q4(c, w) : tc_prefill_usable(c, w);
+  const int most_small = w.quant4 ? kQ4ExpandMinRows - 1 : kSplitMaxRows;
+  Segment big;
+  if (tc_ok) {
+    size_t keep = 0;
+    for (size_t i = 0; i < seg->groups.size(); ++i) {
+      if (seg->groups[i].row_count > most_small) {
+        big.groups.push_back(seg->groups[i]);
+        big.group_line.push_back(seg->group_line[i]);
+      } else {
+        seg->groups[keep] = seg->groups[i];
+        seg->group_line[keep] = seg->group_line[i];
+        ++keep;
+      }
+    }
+    seg->groups.resize(keep);
+    seg->group_line.resize(keep);
+    if (w.quant4 && !big.groups.empty() && !q4_scratch_ready(c, w, (int)big.groups.size())) {
+      seg->groups.insert(seg->groups.end(), big.groups.begin(), big.groups.end());
+      seg->group_line.insert(seg->group_line.end(), big.group_line.begin(), big.group_line.end());
+      big.groups.clear();
+      big.group_line.clear();
+    }
+  }
+  if (!big.groups.empty()) {
+    int rc = flush_segment_tc(c, &big, w, x, n_rows, s, w.quant4 != 0);
     if (rc != PM_OK) return rc;
+  }
+  if (seg->groups.empty()) {
     if (!seg->lines.empty()) {
       cudaEvent_t ev = next_seg_event(c);
       PM_CUDA(cudaEventRecord(ev, s));
       for (int line : seg->lines) c->line_read[line] = ev;
     }
-    seg->groups.clear();
-    seg->group_line.clear();
     seg->lines.clear();
     seg->waits.clear();
     return PM_OK;
@@ -883,6 +957,7 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
   c->tc_plan_used = 0;
   c->xperm_ready = false;
   c->tc_maps_ready = false;
+  c->tc_maps_q4_ready = false;
   if (c->profile_ffn && !c->ffn_samples.empty()) {  // their events have fired: recycle them now
     rc = rt_profile_collect(c);
     if (rc != PM_OK) return rc;
@@ -1140,6 +1215,7 @@ pm_ctx::~pm_ctx() {
   if (ws_dev) cudaFree(ws_dev);
   if (h_stage) cudaFreeHost(h_stage);
   if (h_tc_plan) cudaFreeHost(h_tc_plan);
+  if (q4_scratch) cudaFree(q4_scratch);
   if (h_routed_scores) cudaFreeHost(h_routed_scores);
   if (slab_built) {
     if (slab_vmm) {

@@ -145,6 +145,13 @@ struct pm_ctx {
   bool xperm_ready = false, tc_maps_ready = false;  // per layer call
   pm::TcMaps tc_maps;
   int64_t tc_launches = 0;
+  // uint4 experts on the prefill path: the packed weights of a segment's experts are expanded into
+  // this bf16 slab (one line per expert of the segment) and the tensor-core kernels read it
+  unsigned char* q4_scratch = nullptr;
+  size_t q4_scratch_lines = 0, q4_scratch_stride = 0;
+  pm::TcMaps tc_maps_q4;
+  bool tc_maps_q4_ready = false;  // per layer call
+  int64_t q4_expanded = 0;        // experts expanded so far
 
   bool keep_routing = false;
   int seq_len = 1;
@@ -220,7 +227,10 @@ int rt_temp_move(pm_ctx* c, int layer, int expert, bool to_gpu, cudaStream_t s, 
 void rt_mark_dirty(pm_ctx* c, const std::vector<Action>& actions);
 int rt_profile_collect(pm_ctx* c);
 bool tc_prefill_usable(const pm_ctx* c, const pm_layer_weights& w);
+bool tc_prefill_usable_q4(const pm_ctx* c, const pm_layer_weights& w);
 int tc_build_maps(pm_ctx* c, const pm_layer_weights& w, int rows_cap, TcMaps* m);
+// Same with the routed experts' bf16 weights in `slab` (gate, up, down back to back in every line).
+int tc_build_maps_q4(pm_ctx* c, const pm_layer_weights& w, int rows_cap, TcMaps* m);
 void tc_plan(const std::vector<TcGroup>& groups, int hidden, std::vector<TcTile>* gu, std::vector<TcTile>* dn);
 
 }  // namespace pm

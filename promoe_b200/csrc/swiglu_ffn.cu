@@ -19,7 +19,9 @@
 // lane loads 16 contiguous bytes (8 bf16) of a weight row and of a token row at
 // the same k offset and feeds pairs {0,1} and {2,3} to one m16n8k16 MMA and pairs
 // {4,5}, {6,7} to a second one. Both operands therefore use full 128-bit loads.
+#include <algorithm>
 #include <cstdlib>
+#include <type_traits>
 
 #include "pm_common.cuh"
 
@@ -35,6 +37,12 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
                : "l"(p));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t ldg_stream_u32(const uint32_t* p) {
+  uint32_t r;
+  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(r) : "l"(p));
   return r;
 }
 
@@ -390,6 +398,19 @@ struct FusedGroup {  // shared-memory record of one chunk
   int32_t row_start, rows, inter, ld_down;
   int32_t tile_gu, tile_dn;  // first gate/up tile, first down tile
 };
+struct FusedGroupQ4 : FusedGroup {  // uint4 experts: {scale, zero} fp16 pairs per (row, 128-group)
+  const uint32_t* q_gate;
+  const uint32_t* q_up;
+  const uint32_t* q_down;
+};
+template <bool Q4>
+struct GroupOf {
+  using type = FusedGroup;
+};
+template <>
+struct GroupOf<true> {
+  using type = FusedGroupQ4;
+};
 
 struct FusedLaunch {
   const GroupDesc* groups;  // host-planned launch: n_groups descriptors; nullptr = device-planned
@@ -412,14 +433,15 @@ template <int NT>
 struct TileCtx {
   const unsigned char* a_ptr[4];
   const unsigned char* b_ptr[NT];
+  const uint32_t* sz_ptr[4];  // uint4 experts only
   int s_end;  // this warp's k-steps; a row without a token has b_ptr == nullptr
   int gi;     // chunk index
   int m0;     // first weight row of the tile
 };
 
 // First chunk at or after `from` whose tile range holds `tile` (tiles only move forward).
-template <bool GATEUP>
-__device__ __forceinline__ int find_group(const FusedGroup* sg, int n, int from, int tile) {
+template <bool GATEUP, class G>
+__device__ __forceinline__ int find_group(const G* sg, int n, int from, int tile) {
   int gi = from;
   while (gi + 1 < n && (GATEUP ? sg[gi + 1].tile_gu : sg[gi + 1].tile_dn) <= tile) ++gi;
   return gi;
@@ -438,59 +460,76 @@ __device__ __forceinline__ void load_src_rows(int (&src_row)[NT], const FusedGro
   }
 }
 
-template <int NT, bool GATEUP, int WARPS>
-__device__ __forceinline__ void tile_setup(TileCtx<NT>& t, const FusedGroup& d, int gi, int tile,
+template <int NT, bool GATEUP, int WARPS, class G>
+__device__ __forceinline__ void tile_setup(TileCtx<NT>& t, const G& d, int gi, int tile,
                                            const int (&src_row)[NT], const __nv_bfloat16* bsrc, int ldb, int hidden) {
+  constexpr bool Q4 = std::is_same<G, FusedGroupQ4>::value;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, q = lane & 3;
   const int tile_local = tile - (GATEUP ? d.tile_gu : d.tile_dn);
   const int K = GATEUP ? hidden : d.inter;
-  const size_t row_bytes = (size_t)(GATEUP ? hidden : d.ld_down) * 2;
+  // bf16: a k-step is 32 elements of a row (4 lanes x 16 bytes); uint4: one 128-weight quantisation
+  // group, also 4 lanes x 16 bytes of packed nibbles, against 4 x 64 bytes of token values
+  const size_t row_bytes = Q4 ? (size_t)K / 2 : (size_t)(GATEUP ? hidden : d.ld_down) * 2;
   t.gi = gi;
   t.m0 = tile_local * (GATEUP ? 16 : 32);
   // Every warp takes a contiguous range of k-steps (interleaving them across warps, w, w+8, ...,
   // measured 6 % slower: longer contiguous runs per warp suit DRAM better).
-  const int steps = K / 32;
+  const int steps = Q4 ? K / 128 : K / 32;
   const int first = (warp * steps) / WARPS;
   t.s_end = ((warp + 1) * steps) / WARPS - first;
   const size_t col = (size_t)first * 64 + q * 16;
-  if (GATEUP) {
-    t.a_ptr[0] = d.w_gate + (size_t)(t.m0 + g) * row_bytes + col;
-    t.a_ptr[1] = d.w_gate + (size_t)(t.m0 + g + 8) * row_bytes + col;
-    t.a_ptr[2] = d.w_up + (size_t)(t.m0 + g) * row_bytes + col;
-    t.a_ptr[3] = d.w_up + (size_t)(t.m0 + g + 8) * row_bytes + col;
-  } else {
+  int row[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) t.a_ptr[j] = d.w_down + (size_t)(t.m0 + g + 8 * j) * row_bytes + col;
+  for (int j = 0; j < 4; ++j) row[j] = GATEUP ? t.m0 + g + 8 * (j & 1) : t.m0 + g + 8 * j;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const unsigned char* w = GATEUP ? (j < 2 ? d.w_gate : d.w_up) : d.w_down;
+    t.a_ptr[j] = w + (size_t)row[j] * row_bytes + col;
   }
+  if constexpr (Q4) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t* z = GATEUP ? (j < 2 ? d.q_gate : d.q_up) : d.q_down;
+      t.sz_ptr[j] = z + (size_t)row[j] * steps + first;
+    }
+  }
+  const size_t col_b = Q4 ? (size_t)first * 256 + q * 64 : col;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
-    t.b_ptr[nt] = src_row[nt] >= 0 ? reinterpret_cast<const unsigned char*>(bsrc + (size_t)src_row[nt] * ldb) + col
+    t.b_ptr[nt] = src_row[nt] >= 0 ? reinterpret_cast<const unsigned char*>(bsrc + (size_t)src_row[nt] * ldb) + col_b
                                    : nullptr;
 }
 
 // The DEPTH register slots of a lane hold the k-steps s0 .. s0 + DEPTH - 1 of the tile; the helpers
 // below work on the slots [FIRST, FIRST + COUNT), so that the two halves can be refilled separately.
-template <int NT, int DEPTH, int FIRST = 0, int COUNT = DEPTH>
-__device__ __forceinline__ void tile_issue_a(const TileCtx<NT>& t, int s0, uint4 (&a)[DEPTH][4]) {
+template <int NT, int DEPTH, bool Q4, int FIRST = 0, int COUNT = DEPTH>
+__device__ __forceinline__ void tile_issue_a(const TileCtx<NT>& t, int s0, uint4 (&a)[DEPTH][4],
+                                             uint32_t (&sz)[DEPTH][4]) {
 #pragma unroll
   for (int d = FIRST; d < FIRST + COUNT; ++d) {
     if (s0 + d < t.s_end) {
       const size_t off = (size_t)(s0 + d) * 64;
 #pragma unroll
       for (int j = 0; j < 4; ++j) a[d][j] = ldg_stream(t.a_ptr[j] + off);
+      if constexpr (Q4) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sz[d][j] = __ldg(t.sz_ptr[j] + (s0 + d));
+      }
     }
   }
 }
 
-template <int NT, int DEPTH, bool COHERENT_B, int FIRST = 0, int COUNT = DEPTH>
+template <int NT, int DEPTH, bool COHERENT_B, bool Q4, int FIRST = 0, int COUNT = DEPTH>
 __device__ __forceinline__ void tile_issue_b(const TileCtx<NT>& t, int s0, uint4 (&b)[DEPTH][NT]) {
+  if constexpr (!Q4) {  // uint4 tiles fetch their token values (L1/L2 hits) inside tile_compute_q4
 #pragma unroll
-  for (int d = FIRST; d < FIRST + COUNT; ++d) {
-    if (s0 + d < t.s_end) {
-      const size_t off = (size_t)(s0 + d) * 64;
+    for (int d = FIRST; d < FIRST + COUNT; ++d) {
+      if (s0 + d < t.s_end) {
+        const size_t off = (size_t)(s0 + d) * 64;
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-        b[d][nt] = t.b_ptr[nt] != nullptr ? load_b<COHERENT_B>(t.b_ptr[nt] + off) : make_uint4(0, 0, 0, 0);
+        for (int nt = 0; nt < NT; ++nt)
+          b[d][nt] = t.b_ptr[nt] != nullptr ? load_b<COHERENT_B>(t.b_ptr[nt] + off) : make_uint4(0, 0, 0, 0);
+      }
     }
   }
 }
@@ -509,6 +548,61 @@ __device__ __forceinline__ void tile_compute(const TileCtx<NT>& t, int s0, const
           const uint4& hi = a[d][2 * m + 1];
           mma_bf16(acc[m][nt], lo.x, hi.x, lo.y, hi.y, b[d][nt].x, b[d][nt].y);
           mma_bf16(acc[m][nt], lo.z, hi.z, lo.w, hi.w, b[d][nt].z, b[d][nt].w);
+        }
+      }
+    }
+  }
+}
+
+// uint4 k-step: four 16-byte vectors of token values against the four packed words of each weight row
+// (see the layout note above q4_pair), then the per-group scale / zero fix-up.
+template <int NT, int DEPTH, bool COHERENT_B, int FIRST = 0, int COUNT = DEPTH>
+__device__ __forceinline__ void tile_compute_q4(const TileCtx<NT>& t, int s0, const uint4 (&a)[DEPTH][4],
+                                                const uint32_t (&sz)[DEPTH][4], float (&acc)[2][NT][4]) {
+  constexpr uint32_t kOnes = 0x3F803F80u;  // bf16 (1, 1)
+#pragma unroll
+  for (int d = FIRST; d < FIRST + COUNT; ++d) {
+    if (s0 + d < t.s_end) {
+      float raw[NT][2][4], xs[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) raw[nt][0][i] = raw[nt][1][i] = xs[nt][i] = 0.f;
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        const uint32_t w00 = (&a[d][0].x)[v], w01 = (&a[d][1].x)[v];  // first pair of rows
+        const uint32_t w10 = (&a[d][2].x)[v], w11 = (&a[d][3].x)[v];  // second pair
+        uint4 bv[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+          bv[nt] = t.b_ptr[nt] != nullptr ? load_b<COHERENT_B>(t.b_ptr[nt] + (size_t)(s0 + d) * 256 + v * 16)
+                                          : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {  // nibble pairs {0,1} go with b.x, b.y; pairs {2,3} with b.z, b.w
+          // each word is unpacked once and used for every n-tile
+          const uint32_t a0 = q4_pair(w00, 2 * h), a1 = q4_pair(w01, 2 * h), a2 = q4_pair(w00, 2 * h + 1),
+                         a3 = q4_pair(w01, 2 * h + 1);
+          const uint32_t c0 = q4_pair(w10, 2 * h), c1 = q4_pair(w11, 2 * h), c2 = q4_pair(w10, 2 * h + 1),
+                         c3 = q4_pair(w11, 2 * h + 1);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t b0 = h ? bv[nt].z : bv[nt].x, b1 = h ? bv[nt].w : bv[nt].y;
+            mma_bf16(raw[nt][0], a0, a1, a2, a3, b0, b1);
+            mma_bf16(raw[nt][1], c0, c1, c2, c3, b0, b1);
+            mma_bf16(xs[nt], kOnes, kOnes, kOnes, kOnes, b0, b1);
+          }
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+        const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&sz[d][2 * m]));      // row g (+16)
+        const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&sz[d][2 * m + 1]));  // row g + 8 (+16)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          acc[m][nt][0] += lo.x * (raw[nt][m][0] - (128.f + lo.y) * xs[nt][0]);
+          acc[m][nt][1] += lo.x * (raw[nt][m][1] - (128.f + lo.y) * xs[nt][1]);
+          acc[m][nt][2] += hi.x * (raw[nt][m][2] - (128.f + hi.y) * xs[nt][0]);
+          acc[m][nt][3] += hi.x * (raw[nt][m][3] - (128.f + hi.y) * xs[nt][1]);
         }
       }
     }
@@ -608,15 +702,16 @@ template <int NT, int DEPTH>
 struct StreamState {
   TileCtx<NT> t;
   uint4 a[DEPTH][4];
-  uint4 b[DEPTH][NT];
+  uint4 b[DEPTH][NT];      // bf16 tiles only
+  uint32_t sz[DEPTH][4];   // uint4 tiles only
   int tile, buf;
   bool active, all_done;
 };
 
 // Sets the CTA's first tile of a phase up and issues its weight loads. Reads only the chunk table,
 // the row table and the weights: for the down phase nothing here depends on the gate/up tiles.
-template <int NT, bool GATEUP, int DEPTH, int WARPS>
-__device__ __forceinline__ void stream_begin(StreamState<NT, DEPTH>& st, const FusedGroup* sg, int n_groups,
+template <int NT, bool GATEUP, int DEPTH, int WARPS, class G>
+__device__ __forceinline__ void stream_begin(StreamState<NT, DEPTH>& st, const G* sg, int n_groups,
                                              int first_tile, int n_tiles, const __nv_bfloat16* bsrc, int ldb,
                                              const int32_t* __restrict__ row_token, int hidden) {
   st.tile = first_tile;
@@ -626,21 +721,22 @@ __device__ __forceinline__ void stream_begin(StreamState<NT, DEPTH>& st, const F
   int src_row[NT];
   load_src_rows<NT, GATEUP>(src_row, sg[gi], row_token);
   tile_setup<NT, GATEUP, WARPS>(st.t, sg[gi], gi, first_tile, src_row, bsrc, ldb, hidden);
-  tile_issue_a<NT, DEPTH>(st.t, 0, st.a);
+  tile_issue_a<NT, DEPTH, std::is_same<G, FusedGroupQ4>::value>(st.t, 0, st.a, st.sz);
 }
 
 // Tiles st.tile, st.tile + gridDim.x, ... of one phase. The next tile is known early: its token row
 // numbers are fetched one tile ahead and its first batch of loads is issued before the current
 // tile is reduced, which keeps DRAM requests in flight across tile boundaries. A gate/up tile's
 // arrival is signalled one tile late, behind the next tile's reduction barrier (see tile_finish).
-template <int NT, bool GATEUP, int DEPTH, int WARPS>
-__device__ __forceinline__ void stream_run(StreamState<NT, DEPTH>& st, const FusedGroup* sg, int n_groups, int n_tiles,
+template <int NT, bool GATEUP, int DEPTH, int WARPS, class G>
+__device__ __forceinline__ void stream_run(StreamState<NT, DEPTH>& st, const G* sg, int n_groups, int n_tiles,
                                            const __nv_bfloat16* bsrc, int ldb,
                                            const int32_t* __restrict__ row_token, int hidden,
                                            __nv_bfloat16* __restrict__ hbuf, int ld_h, float* __restrict__ yexp,
                                            float (*red2)[WARPS][2 * NT * 4][32], int32_t* counters, int32_t* total,
                                            int total_target, int32_t* err) {
   constexpr bool COH = !GATEUP;  // the down phase reads rows other CTAs wrote in this kernel
+  constexpr bool Q4 = std::is_same<G, FusedGroupQ4>::value;
   if (!st.active) return;
   TileCtx<NT>& t = st.t;
   float acc[2][NT][4];
@@ -653,7 +749,7 @@ __device__ __forceinline__ void stream_run(StreamState<NT, DEPTH>& st, const Fus
   // arrivals a chunk's counter shows when its intermediate rows are complete
   auto target_of = [&](int gi) { return sg[gi].inter / kSplitTileGu; };
   if (!GATEUP) wait_rows_ready(counters, total, t.gi, target_of(t.gi), total_target, st.all_done, err);
-  tile_issue_b<NT, DEPTH, COH>(t, 0, st.b);
+  tile_issue_b<NT, DEPTH, COH, Q4>(t, 0, st.b);
   const int stride = gridDim.x;
   int next = st.tile + stride;
   int pending = -1;  // chunk of the gate/up tile whose arrival is still to be signalled
@@ -666,20 +762,22 @@ __device__ __forceinline__ void stream_run(StreamState<NT, DEPTH>& st, const Fus
     // with the steps DEPTH further on, so a warp always has loads outstanding while it waits.
     constexpr int HALF = DEPTH / 2;
     for (int s0 = 0; s0 < t.s_end; s0 += DEPTH) {
-      tile_compute<NT, DEPTH, 0, HALF>(t, s0, st.a, st.b, acc);
+      if constexpr (Q4) tile_compute_q4<NT, DEPTH, COH, 0, HALF>(t, s0, st.a, st.sz, acc);
+      else tile_compute<NT, DEPTH, 0, HALF>(t, s0, st.a, st.b, acc);
       if (s0 + DEPTH < t.s_end) {
-        tile_issue_a<NT, DEPTH, 0, HALF>(t, s0 + DEPTH, st.a);
-        tile_issue_b<NT, DEPTH, COH, 0, HALF>(t, s0 + DEPTH, st.b);
+        tile_issue_a<NT, DEPTH, Q4, 0, HALF>(t, s0 + DEPTH, st.a, st.sz);
+        tile_issue_b<NT, DEPTH, COH, Q4, 0, HALF>(t, s0 + DEPTH, st.b);
       }
       if (has_next && !rows_loaded) {  // fetch the next tile's token row numbers under this tile's loads
         load_src_rows<NT, GATEUP>(src_row, sg[gi_next], row_token);
         rows_loaded = true;
       }
       if (s0 + HALF < t.s_end) {
-        tile_compute<NT, DEPTH, HALF, HALF>(t, s0, st.a, st.b, acc);
+        if constexpr (Q4) tile_compute_q4<NT, DEPTH, COH, HALF, HALF>(t, s0, st.a, st.sz, acc);
+        else tile_compute<NT, DEPTH, HALF, HALF>(t, s0, st.a, st.b, acc);
         if (s0 + DEPTH + HALF < t.s_end) {
-          tile_issue_a<NT, DEPTH, HALF, HALF>(t, s0 + DEPTH, st.a);
-          tile_issue_b<NT, DEPTH, COH, HALF, HALF>(t, s0 + DEPTH, st.b);
+          tile_issue_a<NT, DEPTH, Q4, HALF, HALF>(t, s0 + DEPTH, st.a, st.sz);
+          tile_issue_b<NT, DEPTH, COH, Q4, HALF, HALF>(t, s0 + DEPTH, st.b);
         }
       }
     }
@@ -688,8 +786,8 @@ __device__ __forceinline__ void stream_run(StreamState<NT, DEPTH>& st, const Fus
     if (has_next) {
       if (!GATEUP) wait_rows_ready(counters, total, gi_next, target_of(gi_next), total_target, st.all_done, err);
       tile_setup<NT, GATEUP, WARPS>(t, sg[gi_next], gi_next, next, src_row, bsrc, ldb, hidden);
-      tile_issue_a<NT, DEPTH>(t, 0, st.a);
-      tile_issue_b<NT, DEPTH, COH>(t, 0, st.b);
+      tile_issue_a<NT, DEPTH, Q4>(t, 0, st.a, st.sz);
+      tile_issue_b<NT, DEPTH, COH, Q4>(t, 0, st.b);
     }
     tile_finish<NT, GATEUP, WARPS>(sg[gi], m0, acc, red2[st.buf], hbuf, ld_h, yexp, hidden, counters, total, pending);
     pending = gi;
@@ -704,11 +802,18 @@ __device__ __forceinline__ void stream_run(StreamState<NT, DEPTH>& st, const Fus
 }
 
 // Chunk table of the launch in shared memory; meta = {chunks, gate/up tiles, down tiles}.
-__device__ __forceinline__ void build_chunk_table(const FusedLaunch& a, FusedGroup* sg, int* meta) {
+template <class G>
+__device__ __forceinline__ void build_chunk_table(const FusedLaunch& a, G* sg, int* meta) {
+  constexpr bool Q4 = std::is_same<G, FusedGroupQ4>::value;
   if (a.groups != nullptr) {
     for (int i = threadIdx.x; i < a.n_groups; i += blockDim.x) {
       const GroupDesc& d = a.groups[i];
-      FusedGroup g;
+      G g;
+      if constexpr (Q4) {
+        g.q_gate = reinterpret_cast<const uint32_t*>(d.q_gate);
+        g.q_up = reinterpret_cast<const uint32_t*>(d.q_up);
+        g.q_down = reinterpret_cast<const uint32_t*>(d.q_down);
+      }
       g.w_gate = reinterpret_cast<const unsigned char*>(d.w_gate);
       g.w_up = reinterpret_cast<const unsigned char*>(d.w_up);
       g.w_down = reinterpret_cast<const unsigned char*>(d.w_down);
@@ -727,6 +832,10 @@ __device__ __forceinline__ void build_chunk_table(const FusedLaunch& a, FusedGro
     }
     return;
   }
+  if constexpr (Q4) {  // uint4 launches are always host-planned
+    if (threadIdx.x == 0) meta[0] = meta[1] = meta[2] = 0;
+    return;
+  }
   const ResidentArgs& r = a.res;
   const int dn_tiles = a.hidden / kSplitTileDn;
   const int slice = r.shared_slice;
@@ -734,7 +843,7 @@ __device__ __forceinline__ void build_chunk_table(const FusedLaunch& a, FusedGro
   const int sh_tiles = r.shared_inter / kSplitTileGu;
   if ((int)threadIdx.x < n_sh) {  // heaviest rows first: the slices of the shared expert
     const int j = threadIdx.x;
-    FusedGroup g;
+    G g{};
     g.w_gate = reinterpret_cast<const unsigned char*>(r.shared_w_gate) + (size_t)j * slice * a.hidden * 2;
     g.w_up = reinterpret_cast<const unsigned char*>(r.shared_w_up) + (size_t)j * slice * a.hidden * 2;
     g.w_down = reinterpret_cast<const unsigned char*>(r.shared_w_down) + (size_t)j * slice * 2;
@@ -764,7 +873,7 @@ __device__ __forceinline__ void build_chunk_table(const FusedLaunch& a, FusedGro
       if (act) {
         const int idx = base + __popc(mask & lt);
         const unsigned char* line = r.pool_base + (size_t)slot * r.line_stride;
-        FusedGroup g;
+        G g{};
         g.w_gate = line + r.off_gate;
         g.w_up = line + r.off_up;
         g.w_down = line + r.off_down;
@@ -786,11 +895,11 @@ __device__ __forceinline__ void build_chunk_table(const FusedLaunch& a, FusedGro
   }
 }
 
-template <int NT, int DEPTH, int WARPS>
+template <int NT, int DEPTH, int WARPS, bool Q4>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS)
 grouped_ffn_fused_kernel(const __grid_constant__ FusedLaunch a) {
   __shared__ float red[2][WARPS][2 * NT * 4][32];  // two reduction buffers, used alternately
-  __shared__ FusedGroup sg[kMaxFusedGroups];
+  __shared__ typename GroupOf<Q4>::type sg[Q4 ? kMaxFusedGroupsQ4 : kMaxFusedGroups];
   __shared__ int meta[3];
   build_chunk_table(a, sg, meta);
   __syncthreads();
@@ -817,7 +926,7 @@ grouped_ffn_fused_kernel(const __grid_constant__ FusedLaunch a) {
 constexpr int kFusedWarps = 8;
 
 // Resident grid of the fused kernel on the current device (0 if cooperative launch is unavailable).
-template <int NT, int DEPTH>
+template <int NT, int DEPTH, bool Q4>
 int fused_grid_size() {
   static int cached[64] = {};
   int dev = 0;
@@ -827,7 +936,7 @@ int fused_grid_size() {
   cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (!coop || sms <= 0 ||
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, grouped_ffn_fused_kernel<NT, DEPTH, kFusedWarps>,
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, grouped_ffn_fused_kernel<NT, DEPTH, kFusedWarps, Q4>,
                                                     kFusedWarps * 32, 0) != cudaSuccess ||
       per_sm <= 0) {
     cached[dev] = -1;
@@ -837,18 +946,23 @@ int fused_grid_size() {
   return cached[dev];
 }
 
-template <int NT, int DEPTH>
+template <int NT, int DEPTH, bool Q4 = false>
 cudaError_t launch_fused(const FusedLaunch& a, int total_tiles, cudaStream_t s) {
-  int grid = fused_grid_size<NT, DEPTH>();
+  int grid = fused_grid_size<NT, DEPTH, Q4>();
   if (grid <= 0) return cudaErrorNotSupported;
   if (total_tiles > 0) grid = min(grid, total_tiles);
   void* args[] = {(void*)&a};
-  return cudaLaunchCooperativeKernel((const void*)grouped_ffn_fused_kernel<NT, DEPTH, kFusedWarps>, dim3(grid),
+  return cudaLaunchCooperativeKernel((const void*)grouped_ffn_fused_kernel<NT, DEPTH, kFusedWarps, Q4>, dim3(grid),
                                      dim3(kFusedWarps * 32), args, 0, s);
 }
 
 cudaError_t launch_fused_rows(const FusedLaunch& a, int max_rows, int total_tiles, cudaStream_t s) {
   return max_rows <= 8 ? launch_fused<1, 4>(a, total_tiles, s) : launch_fused<2, 2>(a, total_tiles, s);
+}
+
+// uint4 experts: a k-step is a whole 128-weight group, so two steps per lane are in flight
+cudaError_t launch_fused_rows_q4(const FusedLaunch& a, int max_rows, int total_tiles, cudaStream_t s) {
+  return max_rows <= 8 ? launch_fused<1, 2, true>(a, total_tiles, s) : launch_fused<2, 2, true>(a, total_tiles, s);
 }
 
 int kc_cap_for(int nt, int maxK) {
@@ -886,6 +1000,31 @@ cudaError_t dispatch_nt(int max_rows, const GroupDesc* groups, const int32_t* ti
   return launch_one<8, NMAT>(groups, tile_group, tiles, bsrc, ldb, row_token, hidden, maxK, hbuf, ld_h, yexp, s);
 }
 
+// Expands one uint4 group-128 matrix [rows, K] into bf16 (for the prefill path, which reads bf16 tiles
+// by TMA): a thread turns one 32-bit word (8 weights: even-k nibbles in the low half, odd-k nibbles in
+// the high half) into 16 bytes of bf16, w = (q - zero) * scale in float32, rounded once.
+__global__ void __launch_bounds__(256)
+dequant_q4_kernel(const uint32_t* __restrict__ packed, const uint32_t* __restrict__ sz, size_t n_words,
+                  int words_per_row, uint4* __restrict__ out) {
+  const int groups_per_row = words_per_row / 16;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += (size_t)gridDim.x * blockDim.x) {
+    const uint32_t w = ldg_stream_u32(packed + i);
+    const size_t row = i / words_per_row;
+    const int wc = (int)(i - row * words_per_row);
+    const uint32_t m = __ldg(sz + row * groups_per_row + wc / 16);
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&m));  // x = scale, y = zero
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float even = ((float)((w >> (4 * j)) & 0xFu) - f.y) * f.x;
+      const float odd = ((float)((w >> (16 + 4 * j)) & 0xFu) - f.y) * f.x;
+      const __nv_bfloat162 pair = __floats2bfloat162_rn(even, odd);
+      o[j] = *reinterpret_cast<const uint32_t*>(&pair);
+    }
+    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 }  // namespace
 
 cudaError_t launch_resident_ffn(const ResidentArgs& r, int32_t* counters, int32_t* err, int max_rows,
@@ -909,7 +1048,7 @@ cudaError_t launch_resident_ffn(const ResidentArgs& r, int32_t* counters, int32_
 
 bool resident_ffn_available(int max_rows) {
   if (max_rows > kSplitMaxRows) return false;
-  return (max_rows <= 8 ? fused_grid_size<1, 4>() : fused_grid_size<2, 2>()) > 0;
+  return (max_rows <= 8 ? fused_grid_size<1, 4, false>() : fused_grid_size<2, 2, false>()) > 0;
 }
 
 cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& info, int quant4,
@@ -922,20 +1061,6 @@ cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& 
   const int32_t* t_dn = reinterpret_cast<const int32_t*>(blob_dev + info.off_tile_dn());
   const int max_rows = info.max_rows;
   cudaError_t e;
-  if (quant4) {
-    // uint4 experts: split-K decode tiles only (the planner keeps chunks at kSplitMaxRows rows)
-    if (max_rows > kSplitMaxRows) return cudaErrorNotSupported;
-    e = (max_rows <= 8) ? launch_q4<1, 2>(groups, t_gu, info.tiles_gu, x, H, row_token, H, hbuf, ld_h, yexp, s)
-                        : launch_q4<2, 2>(groups, t_gu, info.tiles_gu, x, H, row_token, H, hbuf, ld_h, yexp, s);
-    if (e != cudaSuccess) return e;
-    if (mid_event != nullptr) {
-      e = cudaEventRecord(mid_event, s);
-      if (e != cudaSuccess) return e;
-    }
-    return (max_rows <= 8)
-               ? launch_q4<1, 1>(groups, t_dn, info.tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s)
-               : launch_q4<2, 1>(groups, t_dn, info.tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s);
-  }
   if (ffn_launch_is_fused(info, quant4)) {
     if (info.n_desc > kMaxFusedGroups) return cudaErrorInvalidValue;
     FusedLaunch a{};
@@ -953,7 +1078,23 @@ cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& 
     a.yexp = yexp;
     a.hidden = H;
     a.ld_h = ld_h;
-    return launch_fused_rows(a, max_rows, info.tiles_gu + info.tiles_dn, s);
+    const int tiles = info.tiles_gu + info.tiles_dn;
+    return quant4 ? launch_fused_rows_q4(a, max_rows, tiles, s) : launch_fused_rows(a, max_rows, tiles, s);
+  }
+  if (quant4) {
+    // more uint4 chunks than the fused kernel's table holds: split-K decode tiles in two launches
+    // (the planner keeps uint4 chunks at kSplitMaxRows rows)
+    if (max_rows > kSplitMaxRows) return cudaErrorNotSupported;
+    e = (max_rows <= 8) ? launch_q4<1, 2>(groups, t_gu, info.tiles_gu, x, H, row_token, H, hbuf, ld_h, yexp, s)
+                        : launch_q4<2, 2>(groups, t_gu, info.tiles_gu, x, H, row_token, H, hbuf, ld_h, yexp, s);
+    if (e != cudaSuccess) return e;
+    if (mid_event != nullptr) {
+      e = cudaEventRecord(mid_event, s);
+      if (e != cudaSuccess) return e;
+    }
+    return (max_rows <= 8)
+               ? launch_q4<1, 1>(groups, t_dn, info.tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s)
+               : launch_q4<2, 1>(groups, t_dn, info.tiles_dn, hbuf, ld_h, row_token, H, nullptr, ld_h, yexp, s);
   }
   e = dispatch_nt<2>(max_rows, groups, t_gu, info.tiles_gu, x, H, row_token, H, H, hbuf, ld_h, yexp, s);
   if (e != cudaSuccess) return e;
@@ -963,6 +1104,16 @@ cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& 
   }
   return dispatch_nt<1>(max_rows, groups, t_dn, info.tiles_dn, hbuf, ld_h, row_token, H, ld_h, nullptr, ld_h,
                         yexp, s);
+}
+
+cudaError_t launch_dequant_q4(const void* packed, const void* scale_zero, int rows, int K, __nv_bfloat16* out,
+                              cudaStream_t s) {
+  if (rows <= 0 || K <= 0 || K % 128 != 0) return cudaErrorInvalidValue;
+  const size_t n_words = (size_t)rows * (K / 8);
+  const unsigned blocks = (unsigned)std::min<size_t>((n_words + 255) / 256, 148 * 16);
+  dequant_q4_kernel<<<blocks, 256, 0, s>>>((const uint32_t*)packed, (const uint32_t*)scale_zero, n_words, K / 8,
+                                           (uint4*)out);
+  return cudaGetLastError();
 }
 
 }  // namespace pm

@@ -52,25 +52,34 @@ bool tc_prefill_usable(const pm_ctx* c, const pm_layer_weights& w) {
   return true;
 }
 
-int tc_build_maps(pm_ctx* c, const pm_layer_weights& w, int rows_cap, TcMaps* m) {
+bool tc_prefill_usable_q4(const pm_ctx* c, const pm_layer_weights& w) {
+  if (!c->tc_prefill || !w.quant4 || encode_fn() == nullptr) return false;
+  return w.hidden % 128 == 0 && w.inter % 128 == 0 && w.shared_inter % 64 == 0;
+}
+
+namespace {
+
+// Maps of the token rows, of a slab of bf16 expert lines (`lines` lines `stride` bytes apart, the
+// three matrices at the given addresses of line 0) and of the layer's shared expert.
+int build_maps(pm_ctx* c, const pm_layer_weights& w, int rows_cap, const unsigned char* gate0,
+               const unsigned char* up0, const unsigned char* down0, uint64_t stride, uint64_t lines, TcMaps* m) {
   const uint64_t H = w.hidden, I = w.inter;
   int rc = encode_2d(&m->a_x, c->d_xperm, H, (uint64_t)rows_cap, H);
   if (rc != PM_OK) return rc;
   rc = encode_2d(&m->a_h, c->d_hbuf, (uint64_t)c->ws_inter, (uint64_t)rows_cap, (uint64_t)c->ws_inter);
   if (rc != PM_OK) return rc;
-  const uint64_t lines = (uint64_t)c->n_lines;
   {
     cuuint64_t dims[3] = {H, I, lines};
-    cuuint64_t strides[2] = {H * 2, (cuuint64_t)c->line_stride};
-    rc = encode(&m->slab_gate, c->slab + c->param_offset[c->role_gate], 3, dims, strides);
+    cuuint64_t strides[2] = {H * 2, (cuuint64_t)stride};
+    rc = encode(&m->slab_gate, gate0, 3, dims, strides);
     if (rc != PM_OK) return rc;
-    rc = encode(&m->slab_up, c->slab + c->param_offset[c->role_up], 3, dims, strides);
+    rc = encode(&m->slab_up, up0, 3, dims, strides);
     if (rc != PM_OK) return rc;
   }
   {
     cuuint64_t dims[3] = {I, H, lines};
-    cuuint64_t strides[2] = {I * 2, (cuuint64_t)c->line_stride};
-    rc = encode(&m->slab_down, c->slab + c->param_offset[c->role_down], 3, dims, strides);
+    cuuint64_t strides[2] = {I * 2, (cuuint64_t)stride};
+    rc = encode(&m->slab_down, down0, 3, dims, strides);
     if (rc != PM_OK) return rc;
   }
   if (w.shared_inter > 0) {
@@ -87,6 +96,19 @@ int tc_build_maps(pm_ctx* c, const pm_layer_weights& w, int rows_cap, TcMaps* m)
     m->sh_down = m->slab_down;
   }
   return PM_OK;
+}
+
+}  // namespace
+
+int tc_build_maps(pm_ctx* c, const pm_layer_weights& w, int rows_cap, TcMaps* m) {
+  return build_maps(c, w, rows_cap, c->slab + c->param_offset[c->role_gate], c->slab + c->param_offset[c->role_up],
+                    c->slab + c->param_offset[c->role_down], (uint64_t)c->line_stride, (uint64_t)c->n_lines, m);
+}
+
+int tc_build_maps_q4(pm_ctx* c, const pm_layer_weights& w, int rows_cap, TcMaps* m) {
+  const size_t mat = (size_t)w.inter * w.hidden * 2;
+  return build_maps(c, w, rows_cap, c->q4_scratch, c->q4_scratch + mat, c->q4_scratch + 2 * mat,
+                    (uint64_t)c->q4_scratch_stride, (uint64_t)c->q4_scratch_lines, m);
 }
 
 // Tiles of one segment: every 128-row block of every group times every 128-column block of the

@@ -259,34 +259,115 @@ def launch(model: torch.nn.Module):
 
 
 # ----------------------------------------------------------------------------- transformers loaders
+def _loader_is_static(cls) -> bool:
+    """transformers 5.x: `_load_pretrained_model(model, state_dict, checkpoint_files, load_config, ...)`
+    is a staticmethod and the device map travels inside `load_config`; 4.x: a classmethod
+    `(cls, model, ..., device_map=...)` that returns the model first."""
+    import inspect
+    return isinstance(inspect.getattr_static(cls, "_load_pretrained_model"), staticmethod)
+
+
+def _single_device(device_map):
+    if isinstance(device_map, (str, int, torch.device)):
+        device_map = {"": device_map}
+    assert device_map is not None and len(device_map) == 1 and "" in device_map, "only support single device"
+    return device_map[""]
+
+
+def _wrap_loader(PreTrainedModel, after_load):
+    """Replaces `_load_pretrained_model` by one that loads every tensor on the CPU and then calls
+    `after_load(model, device)`. Works for both loader generations."""
+    import dataclasses
+    old = PreTrainedModel._old_load_pretrained_model
+    if _loader_is_static(PreTrainedModel):
+        @staticmethod
+        @functools.wraps(old)
+        def load_pretrained_model(model, state_dict, checkpoint_files, load_config, *args, **kwargs):
+            device = "cpu"
+            if load_config.device_map is not None:     # without one the static loader stays on the CPU anyway
+                device = _single_device(load_config.device_map)
+                load_config = dataclasses.replace(load_config, device_map={"": "cpu"})
+            ret = old(model, state_dict, checkpoint_files, load_config, *args, **kwargs)
+            model._promoe_target_device = device
+            after_load(model, device)
+            return ret
+    else:
+        @classmethod
+        @functools.wraps(old.__func__)
+        def load_pretrained_model(cls, *args, **kwargs):
+            device = _single_device(kwargs.get("device_map"))
+            kwargs["device_map"] = {"": "cpu"}
+            ret = old.__func__(cls, *args, **kwargs)
+            model = ret[0] if isinstance(ret, tuple) else ret
+            model._promoe_target_device = device
+            after_load(model, device)
+            return ret
+    PreTrainedModel._load_pretrained_model = load_pretrained_model
+
+
+def _inject_loaded(model, device="cuda", **sparse_cache_kwargs):
+    """Per-expert modules (the reference's fork layout): inject_model. Fused expert tensors (stock
+    transformers 5.x): the adapter for that layout, which takes the subset of the options it knows."""
+    from ..hf_fused import find_moe_blocks, inject_hf_fused_model
+    if find_moe_blocks(model):
+        known = ("cache_rate", "cache_policy", "num_predict_expert_per_layer", "reorder_experts", "early_preempt",
+                 "chunk_prefetch", "per_layer_cache", "promote_hit_in_prefetch")
+        opts = {k: v for k, v in sparse_cache_kwargs.items() if k in known and v is not None}
+        inject_hf_fused_model(model, device=device, **opts)
+        model._promoe_fused_layout = True
+    else:
+        inject_model(model, **sparse_cache_kwargs, launch_now=False)
+
+
 def hack_transformers(**sparse_cache_kwargs):
     """Makes `from_pretrained` load the checkpoint on the CPU, inject the cache, then launch
-    (utils/__init__.py:369-392)."""
+    (utils/__init__.py:369-392). The injection runs once the model is complete: inside the loader for
+    the 4.x classmethod (as the reference does), after `from_pretrained` has finalised the weights
+    (tied weights, missing-key initialisation) for the 5.x static loader. There the caller's
+    single-device `device_map` is taken out of the call (5.x loads on the CPU without one, and needs
+    no accelerate for that) and the rest of the model is moved to that device after the injection."""
     from transformers.modeling_utils import PreTrainedModel
     if hasattr(PreTrainedModel, "_old_load_pretrained_model"):
         return
-    PreTrainedModel._old_load_pretrained_model = PreTrainedModel._load_pretrained_model
-    PreTrainedModel._old_from_pretrained = PreTrainedModel.from_pretrained
+    static = _loader_is_static(PreTrainedModel)
+    PreTrainedModel._old_load_pretrained_model = inspect_static(PreTrainedModel, "_load_pretrained_model")
+    PreTrainedModel._old_from_pretrained = inspect_static(PreTrainedModel, "from_pretrained")
+    if not static:
+        _wrap_loader(PreTrainedModel, lambda model, device: _inject_loaded(model, device, **sparse_cache_kwargs))
+    old_from = PreTrainedModel._old_from_pretrained.__func__
 
     @classmethod
-    @functools.wraps(PreTrainedModel._old_load_pretrained_model.__func__)
-    def load_pretrained_model(cls, *args, **kwargs):
-        dm = kwargs.get("device_map")
-        assert dm is not None and len(dm) == 1 and "" in dm, "only support single device"
-        kwargs["device_map"] = {"": "cpu"}
-        ret = PreTrainedModel._old_load_pretrained_model.__func__(cls, *args, **kwargs)
-        inject_model(ret[0] if isinstance(ret, tuple) else ret, **sparse_cache_kwargs, launch_now=False)
-        return ret
-
-    @classmethod
-    @functools.wraps(PreTrainedModel._old_from_pretrained.__func__)
+    @functools.wraps(old_from)
     def from_pretrained(cls, *args, **kwargs):
-        model = PreTrainedModel._old_from_pretrained.__func__(cls, *args, **kwargs)
-        launch(model)
-        return model
+        if static:
+            device = _single_device(kwargs.pop("device_map", None))
+        out = old_from(cls, *args, **kwargs)
+        model = out[0] if isinstance(out, tuple) else out
+        if static:
+            _inject_loaded(model, device, **sparse_cache_kwargs)
+            model.to(device)
+        if not getattr(model, "_promoe_fused_layout", False):
+            launch(model)
+        return out
 
-    PreTrainedModel._load_pretrained_model = load_pretrained_model
     PreTrainedModel.from_pretrained = from_pretrained
+
+
+def unhack_transformers():
+    """Restores the loaders that hack_transformers / hack_transformers_um replaced."""
+    from transformers.modeling_utils import PreTrainedModel
+    if hasattr(PreTrainedModel, "_old_load_pretrained_model"):
+        PreTrainedModel._load_pretrained_model = inspect_static(PreTrainedModel, "_old_load_pretrained_model")
+        del PreTrainedModel._old_load_pretrained_model
+    if hasattr(PreTrainedModel, "_old_from_pretrained"):
+        PreTrainedModel.from_pretrained = inspect_static(PreTrainedModel, "_old_from_pretrained")
+        del PreTrainedModel._old_from_pretrained
+
+
+def inspect_static(cls, name):
+    """The attribute as stored on the class (keeps staticmethod / classmethod wrappers)."""
+    import inspect
+    return inspect.getattr_static(cls, name)
 
 
 def inject_model_um(model, model_id=None):
@@ -311,16 +392,5 @@ def hack_transformers_um():
     from transformers.modeling_utils import PreTrainedModel
     if hasattr(PreTrainedModel, "_old_load_pretrained_model"):
         return
-    PreTrainedModel._old_load_pretrained_model = PreTrainedModel._load_pretrained_model
-
-    @classmethod
-    @functools.wraps(PreTrainedModel._old_load_pretrained_model.__func__)
-    def load_pretrained_model(cls, *args, **kwargs):
-        dm = kwargs.get("device_map")
-        assert dm is not None and len(dm) == 1 and "" in dm, "only support single device"
-        kwargs["device_map"] = {"": "cpu"}
-        ret = PreTrainedModel._old_load_pretrained_model.__func__(cls, *args, **kwargs)
-        inject_model_um(ret[0] if isinstance(ret, tuple) else ret)
-        return ret
-
-    PreTrainedModel._load_pretrained_model = load_pretrained_model
+    PreTrainedModel._old_load_pretrained_model = inspect_static(PreTrainedModel, "_load_pretrained_model")
+    _wrap_loader(PreTrainedModel, lambda model, device: inject_model_um(model))

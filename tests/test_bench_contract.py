@@ -31,9 +31,16 @@ def test_roofline_and_config_helpers():
     r = bench.roofline_entry(prof, 0.0, 0.0, 4000.0, 6553.6, "measured")
     assert r["bound"] == "hbm" and r["unit"] == "GB/s" and abs(r["frac"] - 4000.0 / 6553.6) < 1e-12
     assert r["traffic"] > r["bytes_per_launch"] and r["launches"] == 10 and abs(r["avg_launch_us"] - 50.0) < 1e-9
-    prof2 = dict(prof, fused_launches=0, ffn_launches=4, gateup_ms=0.2, down_ms=0.1)
-    r2 = bench.roofline_entry(prof2, 3000.0, 2000.0, 0.0, 6553.6, "measured")
-    assert r2["achieved"] == 3000.0 and r2["down_kernel"]["achieved"] == 2000.0
+    # launch pairs only: weight bytes of both launches over the time of both
+    prof2 = dict(prof, fused_launches=0, fused_ms=0.0, ffn_launches=4, gateup_ms=0.2, down_ms=0.1,
+                 gateup_bytes=600_000_000, down_bytes=300_000_000)
+    r2 = bench.roofline_entry(prof2, 3000.0, 3000.0, 0.0, 6553.6, "measured")
+    assert abs(r2["achieved"] - 3000.0) < 1e-6 and r2["gateup_gbs"] == 3000.0 and r2["traffic"] is None
+    # both kinds: the one with more device time is reported, the other rides along
+    prof3 = dict(prof2, fused_launches=2, fused_ms=0.1, fused_bytes=400_000_000)
+    r3 = bench.roofline_entry(prof3, 3000.0, 3000.0, 4000.0, 6553.6, "measured")
+    assert "launch pair" in r3["kernel"] and abs(r3["share_of_ffn_time"] - 0.75) < 1e-9
+    assert r3["other_kernel"]["achieved"] == 4000.0
     c = bench.workload_config(synth.CONFIGS["c2"], 4, False)
     assert c["batch_per_gpu"] == 2 and c["global_batch"] == 8 and "expert parallel" in c["parallelism"]
     peak, src = bench.measured_peak_gbs()

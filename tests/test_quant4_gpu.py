@@ -98,6 +98,22 @@ def test_q4_fused_layer_mixtral_like(lib):
             ref, _, _ = model.oracle_forward(l, x, report_experts=lambda u: np.asarray(oc.report_layer(l, u)))
             got = y.float().cpu().numpy()
             np.testing.assert_allclose(got, ref, rtol=RTOL_Q4, atol=RTOL_Q4 * np.abs(ref).max() * 0.25)
+    assert int(cache.get("q4_expanded")) == 0          # decode batches stay on the split-K tiles
+    # a prompt pass: 640 tokens x top-2 over 8 experts = 160 rows per expert on average, so every segment's
+    # experts are expanded to bf16 once and run on the tensor cores
+    T = 640
+    x = om.bf16_round(rng.standard_normal((T, model.H)).astype(np.float32))
+    cache.set("seq_len", T)
+    for l in range(model.L):
+        y = cache.forward(l, dev_bf16(x))
+        torch.cuda.synchronize()
+        ids, _ = cache.last_routing(l, T, model.k)
+        ref_ids, _ = model.canonical_routing(l, x)
+        assert np.array_equal(ids, ref_ids.astype(np.int32))
+        ref, _, _ = model.oracle_forward(l, x, report_experts=lambda u: np.asarray(oc.report_layer(l, u)))
+        got = y.float().cpu().numpy()
+        np.testing.assert_allclose(got, ref, rtol=RTOL_Q4, atol=RTOL_Q4 * np.abs(ref).max() * 0.25)
+    assert int(cache.get("q4_expanded")) >= model.E * model.L and int(cache.get("tc_launches")) >= model.L
     assert cache.events() == oc.events
     cache.close()
 

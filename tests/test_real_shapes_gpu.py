@@ -171,5 +171,6 @@ def test_c3_mixtral_uint4_decode_and_prefill(lib):
     order = np.asarray(oc.report_layer(0, om.unique_sorted_experts(ref_ids)))
     ref = om.moe_block_forward_f32(x, ref_ids, ref_w, model.experts[0], expert_order=order)
     check(y, ref, RTOL_Q4)
+    assert int(cache.get("q4_expanded")) >= E      # the prompt pass ran on the tensor cores from expanded weights
     assert cache.events() == oc.events
     cache.close()
