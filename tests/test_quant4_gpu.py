@@ -27,7 +27,10 @@ def q4_expert(rng, H, I):
 
 
 @pytest.mark.parametrize("H,inters,rows", [(128, [128], [1]), (256, [128, 256], [5, 8]),
-                                           (1024, [512, 512, 1024], [3, 16, 9]), (4096, [1792], [2])])
+                                           (1024, [512, 512, 1024], [3, 16, 9]), (4096, [1792], [2]),
+                                           # 132 chunks of 16 rows: more than the one-launch kernel's chunk
+                                           # table holds, so the gate/up + down launch pair runs
+                                           (128, [128], [2100])])
 def test_q4_ffn_matches_oracle(lib, H, inters, rows):
     rng = np.random.default_rng(3 + H)
     T = 16
