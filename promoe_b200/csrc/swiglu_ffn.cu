@@ -434,7 +434,7 @@ struct TileCtx {
   const unsigned char* a_ptr[4];
   const unsigned char* b_ptr[NT];
   const uint32_t* sz_ptr[4];  // uint4 experts only
-  int s_end;  // this warp's k-steps; a row without a token has b_ptr == nullptr
+  int s_end;  // this warp's k-steps
   int gi;     // chunk index
   int m0;     // first weight row of the tile
 };
@@ -456,7 +456,10 @@ __device__ __forceinline__ void load_src_rows(int (&src_row)[NT], const FusedGro
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int n = nt * 8 + g;
-    src_row[nt] = (n < d.rows) ? (GATEUP ? row_token[d.row_start + n] : d.row_start + n) : -1;
+    // n-tile slots past the chunk's last row repeat that row: their output columns are never stored,
+    // and a valid address spares every token load a null check
+    const int nn = min(n, d.rows - 1);
+    src_row[nt] = GATEUP ? row_token[d.row_start + nn] : d.row_start + nn;
   }
 }
 
@@ -496,8 +499,7 @@ __device__ __forceinline__ void tile_setup(TileCtx<NT>& t, const G& d, int gi, i
   const size_t col_b = Q4 ? (size_t)first * 256 + q * 64 : col;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
-    t.b_ptr[nt] = src_row[nt] >= 0 ? reinterpret_cast<const unsigned char*>(bsrc + (size_t)src_row[nt] * ldb) + col_b
-                                   : nullptr;
+    t.b_ptr[nt] = reinterpret_cast<const unsigned char*>(bsrc + (size_t)src_row[nt] * ldb) + col_b;
 }
 
 // The DEPTH register slots of a lane hold the k-steps s0 .. s0 + DEPTH - 1 of the tile; the helpers
@@ -528,7 +530,7 @@ __device__ __forceinline__ void tile_issue_b(const TileCtx<NT>& t, int s0, uint4
         const size_t off = (size_t)(s0 + d) * 64;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
-          b[d][nt] = t.b_ptr[nt] != nullptr ? load_b<COHERENT_B>(t.b_ptr[nt] + off) : make_uint4(0, 0, 0, 0);
+          b[d][nt] = load_b<COHERENT_B>(t.b_ptr[nt] + off);
       }
     }
   }
@@ -575,8 +577,7 @@ __device__ __forceinline__ void tile_compute_q4(const TileCtx<NT>& t, int s0, co
         uint4 bv[NT];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
-          bv[nt] = t.b_ptr[nt] != nullptr ? load_b<COHERENT_B>(t.b_ptr[nt] + (size_t)(s0 + d) * 256 + v * 16)
-                                          : make_uint4(0, 0, 0, 0);
+          bv[nt] = load_b<COHERENT_B>(t.b_ptr[nt] + (size_t)(s0 + d) * 256 + v * 16);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {  // nibble pairs {0,1} go with b.x, b.y; pairs {2,3} with b.z, b.w
           // each word is unpacked once and used for every n-tile
