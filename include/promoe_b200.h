@@ -356,6 +356,9 @@ int pm_k_combine(const float* yexp, const int32_t* pos, const float* topk_w, int
 int pm_k_predictor_mlp(const void* x, int B, int H, const void* w1, const float* b1, int d,
                        const void* w2, const float* b2, int E, float* hidden_scratch, float* scores,
                        void* stream);
+/* out[r] = id of the r-th best of scores[0 .. width), r < n: descending score, equal scores in
+ * ascending id (rank_experts, src/cpp_worker/predictor.hpp:24-28, ranks the same way on the host). */
+int pm_k_rank_topn(const float* scores, int width, int n, int32_t* out, void* stream);
 
 #ifdef __cplusplus
 }

@@ -119,6 +119,7 @@ SIGNATURES = {
     "pm_k_ep_unpack": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "pm_k_combine": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
     "pm_k_predictor_mlp": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp]),
+    "pm_k_rank_topn": (_i, [_vp, _i, _i, _vp, _vp]),
 }
 _RAW = {"pm_version", "pm_last_error", "pm_k_swiglu_ffn_scratch_bytes", "pm_k_swiglu_ffn_static_capacity"}
 

@@ -218,4 +218,12 @@ int pm_k_predictor_mlp(const void* x, int B, int H, const void* w1, const float*
   return PM_OK;
 }
 
+int pm_k_rank_topn(const float* scores, int width, int n, int32_t* out, void* stream) {
+  if (width <= 0 || n < 0 || n > width || width > 9000) return fail(PM_ERR_INVALID, "rank_topn: bad sizes");
+  if (n == 0) return PM_OK;
+  if (!scores || !out) return fail(PM_ERR_INVALID, "rank_topn: null pointer");
+  PM_CUDA(launch_rank_topn(scores, width, n, out, (cudaStream_t)stream));
+  return PM_OK;
+}
+
 }  // extern "C"

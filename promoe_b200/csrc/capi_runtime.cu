@@ -77,6 +77,8 @@ int pm_ctx_get(pm_ctx* ctx, const char* key, char* buf, size_t cap) {
   else if (k == "seq_len") v = std::to_string(ctx->seq_len);
   else if (k == "tc_launches") v = std::to_string(ctx->tc_launches);
   else if (k == "q4_expanded") v = std::to_string(ctx->q4_expanded);
+  else if (k == "topn_launches") v = std::to_string(ctx->topn_launches);
+  else if (k == "device_topn") v = ctx->device_topn ? "1" : "0";
   else if (k == "tc_error") {
     int32_t code = 0;
     if (ctx->have_last_stream) cudaStreamSynchronize(ctx->last_stream);
@@ -114,6 +116,10 @@ int pm_ctx_set(pm_ctx* ctx, const char* key, const char* value) {
   }
   if (k == "tc_prefill") {
     ctx->tc_prefill = (v == "1" || v == "true" || v == "True" || v == "on");
+    return PM_OK;
+  }
+  if (k == "device_topn") {  // rank the predictor scores on the device (default) or on the host
+    ctx->device_topn = (v == "1" || v == "true" || v == "True" || v == "on");
     return PM_OK;
   }
   if (k == "shared_arena") {

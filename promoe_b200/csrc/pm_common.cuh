@@ -172,6 +172,9 @@ cudaError_t launch_prefill_ffn(const TcMaps& maps, const TcGroup* groups_dev, co
                                const TcTile* tiles_dn_dev, int n_dn, int hidden, __nv_bfloat16* hbuf, int ld_h,
                                float* yexp, int32_t* err_dev, cudaStream_t s, cudaEvent_t mid_event);
 
+// out[r] = index of the r-th best of scores[0 .. width) (descending, ties to the lower index), r < n.
+cudaError_t launch_rank_topn(const float* scores, int width, int n, int32_t* out, cudaStream_t s);
+
 cudaError_t launch_predictor_mlp(const __nv_bfloat16* x, int B, int H, const __nv_bfloat16* w1,
                                  const float* b1, int D, const __nv_bfloat16* w2, const float* b2,
                                  int E, float* hidden_scratch, float* scores, cudaStream_t s);

@@ -110,7 +110,56 @@ predictor_fc2_kernel(const float* __restrict__ hidden, int B, int D,
   if (lane == 0) scores[e] = acc + (b2 != nullptr ? (float)B * b2[e] : 0.f);
 }
 
+// The n best of `width` scores in rank order (descending score, ties to the lower id: what a stable
+// descending sort gives, predictor.hpp:24-28 of the reference). One warp: every round each lane
+// scans its strided share of the scores that are still in, the warp agrees on the best, lane 0
+// writes it and takes it out.
+__global__ void __launch_bounds__(32)
+rank_topn_kernel(const float* __restrict__ scores, int width, int n, int32_t* __restrict__ out) {
+  extern __shared__ float sc[];  // [width] scores, then [width] taken flags as floats' bytes
+  unsigned char* taken = reinterpret_cast<unsigned char*>(sc + width);
+  const int lane = threadIdx.x;
+  for (int i = lane; i < width; i += 32) {
+    sc[i] = scores[i];
+    taken[i] = 0;
+  }
+  __syncwarp();
+  for (int r = 0; r < n; ++r) {
+    float best = 0.f;
+    int arg = -1;
+    for (int i = lane; i < width; i += 32) {
+      if (!taken[i] && (arg < 0 || sc[i] > best)) {  // ascending i: the first of equal scores stays
+        best = sc[i];
+        arg = i;
+      }
+    }
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, m);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, m);
+      if (oa >= 0 && (arg < 0 || ob > best || (ob == best && oa < arg))) {
+        best = ob;
+        arg = oa;
+      }
+    }
+    if (lane == 0) {
+      out[r] = arg;
+      if (arg >= 0) taken[arg] = 1;
+    }
+    __syncwarp();
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_rank_topn(const float* scores, int width, int n, int32_t* out, cudaStream_t s) {
+  if (n <= 0 || width <= 0) return cudaSuccess;
+  if (n > width) n = width;
+  const size_t smem = (size_t)width * 5;
+  if (smem > 48 * 1024) return cudaErrorInvalidValue;
+  rank_topn_kernel<<<1, 32, smem, s>>>(scores, width, n, out);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_predictor_mlp(const __nv_bfloat16* x, int B, int H, const __nv_bfloat16* w1,
                                  const float* b1, int D, const __nv_bfloat16* w2, const float* b2,

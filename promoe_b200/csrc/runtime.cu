@@ -234,18 +234,46 @@ Stage stage_of(pm_ctx* c) {
 // src/cpp_worker/worker.cpp:6-77). `scores` covers `width` experts of which this context holds
 // [first, first + num_expert): the `top` best of the whole list are taken and those this context
 // holds are prefetched in rank order (width = num_expert, first = 0: the plain single-context case).
-int issue_prediction(pm_ctx* c, int dst, const float* scores, int width = 0, int first = 0, int top = -1) {
+constexpr int kTopCap = 64;  // most ids the device-side ranking returns per predicted layer
+
+// How many of the best-ranked experts a prediction for layer `dst` takes.
+int prediction_count(const pm_ctx* c, int dst, int width, int top) {
+  int n = std::min(top >= 0 ? top : c->cfg.num_predict_expert_per_layer, width);
+  if (dst == 0 && c->cfg.limit_layer_0_num_predict != -1) n = std::min(n, c->cfg.limit_layer_0_num_predict);
+  return n;
+}
+
+bool topn_on_device(const pm_ctx* c, int n, int width) { return c->device_topn && n > 0 && n <= kTopCap && width <= 9000; }
+
+int ensure_topn(pm_ctx* c) {
+  if (c->d_topn != nullptr) return PM_OK;
+  const size_t bytes = (size_t)2 * c->cfg.num_layer * kTopCap * 4;
+  PM_CUDA(cudaMalloc((void**)&c->d_topn, bytes));
+  PM_CUDA(cudaHostAlloc((void**)&c->h_topn, bytes, cudaHostAllocDefault));
+  return PM_OK;
+}
+
+// `ranked`: the ids the device ranked best (prediction_count of them), or nullptr to rank here.
+int issue_prediction(pm_ctx* c, int dst, const float* scores, int width = 0, int first = 0, int top = -1,
+                     const int32_t* ranked = nullptr) {
   const int E = c->cfg.num_expert;
   if (width <= 0) width = E;
   if (c->cfg.cache_policy == "nn") {
     std::string err = c->eng->update_priority(scores + first, 1, dst);
     if (!err.empty()) return fail(PM_ERR_STATE, err);
   }
-  int n = std::min(top >= 0 ? top : c->cfg.num_predict_expert_per_layer, width);
-  if (dst == 0 && c->cfg.limit_layer_0_num_predict != -1) n = std::min(n, c->cfg.limit_layer_0_num_predict);
-  std::vector<int64_t> order(width);
-  for (int i = 0; i < width; ++i) order[i] = i;
-  std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return scores[a] > scores[b]; });
+  const int n = prediction_count(c, dst, width, top);
+  std::vector<int64_t> order;
+  if (ranked != nullptr) {
+    for (int i = 0; i < n; ++i) {
+      if (ranked[i] < 0 || ranked[i] >= width) return fail(PM_ERR_STATE, "device ranking returned an id out of range");
+      order.push_back(ranked[i]);
+    }
+  } else {
+    order.resize(width);
+    for (int i = 0; i < width; ++i) order[i] = i;
+    std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return scores[a] > scores[b]; });
+  }
   std::vector<int64_t> mine;
   for (int i = 0; i < n; ++i)
     if (order[i] >= first && order[i] < first + E) mine.push_back(order[i] - first);
@@ -276,6 +304,14 @@ int launch_predictors(pm_ctx* c, int src, const __nv_bfloat16* x, int B, int H, 
     PM_CUDA(launch_predictor_mlp(x, B, H, (const __nv_bfloat16*)p.w1, p.b1, p.d, (const __nv_bfloat16*)p.w2,
                                  p.b2, E, c->d_pred_hidden, c->d_scores + (size_t)dst * E, s));
     c->kernel_launches += 2;
+    const int n = prediction_count(c, dst, E, -1);
+    if (topn_on_device(c, n, E)) {  // rank on the device: the host reads n ids instead of sorting E scores
+      int rc = ensure_topn(c);
+      if (rc != PM_OK) return rc;
+      PM_CUDA(launch_rank_topn(c->d_scores + (size_t)dst * E, E, n, c->d_topn + (size_t)dst * kTopCap, s));
+      c->kernel_launches += 1;
+      c->topn_launches += 1;
+    }
     dsts->push_back(dst);
   }
   return PM_OK;
@@ -862,13 +898,40 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
     rc = launch_predictors(c, layer, x, T, H, s, &pred_dsts);
     if (rc != PM_OK) return rc;
   }
+  const bool routed_pred = routed && routed->n_pred > 0 && routed->pred_scores != nullptr && c->seq_len == 1;
+  const int L_all = c->cfg.num_layer;
+  bool routed_ranked = false;
+  if (routed_pred && routed->n_pred <= L_all) {
+    routed_ranked = true;
+    for (int i = 0; i < routed->n_pred; ++i) {
+      const int dst = routed->pred_layers[i];
+      if (dst < 0 || dst >= L_all) return fail(PM_ERR_INVALID, "predicted layer out of range");
+      if (!topn_on_device(c, prediction_count(c, dst, routed->pred_width, routed->pred_top), routed->pred_width))
+        routed_ranked = false;
+    }
+    if (routed_ranked) {
+      rc = ensure_topn(c);
+      if (rc != PM_OK) return rc;
+      for (int i = 0; i < routed->n_pred; ++i) {
+        const int n = prediction_count(c, routed->pred_layers[i], routed->pred_width, routed->pred_top);
+        PM_CUDA(launch_rank_topn(routed->pred_scores + (size_t)i * routed->pred_width, routed->pred_width, n,
+                                 c->d_topn + (size_t)(L_all + i) * kTopCap, s));
+        c->kernel_launches += 1;
+        c->topn_launches += 1;
+      }
+    }
+  }
   // The router's results travel to the host on a side stream, so the resident experts can start on
   // the compute stream at once instead of waiting for the host's decisions about the misses.
   PM_CUDA(cudaEventRecord(c->routed_event, s));
   cudaStream_t rb = c->readback_stream;
   PM_CUDA(cudaStreamWaitEvent(rb, c->routed_event, 0));
-  const bool routed_pred = routed && routed->n_pred > 0 && routed->pred_scores != nullptr && c->seq_len == 1;
-  if (routed_pred) {
+  const bool own_ranked = !pred_dsts.empty() && c->d_topn != nullptr &&
+                          topn_on_device(c, prediction_count(c, pred_dsts.back(), E, -1), E);
+  if (routed_ranked || own_ranked)
+    PM_CUDA(cudaMemcpyAsync(c->h_topn, c->d_topn, (size_t)2 * L_all * kTopCap * 4, cudaMemcpyDeviceToHost, rb));
+  const bool need_scores = c->cfg.cache_policy == "nn";  // the NN policy updates its priorities from the scores
+  if (routed_pred && (need_scores || !routed_ranked)) {
     // scores computed elsewhere (the expert-parallel sources): they ride to the host with the counts
     const size_t bytes = (size_t)routed->n_pred * routed->pred_width * 4;
     if (routed->n_pred > c->cfg.num_layer) return fail(PM_ERR_INVALID, "more predicted layers than layers");
@@ -882,7 +945,7 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
       c->h_routed_scores_cap = bytes;
     }
     PM_CUDA(cudaMemcpyAsync(c->h_routed_scores, routed->pred_scores, bytes, cudaMemcpyDeviceToHost, rb));
-  } else if (!pred_dsts.empty()) {
+  } else if (!pred_dsts.empty() && (need_scores || !own_ranked)) {
     PM_CUDA(cudaMemcpyAsync(st.scores, c->d_scores, (size_t)c->cfg.num_layer * E * 4, cudaMemcpyDeviceToHost, rb));
   }
   PM_CUDA(cudaMemcpyAsync(st.counts, c->d_counts, (size_t)(2 * E + 3) * 4, cudaMemcpyDeviceToHost, rb));
@@ -984,13 +1047,17 @@ int rt_forward(pm_ctx* c, int layer, const void* xv, int T, void* yv, cudaStream
   // Prediction made from this layer's input comes before the layer's own report, as in the
   // reference (report_moe_layer_logits precedes report_one_layer for the same index).
   for (int dst : pred_dsts) {
-    rc = issue_prediction(c, dst, st.scores + (size_t)dst * E);
+    const bool dev = own_ranked && topn_on_device(c, prediction_count(c, dst, E, -1), E);
+    rc = issue_prediction(c, dst, st.scores + (size_t)dst * E, 0, 0, -1,
+                          dev ? c->h_topn + (size_t)dst * kTopCap : nullptr);
     if (rc != PM_OK) return rc;
   }
   if (routed_pred)
     for (int i = 0; i < routed->n_pred; ++i) {
-      rc = issue_prediction(c, routed->pred_layers[i], c->h_routed_scores + (size_t)i * routed->pred_width,
-                            routed->pred_width, routed->pred_first, routed->pred_top);
+      rc = issue_prediction(c, routed->pred_layers[i],
+                            c->h_routed_scores != nullptr ? c->h_routed_scores + (size_t)i * routed->pred_width : nullptr,
+                            routed->pred_width, routed->pred_first, routed->pred_top,
+                            routed_ranked ? c->h_topn + (size_t)(L_all + i) * kTopCap : nullptr);
       if (rc != PM_OK) return rc;
     }
 
@@ -1216,6 +1283,8 @@ pm_ctx::~pm_ctx() {
   if (h_stage) cudaFreeHost(h_stage);
   if (h_tc_plan) cudaFreeHost(h_tc_plan);
   if (q4_scratch) cudaFree(q4_scratch);
+  if (d_topn) cudaFree(d_topn);
+  if (h_topn) cudaFreeHost(h_topn);
   if (h_routed_scores) cudaFreeHost(h_routed_scores);
   if (slab_built) {
     if (slab_vmm) {

@@ -145,6 +145,12 @@ struct pm_ctx {
   bool xperm_ready = false, tc_maps_ready = false;  // per layer call
   pm::TcMaps tc_maps;
   int64_t tc_launches = 0;
+  // device-side ranking of the predictor scores: [2 * num_layer][kTopCap] ids (own predictions by
+  // target layer, then the caller-supplied score rows of the routed-rows form)
+  bool device_topn = true;
+  int32_t* d_topn = nullptr;
+  int32_t* h_topn = nullptr;
+  int64_t topn_launches = 0;
   // uint4 experts on the prefill path: the packed weights of a segment's experts are expanded into
   // this bf16 slab (one line per expert of the segment) and the tensor-core kernels read it
   unsigned char* q4_scratch = nullptr;

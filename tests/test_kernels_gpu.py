@@ -224,3 +224,20 @@ def test_predictor_mlp_matches_oracle(lib, B, H, D, E):
     ref = om.predictor_scores(x, w1, b1, w2, b2)
     np.testing.assert_allclose(sc.cpu().numpy(), ref, rtol=1e-3, atol=1e-3)
     assert np.array_equal(om.rank_experts(sc.cpu().numpy().astype(np.float64), 4), om.rank_experts(ref, 4))
+
+
+@pytest.mark.parametrize("width,n", [(60, 4), (64, 6), (8, 8), (480, 12), (1000, 64)])
+def test_rank_topn_matches_a_stable_descending_sort(lib, width, n):
+    """Device-side ranking of predictor scores: the n best ids, descending score, equal scores in
+    ascending id (the scores below repeat values on purpose)."""
+    rng = np.random.default_rng(5 + width)
+    scores = np.round(rng.standard_normal(width) * 3).astype(np.float32) / 2     # many exact ties
+    sd = dev(scores)
+    out = torch.full((n,), -7, dtype=torch.int32, device="cuda")
+    _lib.call("pm_k_rank_topn", ptr(sd), width, n, ptr(out), None)
+    torch.cuda.synchronize()
+    want = np.argsort(-scores.astype(np.float64), kind="stable")[:n]
+    assert np.array_equal(out.cpu().numpy(), want.astype(np.int32))
+    assert np.array_equal(want, om.rank_experts(scores.astype(np.float64), n))
+    with pytest.raises(_lib.PromoeError):
+        _lib.call("pm_k_rank_topn", ptr(sd), width, width + 1, ptr(out), None)

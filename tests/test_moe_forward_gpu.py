@@ -87,12 +87,15 @@ def test_prefetch_requests_interleaved(lib):
     cache.close()
 
 
-def test_predictor_inside_forward(lib):
+@pytest.mark.parametrize("device_topn", [True, False])
+def test_predictor_inside_forward(lib, device_topn):
     """With predict_from_moe_input the forward runs the predictor MLP on its own input, ranks
-    the scores on the host and prefetches the predicted layers before it reports its own."""
+    the scores (on the device: the host reads the best ids; or on the host from all scores) and
+    prefetches the predicted layers before it reports its own."""
     model = TinyModel(seed=9, L=5, E=12, H=128, I=64, k=3)
     cfg = dict(cache_rate=0.5, num_predict_expert_per_layer=3, predict_from_moe_input=True)
     cache = model.make_cache(**cfg)
+    cache.set("device_topn", "1" if device_topn else "0")
     rng = np.random.default_rng(2)
     D = 32
     mapping = []  # (src, dst) pairs of the default window: 0 -> [0,1), 1 -> [1,4), l>=2 -> l+2
@@ -130,6 +133,7 @@ def test_predictor_inside_forward(lib):
             check_output(y, ref_y)
     assert cache.events() == oc.events
     assert cache.stats()["prefetch_miss"] > 0
+    assert (int(cache.get("topn_launches")) > 0) == device_topn
     cache.close()
 
 
