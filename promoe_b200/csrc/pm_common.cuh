@@ -132,7 +132,7 @@ bool resident_ffn_available(int max_rows);
 
 // Launches of at most kSplitMaxRows rows per chunk run as ONE cooperative kernel (gate/up tiles,
 // then down tiles, a chunk's down tiles waiting on its gate/up tiles through the blob's counters),
-// bf16 and uint4 alike (uint4: up to kMaxFusedGroupsQ4 chunks); anything else runs as a gate/up and
+// bf16 and uint4 alike (up to kMaxFusedGroups / kMaxFusedGroupsQ4 chunks); anything else runs as a gate/up and
 // a down launch, and mid_event (optional) is recorded between the two. err (optional): device word
 // that receives a code when a bounded wait of the fused kernel gives up (default: the blob's own
 // error word).
@@ -141,7 +141,7 @@ cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& 
                               __nv_bfloat16* hbuf, int ld_h, float* yexp, cudaStream_t s,
                               cudaEvent_t mid_event = nullptr, int32_t* err = nullptr);
 inline bool ffn_launch_is_fused(const FfnPlanInfo& info, int quant4) {
-  return info.max_rows <= kSplitMaxRows && (!quant4 || info.n_desc <= kMaxFusedGroupsQ4);
+  return info.max_rows <= kSplitMaxRows && info.n_desc <= (quant4 ? kMaxFusedGroupsQ4 : kMaxFusedGroups);
 }
 
 // uint4 group-128 matrix [rows, K] (packed words + {scale, zero} fp16 pairs) -> bf16 [rows, K].

@@ -614,7 +614,7 @@ int flush_segment_tc(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const _
   return PM_OK;
 }
 
-// Rows per expert from which a segment of uint4 experts is expanded to bf16 and run on the tensor
+// Rows per expert from which uint4 experts are expanded to bf16 and run on the tensor
 // cores: below it, re-reading the packed weights once per 16 rows is cheaper than writing and
 // re-reading four times as many bf16 bytes.
 constexpr int kQ4ExpandMinRows = 64;
@@ -657,7 +657,10 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
   // kinds in one layer call). uint4 groups change over later: expanding an expert to bf16 costs more
   // than re-reading its packed weights a few times.
   const bool tc_ok = w.quant4 ? tc_prefill_usable_q4(c, w) : tc_prefill_usable(c, w);
-  const int most_small = w.quant4 ? kQ4ExpandMinRows - 1 : kSplitMaxRows;
+  // Up to kMaxChunkRows rows a group runs as chunks of 16 rows through the split-K tiles (its weights
+  // are read once from HBM and again from L2 for the later chunks): a 128-row tensor-core tile would be
+  // mostly padding there, and a few such groups alone give that kernel too few CTAs to stream from.
+  const int most_small = w.quant4 ? kQ4ExpandMinRows - 1 : kMaxChunkRows;
   Segment big;
   if (tc_ok) {
     size_t keep = 0;
@@ -695,7 +698,8 @@ int flush_segment(pm_ctx* c, Segment* seg, const pm_layer_weights& w, const __nv
     return PM_OK;
   }
   FfnPlanInfo info;
-  const int chunk_rows = w.quant4 ? kSplitMaxRows : kMaxChunkRows;
+  // without the tensor-core path (shapes it cannot tile) larger groups stay in 64-row chunks for the staged kernel
+  const int chunk_rows = (w.quant4 || tc_ok) ? kSplitMaxRows : kMaxChunkRows;
   int rc = plan_groups_size(seg->groups.data(), (int)seg->groups.size(), w.hidden, &info, chunk_rows);
   if (rc != PM_OK) return rc;
   if (*desc_used + info.blob_bytes() > c->plan_cap) return fail(PM_ERR_STATE, "launch plan buffer overflow");

@@ -1063,7 +1063,6 @@ cudaError_t launch_swiglu_ffn(const unsigned char* blob_dev, const FfnPlanInfo& 
   const int max_rows = info.max_rows;
   cudaError_t e;
   if (ffn_launch_is_fused(info, quant4)) {
-    if (info.n_desc > kMaxFusedGroups) return cudaErrorInvalidValue;
     FusedLaunch a{};
     a.groups = groups;
     a.n_groups = info.n_desc;
