@@ -171,10 +171,10 @@ int pm_iter_marks_read(pm_ctx* ctx, pm_stats* out, size_t cap, size_t* n);
 /* Device time and weight bytes of the grouped FFN launches made while the context option
  * profile_ffn=1 was set (CUDA events on the caller's stream around each launch). */
 typedef struct pm_profile {
-  int64_t ffn_launches;  /* gate/up + down launch pairs (two-launch path) */
+  int64_t ffn_launches;  /* gate/up + down launch pairs (tensor-core tiles, staged kernel) */
   double gateup_ms, down_ms;
   int64_t gateup_bytes, down_bytes; /* weight bytes those launches had to read once */
-  int64_t fused_launches; /* single cooperative launches (gate/up, grid barrier, down) */
+  int64_t fused_launches; /* single cooperative launches (gate/up and down tiles, per-chunk counters) */
   double fused_ms;
   int64_t fused_bytes;
   int64_t resident_launches; /* the part of the fused figures that belongs to device-planned launches */

@@ -628,7 +628,10 @@ class PrefetchMngr:
                 self._cache.prefetch_layer(start + i, order[i].tolist())
 
     def report_moe_attn_logits(self, layer_id: int, attn_logits: torch.Tensor):
-        pass  # only the moe_layer_logits input mode has a device predictor
+        # The separate-model predictor ignores attention logits, as the reference's does (the base
+        # class method is empty, src/cpp_worker/predictor.hpp:53); only the legacy predictor's input
+        # modes consume them, and those have no device path here.
+        return None
 
     def report_moe_layer_logits(self, layer_id: int, layer_logits: torch.Tensor):
         if layer_id == 0 and layer_logits.dim() == 3:

@@ -3,10 +3,12 @@
 //   gate/up : h[r, i] = silu(x_r . Wg[i, :]) * (x_r . Wu[i, :])
 //   down    : y[r, n] = h_r . Wd[n, :]
 // Three kernels share the arithmetic: the fused decode kernel (chunks of at most 16 token rows,
-// one cooperative launch for both passes), the uint4 decode kernel (two launches) and the staged
-// kernel for chunks of up to 64 rows (two launches; every CTA tile streams 64 weight rows, 4 warps
-// x 16 rows, and applies them to all token rows of its chunk). Every weight byte of an activated
-// expert is read exactly once with warp-level bf16 MMAs and fp32 accumulation: the kernels are
+// bf16 or uint4 weights, one cooperative launch for both passes), the two-launch uint4 kernel
+// (launches with more chunks than the fused kernel's table holds) and the staged kernel for chunks
+// of up to 64 rows (two launches; every CTA tile streams 64 weight rows, 4 warps x 16 rows, and
+// applies them to all token rows of its chunk; used where the tensor-core path cannot tile the
+// shapes and by the stateless entry point). Every weight byte of an activated expert is read once
+// from HBM per chunk with warp-level bf16 MMAs and fp32 accumulation: the bf16 kernels are
 // HBM-bound and the weight bytes are the algorithmic traffic.
 //
 // It replaces the per-expert Python loop over torch linears that the reference
