@@ -216,7 +216,7 @@ def launch_kinds(prof):
 def roofline_entry(prof, gu_gbs, dn_gbs, fu_gbs, peak, peak_src):
     """Roofline of the dominant FFN kernel (by device time) from the library's CUDA-event timing of every
     FFN launch: the fused split-K kernel, or the gate/up + down launch pair (tensor-core tiles for
-    groups of more than 16 rows)."""
+    groups of more than 64 rows)."""
     pair_ms = prof["gateup_ms"] + prof["down_ms"]
     fused = None
     if prof["fused_launches"] > 0:
@@ -236,7 +236,7 @@ def roofline_entry(prof, gu_gbs, dn_gbs, fu_gbs, peak, peak_src):
         n = prof["ffn_launches"]
         both = (prof["gateup_bytes"] + prof["down_bytes"]) / (pair_ms / 1e3) / 1e9
         pair = {"bound": "hbm", "kernel": "gate/up + down launch pair (prefill_ffn_kernel tensor-core tiles for groups "
-                                          "of more than 16 rows; weight bytes over both launches)",
+                                          "of more than 64 rows; weight bytes over both launches)",
                 "achieved": both, "peak": peak, "unit": "GB/s", "frac": both / peak, "peak_source": peak_src,
                 "traffic": None, "launches": n, "avg_launch_us": pair_ms * 1e3 / n,
                 "bytes_per_launch": (prof["gateup_bytes"] + prof["down_bytes"]) / n, "frac_of_8tbs_nominal": both / 8000.0,

@@ -133,7 +133,7 @@ struct pm_ctx {
   size_t h_stage_bytes = 0;
 
   // ---- prefill (tcgen05) path ---------------------------------------------------------------------
-  bool tc_prefill = true;             // use it for segments with more than 16 rows per expert
+  bool tc_prefill = true;             // use it for experts with more than 64 rows in a call
   __nv_bfloat16* d_xperm = nullptr;   // expert-sorted copy of the token rows [rows, hidden]
   unsigned char* d_tc_plan = nullptr; // groups + tiles of the segments of one layer call
   unsigned char* h_tc_plan = nullptr; // pinned staging of the same
